@@ -1,0 +1,112 @@
+"""Generates tests/golden/ref_vectors.npz from the reference's own portable C++.
+
+Run in a container that has the reference checkout (``make -C oracle ref`` first).  Inputs are
+drawn with the reference's seeded generators (test/common/data_generator.h: mt19937, seed 42 for
+A and C, 123 for B, 7 for bias) on the shape lists of its gtest suites
+(test/gemm/test_gemm_i8_i8_rvv.cpp:31-41, test/gemm/test_gemm_f16_i4_rvv.cpp:19-49); outputs
+come from the reference functions behind oracle/ref_shim.cpp.  The file is small (< 1 MB) and
+committed, so the pins also run where the reference checkout does not exist.
+"""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(HERE, "..", ".."))
+from oracle.tqo import TD_F16, TD_F32, Reference  # noqa: E402
+
+I8_SHAPES = [(32, 32, 32, False), (3, 8, 11, False), (5, 11, 10, False), (9, 19, 23, False),
+             (15, 32, 25, False), (60, 63, 127, False), (32, 32, 32, True), (60, 63, 127, True)]
+# (m, n, k, bl, bias, c, clamp)
+W4A16_CASES = [(8, 8, 4, 2, 0, 0, None), (16, 16, 8, 2, 0, 0, None), (32, 32, 32, 2, 0, 0, None),
+               (32, 32, 32, 4, 0, 0, None), (32, 32, 32, 32, 0, 0, None), (5, 11, 10, 2, 0, 0, None),
+               (7, 3, 10, 2, 0, 0, None), (17, 19, 24, 4, 0, 0, None), (31, 35, 64, 32, 0, 0, None),
+               (60, 61, 128, 32, 0, 0, None), (32, 32, 32, 2, 1, 0, None), (17, 19, 24, 4, 1, 0, None),
+               (32, 32, 32, 4, 0, 0, (-0.5, 0.5)), (32, 32, 32, 4, 0, 1, None),
+               (32, 32, 32, 4, 1, 1, (-0.5, 0.5))]
+MULTIPLIERS = [0.0025, 0.0, 1.0, 0.5, 0.75, 1e-12, 1e-9, 2.0 ** -31, 2.0 ** -32, 2.0 ** -33, 123.456,
+               0.05 * 0.001 / 0.1, 0.05 * 0.01 / 0.1, 0.9999999999, 0.99999999999999989,
+               1.0 - 2.0 ** -31, 1.0 - 2.0 ** -32, 0.5 + 2.0 ** -32, 0.5 + 3 * 2.0 ** -33,
+               0.5 + 2.0 ** -33, -0.0025, -1.5, 3.0e-5, 7.7e-3, 1.0 / 3.0, 2.0 / 3.0]
+
+
+def main():
+    ref = Reference()
+    assert ref.available(), "build oracle/_ref first: make -C oracle ref"
+    out = {}
+    # ---- gemm_clamp_i32_i8_i8: int8 in U[-50,50], C in U[-1000,1000], clamp +-100000 ----------
+    for idx, (m, n, k, has_c) in enumerate(I8_SHAPES):
+        A = ref.fill_uniform((m, k), np.int8, -50, 50, 42)
+        Bt = ref.fill_uniform((n, k), np.int8, -50, 50, 123)   # [n, k]
+        Bn = ref.fill_uniform((k, n), np.int8, -50, 50, 123)   # [k, n]
+        Cm = ref.fill_uniform((m, n), np.int32, -1000, 1000, 42) if has_c else None
+        out[f"i8_{idx}_A"], out[f"i8_{idx}_Bt"], out[f"i8_{idx}_Bn"] = A, Bt, Bn
+        if has_c:
+            out[f"i8_{idx}_C"] = Cm
+        out[f"i8_{idx}_Dt"] = ref.gemm_i32_i8(A, Bt, True, Cm, (-100000, 100000))
+        out[f"i8_{idx}_Dn"] = ref.gemm_i32_i8(A, Bn, False, Cm, (-100000, 100000))
+        # a narrow clamp so that both clamp edges are exercised
+        out[f"i8_{idx}_Dn_narrow"] = ref.gemm_i32_i8(A, Bn, False, Cm, (-3000, 2500))
+    out["i8_shapes"] = np.array([(m, n, k, int(c)) for m, n, k, c in I8_SHAPES], np.int64)
+    # ---- requantisation multiplier ---------------------------------------------------------
+    ms = [ref.quantize_multiplier(v) for v in MULTIPLIERS]
+    rng = np.random.default_rng(5)
+    rnd = np.concatenate([rng.uniform(1e-6, 1.0, 200), np.exp(rng.uniform(-30, 5, 200))])
+    out["mult_in"] = np.concatenate([np.array(MULTIPLIERS, np.float64), rnd])
+    out["mult_out"] = np.array([ref.quantize_multiplier(float(v)) for v in out["mult_in"]], np.int64)
+    assert ms[0] == (1374389535, -8)
+    # ---- scalar quantiser ----------------------------------------------------------------
+    vals = rng.normal(0, 2, 4000).astype(np.float32)
+    scales = rng.uniform(1e-3, 0.1, 4000).astype(np.float32)
+    zps = rng.integers(-128, 128, 4000).astype(np.int32)
+    vals[:8] = [0.5, 1.5, 2.5, -0.5, -1.5, 1e9, -1e9, 0.0]
+    scales[:8] = 1.0
+    zps[:8] = 0
+    out["qi8_val"], out["qi8_scale"], out["qi8_zp"] = vals, scales, zps
+    out["qi8_out"] = np.array([ref.lib.ref_quantize_i8(float(v), float(s), int(z))
+                               for v, s, z in zip(vals, scales, zps)], np.int8)
+    # ---- zero-point fusion ------------------------------------------------------------------
+    data = ref.fill_uniform((19, 23), np.int8, -128, 127, 123)
+    bias = ref.fill_uniform((1, 19), np.int32, -1000, 1000, 7).reshape(19)
+    out["fuse_data"], out["fuse_bias"] = data, bias
+    out["fuse_out"] = ref.fuse_zp_to_bias(bias, data, 3)
+    # ---- 16-bit float conversions ----------------------------------------------------------
+    bits = rng.integers(0, 2 ** 32, 6000, dtype=np.uint64).astype(np.uint32)
+    f = bits.view(np.float32)
+    f = f[np.isfinite(f)]
+    special = np.array([0.0, -0.0, 65504.0, 65519.99, 65520.0, 1e-8, 5.96e-8, 2.98e-8, 2.9802322e-8,
+                        6.1e-5, 6.0975552e-5, 1.0009765625, 1.00048828125, 1.00146484375, 3.0e38,
+                        -3.0e38, 1e-40], np.float32)
+    f = np.concatenate([special, f, rng.normal(0, 1, 3000).astype(np.float32)])
+    out["cvt_in"] = f
+    out["cvt_f16"] = np.array([ref.lib.ref_f32_to_f16(float(x)) for x in f], np.uint16)
+    out["cvt_bf16"] = np.array([ref.lib.ref_f32_to_bf16(float(x)) for x in f], np.uint16)
+    # ---- W4A16 ------------------------------------------------------------------------------
+    for idx, (m, n, k, bl, has_bias, has_c, clamp) in enumerate(W4A16_CASES):
+        A = ref.fill_uniform((m, k), np.float16, -1.0, 1.0, 42)
+        W = ref.fill_uniform((n, k), np.float16, -1.0, 1.0, 123)
+        nib, sc = ref.quantize_fp16_to_int4(W.view(np.uint16), bl)
+        out[f"w4a16_{idx}_A"], out[f"w4a16_{idx}_W"] = A, W
+        out[f"w4a16_{idx}_nib"], out[f"w4a16_{idx}_scale"] = nib, sc
+        cl = clamp if clamp else (-65504.0, 65504.0)
+        for td, tag, dt in ((TD_F16, "f16", np.float16), (TD_F32, "f32", np.float32)):
+            Cm = ref.fill_uniform((m, n), dt, -5.0, 5.0, 42) if has_c else None
+            bias = ref.fill_uniform((1, n), dt, -0.5, 0.5, 7).reshape(n) if has_bias else None
+            if has_c:
+                out[f"w4a16_{idx}_C_{tag}"] = Cm
+            if has_bias:
+                out[f"w4a16_{idx}_bias_{tag}"] = bias
+            cv = None if Cm is None else (Cm.view(np.uint16) if td == TD_F16 else Cm)
+            bv = None if bias is None else (bias.view(np.uint16) if td == TD_F16 else bias)
+            cl_td = cl if clamp else ((-65504.0, 65504.0) if td == TD_F16 else (-3.4028234663852886e38, 3.4028234663852886e38))
+            out[f"w4a16_{idx}_D_{tag}"] = ref.gemm_w4a16(A.view(np.uint16), nib, sc, bl, td, cv, bv, cl_td)
+    out["w4a16_cases"] = np.array([(m, n, k, bl, b, c, 0 if cl is None else 1)
+                                   for m, n, k, bl, b, c, cl in W4A16_CASES], np.int64)
+    path = os.path.join(HERE, "ref_vectors.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    main()

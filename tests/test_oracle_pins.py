@@ -1,0 +1,194 @@
+"""Pins the restated CPU oracle (oracle/tqt_oracle.c) against the reference.
+
+Two sources: the committed golden vectors generated from the reference's own portable C++
+(tests/golden/make_golden.py) and, where oracle/_ref has been built, the same functions live.
+"""
+import numpy as np
+import pytest
+
+from oracle.tqo import TD_BF16, TD_F16, TD_F32, Reference
+
+FMAX = 3.4028234663852886e38
+
+
+def test_known_answer_quantize_multiplier(oracle):
+    # produced by the reference's tqt_quantize_multiplier (src/gemm/gemm_i8_i8/tqt_utils_i8_i8.h:98-132)
+    assert oracle.quantize_multiplier(0.0025) == (1374389535, -8)
+    assert oracle.quantize_multiplier(0.0) == (0, 0)
+
+
+def test_quantize_multiplier_golden(oracle, golden):
+    for v, (m, s) in zip(golden["mult_in"], golden["mult_out"]):
+        assert oracle.quantize_multiplier(float(v)) == (int(m), int(s)), v
+
+
+def test_gemm_i32_golden(oracle, golden):
+    for idx, (m, n, k, has_c) in enumerate(golden["i8_shapes"]):
+        A, Bt, Bn = golden[f"i8_{idx}_A"], golden[f"i8_{idx}_Bt"], golden[f"i8_{idx}_Bn"]
+        Cm = golden[f"i8_{idx}_C"] if has_c else None
+        assert np.array_equal(oracle.gemm_clamp_i32_i8_i8(A, Bt, True, Cm, (-100000, 100000)), golden[f"i8_{idx}_Dt"])
+        assert np.array_equal(oracle.gemm_clamp_i32_i8_i8(A, Bn, False, Cm, (-100000, 100000)), golden[f"i8_{idx}_Dn"])
+        assert np.array_equal(oracle.gemm_clamp_i32_i8_i8(A, Bn, False, Cm, (-3000, 2500)), golden[f"i8_{idx}_Dn_narrow"])
+
+
+def test_quantize_i8_golden(oracle, golden):
+    got = np.array([oracle.lib.tqo_quantize_i8(float(v), float(s), int(z))
+                    for v, s, z in zip(golden["qi8_val"], golden["qi8_scale"], golden["qi8_zp"])], np.int8)
+    assert np.array_equal(got, golden["qi8_out"])
+
+
+def test_fuse_zp_golden(oracle, golden):
+    assert np.array_equal(oracle.fuse_zp_to_bias(golden["fuse_bias"], golden["fuse_data"], 3), golden["fuse_out"])
+
+
+def test_half_conversions_golden(oracle, golden):
+    f = golden["cvt_in"]
+    f16 = np.array([oracle.lib.tqo_f32_to_f16(float(x)) for x in f], np.uint16)
+    bf16 = np.array([oracle.lib.tqo_f32_to_bf16(float(x)) for x in f], np.uint16)
+    assert np.array_equal(f16, golden["cvt_f16"])
+    assert np.array_equal(bf16, golden["cvt_bf16"])
+    # widening is exact: compare with numpy's for every f16 pattern
+    allh = np.arange(65536, dtype=np.uint16)
+    want = allh.view(np.float16).astype(np.float32)
+    got = np.array([oracle.lib.tqo_f16_to_f32(int(h)) for h in allh], np.float32)
+    assert np.array_equal(got.view(np.uint32)[~np.isnan(want)], want.view(np.uint32)[~np.isnan(want)])
+
+
+def test_w4a16_golden(oracle, golden):
+    for idx, (m, n, k, bl, has_bias, has_c, has_clamp) in enumerate(golden["w4a16_cases"]):
+        A, W = golden[f"w4a16_{idx}_A"], golden[f"w4a16_{idx}_W"]
+        nib, sc = oracle.quantize_fp16_to_int4(W.view(np.uint16), int(bl))
+        assert np.array_equal(nib, golden[f"w4a16_{idx}_nib"])
+        assert np.array_equal(sc, golden[f"w4a16_{idx}_scale"])
+        for td, tag in ((TD_F16, "f16"), (TD_F32, "f32")):
+            Cm = golden[f"w4a16_{idx}_C_{tag}"] if has_c else None
+            bias = golden[f"w4a16_{idx}_bias_{tag}"] if has_bias else None
+            if td == TD_F16:
+                Cm = None if Cm is None else Cm.view(np.uint16)
+                bias = None if bias is None else bias.view(np.uint16)
+            clamp = (-0.5, 0.5) if has_clamp else ((-65504.0, 65504.0) if td == TD_F16 else (-FMAX, FMAX))
+            D = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, int(bl), td, Cm, bias, clamp)
+            want = golden[f"w4a16_{idx}_D_{tag}"]
+            assert np.array_equal(D.view(np.uint8), want.view(np.uint8)), (idx, tag)
+
+
+def test_w4a8_integer_core_against_i32_golden(oracle, golden):
+    """The W4A8 restatement has no compilable counterpart; its integer core is pinned by
+    unpacking nibbles to int8 and comparing with the pinned int32 GEMM: with scale 1, zero point 0
+    the f32 output equals float(acc) exactly while |acc| < 2^24."""
+    rng = np.random.default_rng(11)
+    for (m, n, k) in [(8, 8, 8), (5, 11, 16), (7, 3, 8), (17, 19, 24), (31, 35, 64), (60, 61, 128)]:
+        A = rng.integers(-128, 128, (m, k), dtype=np.int8)
+        q = rng.integers(-8, 8, (n, k), dtype=np.int8)
+        nib = ((q[:, 0::2] + 8).astype(np.uint8) | ((q[:, 1::2] + 8).astype(np.uint8) << 4)).astype(np.uint8)
+        sa = np.ones(m, np.float32)
+        zp = np.zeros(m, np.int32)
+        sb = np.ones(n, np.float32)
+        D = oracle.gemm_w4a8(A, np.ascontiguousarray(nib), sa, zp, sb, TD_F32)
+        want = oracle.gemm_clamp_i32_i8_i8(A, np.ascontiguousarray(q), True)
+        assert np.array_equal(D, want.astype(np.float32))
+        # zero-point correction: acc - zp * rowsum(q)
+        zp2 = rng.integers(-128, 128, m).astype(np.int32)
+        D2 = oracle.gemm_w4a8(A, np.ascontiguousarray(nib), sa, zp2, sb, TD_F32)
+        want2 = want.astype(np.int64) - zp2[:, None].astype(np.int64) * q.sum(1, dtype=np.int64)[None, :]
+        assert np.array_equal(D2, want2.astype(np.float32))
+
+
+def test_w4a8_quantisers_and_epilogue_numpy(oracle):
+    """Cross-check of the restated quantisers and float epilogue against an independent numpy
+    statement of the formulas in test/gemm/test_gemm_i8_i4_rvv.cpp:40-156."""
+    rng = np.random.default_rng(3)
+    m, n, k = 17, 19, 24
+    A = rng.normal(0, 1, (m, k)).astype(np.float32)
+    A[3] = 0.0                 # all-zero row: scale 1, zp 0
+    A[4] = np.abs(A[4])        # all-positive row: fmin forced to 0
+    W = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+    W[2] = 0.0
+    q, s, z = oracle.quantize_a_per_row_asym(A)
+    fmin = np.minimum(A.min(1), 0).astype(np.float32)
+    fmax = np.maximum(A.max(1), 0).astype(np.float32)
+    s_np = ((fmax - fmin) / np.float32(255.0)).astype(np.float32)
+    for r in range(m):
+        if s_np[r] == 0:
+            assert s[r] == 1.0 and z[r] == 0 and not q[r].any()
+            continue
+        assert s[r] == s_np[r]
+        zp = int(np.clip(np.rint(np.float32(-128.0) - fmin[r] / s_np[r]), -128, 127))
+        assert z[r] == zp
+        want = np.clip(np.rint(A[r] / s_np[r]) + np.float32(zp), -128, 127).astype(np.int8)
+        assert np.array_equal(q[r], want)
+    nib, sb = oracle.quantize_b_per_channel_sym_int4(W)
+    amax = np.abs(W).max(1)
+    sb_np = np.where(amax == 0, np.float32(1.0), amax / np.float32(8.0)).astype(np.float32)
+    assert np.array_equal(sb, sb_np)
+    qw = np.clip(np.rint(W / sb_np[:, None]), -8, 7).astype(np.int32)
+    assert np.array_equal(nib & 0xF, (qw[:, 0::2] + 8))
+    assert np.array_equal(nib >> 4, (qw[:, 1::2] + 8))
+    bias = rng.normal(0, 0.1, n).astype(np.float32)
+    Cm = rng.uniform(-2, 2, (m, n)).astype(np.float32)
+    D = oracle.gemm_w4a8(q, nib, s, z, sb, TD_F32, Cm, bias, (-0.5, 0.5))
+    acc = q.astype(np.int64) @ qw.T.astype(np.int64) - z[:, None].astype(np.int64) * qw.sum(1)[None, :]
+    r = (acc.astype(np.float32) * s[:, None]).astype(np.float32) * sb[None, :]
+    r = (r + Cm).astype(np.float32)
+    r = (r + bias[None, :]).astype(np.float32)
+    r = np.clip(r, np.float32(-0.5), np.float32(0.5))
+    assert np.array_equal(D, r)
+    # bf16 / f16 outputs are the f32 result rounded to nearest even
+    Dh = oracle.gemm_w4a8(q, nib, s, z, sb, TD_F16, None, None, (-65504.0, 65504.0))
+    Df = oracle.gemm_w4a8(q, nib, s, z, sb, TD_F32)
+    assert np.array_equal(Dh, Df.astype(np.float16).view(np.uint16))
+    Db = oracle.gemm_w4a8(q, nib, s, z, sb, TD_BF16, None, None, (-65504.0, 65504.0))
+    u = Df.view(np.uint32).astype(np.uint64)
+    want_b = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    assert np.array_equal(Db, want_b)
+
+
+def test_requant_tail_semantics(oracle):
+    """The integer tail follows the RVV sequence (vmulh, vsra with the low five shift bits, wrapping
+    add, two saturating narrows): spot values worked out by hand."""
+    f = oracle.lib.tqo_requantize_one
+    assert f(400, 1 << 30, 0, 0) == 100           # mulh(400, 2^30) = 100
+    assert f(-1, 1 << 30, 0, 0) == -1             # floor, not round-to-zero
+    assert f(-400, 1 << 30, 3, 0) == -13          # -100 >> 3 = floor(-12.5)
+    assert f(1 << 30, 0x7FFFFFFF, 0, 5) == 127    # saturates
+    assert f(-(1 << 30), 0x7FFFFFFF, 0, 5) == -128
+    assert f(400, 1 << 30, 32 + 1, 0) == 50       # shift operand uses only its low five bits
+    rng = np.random.default_rng(0)
+    m, n, k = 9, 19, 23
+    A = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    Bt = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    bias = rng.integers(-1000, 1000, n).astype(np.int32)
+    sb = rng.uniform(0.001, 0.01, n).astype(np.float32)
+    D = oracle.gemm_reqi32toi8(A, Bt, True, 0.05, sb, 3.0, -5, bias)
+    acc = A.astype(np.int64) @ Bt.T.astype(np.int64) + bias[None, :]
+    for j in range(n):
+        real = float(np.float32(0.05)) * float(sb[j]) / float(np.float32(3.0))
+        mult, s = oracle.quantize_multiplier(real)
+        sh = (-s - 1) & 31
+        t = ((acc[:, j] * mult) >> 32) >> sh
+        t = np.clip(t - 5, -128, 127)
+        assert np.array_equal(D[:, j], t.astype(np.int8))
+    # per-tensor mode shares column 0's multiplier
+    D1 = oracle.gemm_reqi32toi8(A, Bt, True, 0.05, sb, 3.0, -5, bias, quant_channel_b=1)
+    sb0 = np.full(n, sb[0], np.float32)
+    assert np.array_equal(D1, oracle.gemm_reqi32toi8(A, Bt, True, 0.05, sb0, 3.0, -5, bias))
+
+
+def test_live_reference_when_built(oracle):
+    ref = Reference()
+    if not ref.available():
+        pytest.skip("oracle/_ref not built on this machine")
+    rng = np.random.default_rng(2)
+    for v in np.exp(rng.uniform(-40, 10, 3000)):
+        assert oracle.quantize_multiplier(float(v)) == ref.quantize_multiplier(float(v))
+    A = rng.integers(-128, 128, (33, 70), dtype=np.int8)
+    B = rng.integers(-128, 128, (70, 41), dtype=np.int8)
+    assert np.array_equal(oracle.gemm_clamp_i32_i8_i8(A, B, False), ref.gemm_i32_i8(A, B, False))
+    # every f16 bit pattern round-trips, and a dense sweep of f32 inputs narrows identically
+    f = rng.integers(0, 2 ** 32, 200000, dtype=np.uint64).astype(np.uint32).view(np.float32)
+    f = f[np.isfinite(f)]
+    f = np.concatenate([f, rng.normal(0, 1, 50000).astype(np.float32) * np.float32(1e-6),
+                        rng.normal(0, 300, 50000).astype(np.float32) * np.float32(200.0)])
+    for x in f[::7]:
+        assert oracle.lib.tqo_f32_to_f16(float(x)) == ref.lib.ref_f32_to_f16(float(x)), x
+        assert oracle.lib.tqo_f32_to_bf16(float(x)) == ref.lib.ref_f32_to_bf16(float(x)), x
