@@ -1,0 +1,76 @@
+/*
+ * Extensions of the B200 library that have no function of the same name in the reference.
+ */
+#ifndef TQT_B200_EXT_H
+#define TQT_B200_EXT_H
+
+#include "tqt_b200_common.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/*
+ * qai8dx: dynamic per-row asymmetric int8 quantisation of activations, fused with the LHS pack.
+ * In the reference this arithmetic exists only as a test/example helper
+ * (quantize_a_per_row_asym, test/gemm/test_gemm_i8_i4_rvv.cpp:40-77, with quantize_i8,
+ * test/common/test_common.h:232-240); run_a_pack there takes already quantised int8.  Per row:
+ *   fmin = min(0, min x), fmax = max(0, max x), s = (fmax - fmin) / 255;
+ *   s == 0 -> scale 1, zero point 0, q = 0;
+ *   zp = clamp(nearbyintf(-128 - fmin / s), -128, 127); q = clamp(nearbyintf(x / s) + zp, -128, 127)
+ * with true IEEE division and round-half-to-even, so the int8 values are bit-identical to the
+ * helper's.  A is [m,k] row-major (lda in elements) of f32 / f16 / bf16; A_packed is the packed
+ * LHS layout of the qai8dxp kernel types (size from their get_a_packed_size); scale_a [m] and
+ * zero_point_a [m] are device arrays.
+ */
+void tqt_run_quant_pack_qai8dxp_f32_128x128_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_packed,
+                                                   float *scale_a, int32_t *zero_point_a);
+void tqt_run_quant_pack_qai8dxp_f16_128x128_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_packed,
+                                                   float *scale_a, int32_t *zero_point_a);
+void tqt_run_quant_pack_qai8dxp_bf16_128x128_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_packed,
+                                                    float *scale_a, int32_t *zero_point_a);
+/* Same quantiser with a plain row-major int8 result [m,k] (ldq in elements), for the unpacked
+ * (qai8dx) kernel types and for inspection. */
+void tqt_run_quant_qai8dx_f32_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_q, size_t ldq,
+                                     float *scale_a, int32_t *zero_point_a);
+void tqt_run_quant_qai8dx_f16_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_q, size_t ldq,
+                                     float *scale_a, int32_t *zero_point_a);
+void tqt_run_quant_qai8dx_bf16_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_q, size_t ldq,
+                                      float *scale_a, int32_t *zero_point_a);
+
+/* Inverse of the packers, for tests and for callers that need the plain data back. */
+void tqt_run_a_unpack_i8_128x128_sm100a(size_t m, size_t k, const void *A_packed, size_t lda_packed, void *A,
+                                        size_t lda);
+void tqt_run_bt_unpack_qsi4cxp_128x128_sm100a(size_t n, size_t k, const void *B_packed, size_t ldb_packed,
+                                              void *B, size_t ldb);
+void tqt_run_bt_unpack_qsi4c2p_128x128_sm100a(size_t n, size_t k, const void *B_packed, size_t ldb_packed,
+                                              void *B, size_t ldb);
+void tqt_run_a_unpack_f16_128x128_sm100a(size_t m, size_t k, const void *A_packed, size_t lda_packed, void *A,
+                                         size_t lda);
+
+/*
+ * Column-parallel sharding of the weight matrix across the GPUs of one node.  The reference has no
+ * multi-device code; its tile-portion API (any n_idx that is a multiple of n_step, params arrays
+ * indexed from the call's own origin) is what makes the shards independent.  Rank r of `world`
+ * owns output columns [n_begin, n_begin + n_count): contiguous ranges whose starts are multiples
+ * of 128, sizes differing by at most one 128-column block.  Every rank runs the unchanged
+ * single-GPU kernels on its slice of B_packed / scale_b / bias and a replica of A.
+ */
+void tqt_shard_plan_n(size_t n, size_t world, size_t rank, size_t *n_begin, size_t *n_count);
+
+/* Which device kernel a run_gemm call of the given shape would launch: 0 = tcgen05 tensor-core
+ * GEMM, 1 = HBM-streaming GEMV (m <= 16), 2 = generic CUDA-core kernel (unpacked operands). */
+int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k);
+
+#if !defined(TQT_B200_NO_HALF_TYPES)
+/* Return the bit pattern of a 16-bit float received by value: lets a foreign-function binding
+ * verify how it passes the clamp arguments of the f16 / bf16 kernel types. */
+uint16_t tqt_cuda_debug_f16_bits(float16_t v);
+uint16_t tqt_cuda_debug_bf16_bits(bfloat16_t v);
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TQT_B200_EXT_H */

@@ -1,0 +1,133 @@
+"""CPU-only checks of the C ABI: the library loads, exports every symbol the headers declare,
+and its host-side helpers (steps, offsets, sizes, shard plan, half-by-value passing) compute what
+the headers say.  No kernel is launched."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from __graft_entry__ import ROOT, load
+
+
+@pytest.fixture(scope="module")
+def pkg():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("tqt_b200_build", os.path.join(ROOT, "torq-tile_b200", "build.py"))
+    b = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(b)
+    b.build()
+    return load()
+
+
+def _declared_symbols():
+    """Expand the declaration macros of include/*.h the way the preprocessor does (g++ -E)."""
+    import subprocess
+    names = set()
+    for h in ("tqt_b200_common.h", "tqt_b200_gemm_i8_i8.h", "tqt_b200_gemm_i8_i4.h", "tqt_b200_gemm_f16_i4.h",
+              "tqt_b200_ext.h"):
+        out = subprocess.check_output(["/usr/bin/g++", "-E", "-P", "-x", "c++", os.path.join(ROOT, "include", h)], text=True)
+        names |= set(re.findall(r"\b(tqt_[a-z0-9_]+?)\s*\(", out))
+    return {n for n in names if not n.endswith("_t")}
+
+
+def test_exports_every_declared_symbol(pkg):
+    lib = pkg.lib()
+    declared = _declared_symbols()
+    assert len(declared) > 100
+    missing = [n for n in sorted(declared) if not hasattr(lib, n)]
+    assert not missing, missing
+    for uk in pkg.all_ukernels():
+        for s in uk.symbol_names():
+            assert s in declared, s
+    for s in pkg.EXTENSION_SYMBOLS:
+        assert s in declared, s
+
+
+def test_steps_and_plain_offsets(pkg):
+    for uk in pkg.all_ukernels():
+        assert uk.get_m_step() == 128 and uk.get_n_step() == 128
+    u = pkg.GemmClampI32I8I8()
+    # reference: (m_idx*lda + k_idx), (k_idx*ldb + n_idx), int32 C/D  (gemm_clamp_i32_i8_i8 ..._4x1vl_rvv.cpp:35-64)
+    assert u.get_a_offset(128, 7, 512) == 128 * 512 + 7
+    assert u.get_b_offset(256, 3, 1000) == 3 * 1000 + 256
+    assert u.get_c_offset(128, 256, 300) == (128 * 300 + 256) * 4
+    assert u.get_d_offset(128, 256, 300) == (128 * 300 + 256) * 4
+    assert u.get_d_size(5, 7) == 140
+    w = pkg.GemmW4A8("bf16")
+    assert w.get_c_offset(128, 128, 1000) == (128 * 1000 + 128) * 2
+    assert w.get_bias_offset(256) == 512 and w.get_d_size(3, 5) == 30
+    assert pkg.GemmW4A8("f32").get_d_offset(128, 0, 10) == 128 * 10 * 4
+    r = pkg.GemmReqI8()
+    assert r.get_d_offset(128, 128, 4096) == 128 * 4096 + 128 and r.get_bias_offset(128) == 512
+    assert r.get_c_offset(128, 0, 64) == 128 * 64 * 4
+
+
+def test_packed_sizes_and_offsets(pkg):
+    w = pkg.GemmW4A8("f32")
+    assert w.get_a_packed_size(1, 4096) == 32 * 16384
+    assert w.get_a_packed_size(2048, 4096) == 16 * 32 * 16384
+    assert w.get_b_packed_size(4096, 4096) == 32 * 32 * 8448
+    assert w.get_b_packed_size(129, 130) == 2 * 2 * 8448
+    assert w.get_b_packed_offset(256, 0, 4096, 128) == 2 * 32 * 8448
+    assert w.get_b_packed_offset(256, 384, 4096, 128) == (2 * 32 + 3) * 8448
+    assert w.get_a_packed_offset(128, 256, 4096, 128) == (32 + 2) * 16384
+    r = pkg.GemmReqI8()
+    assert r.get_b_packed_size(4096, 4096) == 32 * 32 * 16384
+    assert r.get_b_packed_offset(128, 128, 300, 128) == (3 + 1) * 16384
+    h = pkg.GemmW4A16("f16")
+    assert h.get_a_packed_size(8192, 8192) == 64 * 128 * 16384
+    assert h.get_b_packed_size(28672, 8192) == 224 * 64 * 8192
+    assert h.get_a_packed_offset(128, 64, 8192, 128) == (128 + 1) * 16384
+    assert h.get_scale_b_offset(128, 3, 256) == (128 * 256 + 3) * 2
+
+
+def test_shard_plan(pkg):
+    # the N of the three sharded configurations, at 1/2/4/8 ranks: contiguous, 128-aligned, complete
+    for n in (4096, 14336, 28672, 1000, 128, 130):
+        for world in (1, 2, 4, 8):
+            pos = 0
+            sizes = []
+            for rank in range(world):
+                b, c = pkg.shard_plan_n(n, world, rank)
+                assert b == pos and b % 128 == 0 or c == 0
+                pos = b + c
+                sizes.append(c)
+            assert pos == n
+            full = [s for s in sizes if s]
+            assert max(sizes) - min(sizes) <= 128 or n % 128
+    assert pkg.shard_plan_n(14336, 8, 3) == (3 * 1792, 1792)
+    assert pkg.shard_plan_n(28672, 8, 7) == (7 * 3584, 3584)
+
+
+def test_half_by_value_passing(pkg):
+    lib = pkg.lib()
+    lib.tqt_cuda_debug_f16_bits.restype = C.c_uint16
+    lib.tqt_cuda_debug_f16_bits.argtypes = [C.c_float]
+    lib.tqt_cuda_debug_bf16_bits.restype = C.c_uint16
+    lib.tqt_cuda_debug_bf16_bits.argtypes = [C.c_float]
+    for bits in (0x0000, 0x3C00, 0xBC00, 0x7BFF, 0xFBFF, 0x0001, 0x1234, 0xFFFF):
+        assert lib.tqt_cuda_debug_f16_bits(pkg.half_arg(bits)) == bits
+        assert lib.tqt_cuda_debug_bf16_bits(pkg.half_arg(bits)) == bits
+    assert pkg.f16_bits(65504.0) == 0x7BFF and pkg.f16_bits(-0.5) == 0xB800
+    assert pkg.bf16_bits(1.0) == 0x3F80 and pkg.bf16_bits(65504.0) == 0x4780 and pkg.bf16_bits(-65504.0) == 0xC780
+
+
+def test_status_word_without_gpu(pkg):
+    """params == NULL returns silently with status OK (reference ..._qsi4cxp_4x1vl_rvv.cpp:205-207); a
+    NULL output with a non-empty problem is rejected before any launch."""
+    w = pkg.GemmW4A8("f32")
+    w.run_gemm(4, 4, 8, 0, 8, 0, 0, 8, 0, None, 4, 0, 4, None, -1.0, 1.0, None)
+    assert pkg.lib().tqt_cuda_get_last_status() == 0
+    p = pkg.QaI8DxQsI4CxParams(16, 16, 16)
+    with pytest.raises(pkg.TqtError):
+        w.run_gemm(4, 4, 8, 16, 8, 0, 16, 8, 0, None, 4, None, 4, None, -1.0, 1.0, p)
+    assert pkg.lib().tqt_cuda_get_last_status() == 1
+    # odd k is illegal for int4 weights ("Must be a multiple of 2")
+    with pytest.raises(pkg.TqtError):
+        w.run_gemm(4, 4, 7, 16, 7, 0, 16, 7, 0, None, 4, 16, 4, None, -1.0, 1.0, p)
+    # empty problems are accepted
+    w.run_gemm(0, 4, 8, None, 8, 0, None, 8, 0, None, 4, None, 4, None, -1.0, 1.0, p)
+    assert pkg.lib().tqt_cuda_get_last_status() == 0
+    assert pkg.lib().tqt_cuda_kernel_choice_w4a8(1, 4096, 4096) == 1
+    assert pkg.lib().tqt_cuda_kernel_choice_w4a8(2048, 14336, 4096) == 0

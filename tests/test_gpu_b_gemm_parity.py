@@ -1,0 +1,211 @@
+"""GPU parity tests of the GEMM kernel types against the CPU oracle, through the C ABI.
+
+Integer outputs (int32, requantised int8) are compared bit for bit.  The W4A8 float epilogue is a
+fixed sequence of IEEE f32 operations on an exact int32 accumulator, so it is compared bit for bit
+as well (the stated bars, rel 1e-3 for f32 and 2e-2 for f16/bf16, are implied).  W4A16 accumulates
+f16 products in f32 in a different order than the oracle: tolerance rel 2e-2 with an RMS floor,
+plus the reference's own thresholds (abs 1.0, cosine 0.9999; test/common/test_common.h:47-66).
+
+Each packed kernel type is run on the path run_gemm picks by itself and, through TQT_B200_PATH, on
+the generic CUDA-core path, so that the tensor-core, GEMV and CUDA-core kernels check each other.
+"""
+import numpy as np
+import pytest
+
+from oracle.tqo import TD_BF16, TD_F16, TD_F32
+from tqt_testlib import (FMAX, bf16_bits_to_f32, cosine, f16_bits_to_f32, f32_to_bf16_bits, rel_err, run_i32_packed,
+                         run_i32_unpacked, run_requant, run_w4a16, run_w4a8)
+
+pytestmark = pytest.mark.gpu
+
+TD_CODE = {"f32": TD_F32, "f16": TD_F16, "bf16": TD_BF16}
+# shape lists of the reference's suites (test_gemm_i8_i8_rvv.cpp:31-41, test_gemm_i8_i4_rvv.cpp:164-179)
+I8_SHAPES = [(32, 32, 32), (3, 8, 11), (5, 11, 10), (9, 19, 23), (15, 32, 25), (60, 63, 127)]
+W4A8_SHAPES = [(8, 8, 8), (16, 16, 16), (32, 32, 32), (5, 11, 16), (7, 3, 8), (17, 19, 24), (31, 35, 64), (60, 61, 128)]
+BIG_SHAPES = [(129, 257, 130), (200, 300, 1000), (256, 512, 512), (300, 130, 384)]
+PATHS = ["auto", "simt"]
+
+
+@pytest.fixture(params=PATHS)
+def path(request, monkeypatch):
+    monkeypatch.setenv("TQT_B200_PATH", request.param)
+    return request.param
+
+
+# ---- gemm_clamp_i32_i8_i8 (configuration 1) and its packed sibling ---------------------------------
+def test_i32_unpacked_golden(golden):
+    for idx, (m, n, k, has_c) in enumerate(golden["i8_shapes"]):
+        A, Bn = golden[f"i8_{idx}_A"], golden[f"i8_{idx}_Bn"]
+        Cm = golden[f"i8_{idx}_C"] if has_c else None
+        assert np.array_equal(run_i32_unpacked(A, Bn, Cm, (-100000, 100000)), golden[f"i8_{idx}_Dn"])
+        assert np.array_equal(run_i32_unpacked(A, Bn, Cm, (-3000, 2500)), golden[f"i8_{idx}_Dn_narrow"])
+
+
+def test_i32_unpacked_config1(oracle):
+    """M=64, K=512, N=256, int8 uniform in [-128,127], clamp to int32 min/max."""
+    rng = np.random.default_rng(42)
+    A = rng.integers(-128, 128, (64, 512), dtype=np.int8)
+    B = rng.integers(-128, 128, (512, 256), dtype=np.int8)
+    assert np.array_equal(run_i32_unpacked(A, B), oracle.gemm_clamp_i32_i8_i8(A, B, False))
+
+
+def test_i32_packed_golden(golden, path):
+    for idx, (m, n, k, has_c) in enumerate(golden["i8_shapes"]):
+        A, Bt, Bn = golden[f"i8_{idx}_A"], golden[f"i8_{idx}_Bt"], golden[f"i8_{idx}_Bn"]
+        Cm = golden[f"i8_{idx}_C"] if has_c else None
+        assert np.array_equal(run_i32_packed(A, Bt, True, Cm, (-100000, 100000)), golden[f"i8_{idx}_Dt"])
+        assert np.array_equal(run_i32_packed(A, Bn, False, Cm, (-100000, 100000)), golden[f"i8_{idx}_Dn"])
+
+
+@pytest.mark.parametrize("m,n,k", BIG_SHAPES + [(64, 256, 512)])
+def test_i32_packed_big(oracle, path, m, n, k):
+    rng = np.random.default_rng(m + n + k)
+    A = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    Bt = rng.integers(-128, 128, (n, k), dtype=np.int8)
+    Cm = rng.integers(-100000, 100000, (m, n)).astype(np.int32)
+    assert np.array_equal(run_i32_packed(A, Bt, True, Cm, (-900000, 800000)),
+                          oracle.gemm_clamp_i32_i8_i8(A, Bt, True, Cm, (-900000, 800000)))
+
+
+# ---- static W8A8 with int8 requantisation (configuration 4) -------------------------------------------
+@pytest.mark.parametrize("m,n,k", I8_SHAPES + BIG_SHAPES)
+@pytest.mark.parametrize("scale_d", [0.1, 30.0])
+def test_requant_bit_exact(oracle, path, m, n, k, scale_d):
+    """scale_d = 0.1 is the configuration's value (most outputs saturate at K = 4096); 30.0 keeps the
+    outputs inside the int8 range so that the multiply / shift path is what is compared."""
+    rng = np.random.default_rng(m * 3 + n * 5 + k)
+    A = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    W = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    sb = rng.uniform(0.001, 0.01, n).astype(np.float32)
+    bias = rng.integers(-1000, 1001, n).astype(np.int32)
+    fused = oracle.fuse_zp_to_bias(bias, W, 3)       # callers fold zero_point_a into the bias
+    want = oracle.gemm_reqi32toi8(A, W, True, 0.05, sb, scale_d, -5, fused)
+    got = run_requant(A, W, 0.05, sb, scale_d, -5, fused)
+    assert np.array_equal(got, want)
+    if scale_d == 30.0:
+        assert (np.abs(want.astype(np.int32)) < 127).mean() > 0.5
+
+
+def test_requant_options(oracle, path):
+    rng = np.random.default_rng(8)
+    m, n, k = 130, 260, 200
+    A = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    W = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    sb = rng.uniform(0.001, 0.01, n).astype(np.float32)
+    Cm = rng.integers(-5000, 5000, (m, n)).astype(np.int32)
+    # C without bias, narrow clamp, per-tensor scale (quant_channel_b == 1 uses column 0 for all)
+    want = oracle.gemm_reqi32toi8(A, W, True, 0.05, sb, 8.0, 4, None, Cm, (-50, 60), 1)
+    got = run_requant(A, W, 0.05, sb, 8.0, 4, None, Cm, (-50, 60), 1)
+    assert np.array_equal(got, want)
+    # caller-side tile loop with offset helpers: scale_b is indexed from each call's first column
+    bias = rng.integers(-1000, 1001, n).astype(np.int32)
+    want = oracle.gemm_reqi32toi8(A, W, True, 0.05, sb, 8.0, 4, bias)
+    got = run_requant(A, W, 0.05, sb, 8.0, 4, bias, tile=(128, 128))
+    assert np.array_equal(got, want)
+
+
+# ---- W4A8 (configurations 2 and 3) ---------------------------------------------------------------------
+def _w4a8_case(oracle, rng, m, n, k, td, has_c, has_bias, clamp):
+    A = rng.uniform(-1, 1, (m, k)).astype(np.float32)
+    W = rng.uniform(-1, 1, (n, k)).astype(np.float32)
+    q, sa, zp = oracle.quantize_a_per_row_asym(A)
+    nib, sb = oracle.quantize_b_per_channel_sym_int4(W)
+    Cm = bias = None
+    if has_c:
+        Cm = rng.uniform(-2, 2, (m, n)).astype(np.float32)
+    if has_bias:
+        bias = rng.uniform(-0.5, 0.5, n).astype(np.float32)
+    if td == "f16":
+        Cm = None if Cm is None else Cm.astype(np.float16).view(np.uint16)
+        bias = None if bias is None else bias.astype(np.float16).view(np.uint16)
+    elif td == "bf16":
+        Cm = None if Cm is None else f32_to_bf16_bits(Cm)
+        bias = None if bias is None else f32_to_bf16_bits(bias)
+    if clamp is None:
+        clamp = (-FMAX, FMAX) if td == "f32" else (-65504.0, 65504.0)
+    want = oracle.gemm_w4a8(q, nib, sa, zp, sb, TD_CODE[td], Cm, bias, clamp)
+    return q, sa, zp, nib, sb, Cm, bias, clamp, want
+
+
+@pytest.mark.parametrize("td", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("m,n,k", W4A8_SHAPES + BIG_SHAPES)
+def test_w4a8_shapes(oracle, path, td, m, n, k):
+    rng = np.random.default_rng(m * 7 + n * 11 + k)
+    q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, m, n, k, td, False, False, None)
+    got = run_w4a8(td, q, sa, zp, nib, sb, Cm, bias, clamp)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("td", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("has_c,has_bias,clamp", [(False, True, None), (False, False, (-0.5, 0.5)), (True, False, None),
+                                                  (True, True, (-0.5, 0.5))])
+@pytest.mark.parametrize("m,n,k", [(32, 32, 32), (17, 19, 24), (140, 270, 256)])
+def test_w4a8_options(oracle, path, td, has_c, has_bias, clamp, m, n, k):
+    rng = np.random.default_rng(m + n + k + 3 * has_c + 5 * has_bias)
+    q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, m, n, k, td, has_c, has_bias, clamp)
+    got = run_w4a8(td, q, sa, zp, nib, sb, Cm, bias, clamp)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 11, 16])
+@pytest.mark.parametrize("n,k", [(128, 128), (130, 258), (512, 1024), (1000, 384), (4096, 4096)])
+def test_w4a8_decode_gemv(oracle, m, n, k):
+    """m <= 16 takes the HBM-streaming GEMV; integer combine makes it bit-exact like the GEMM."""
+    rng = np.random.default_rng(m * 100 + n + k)
+    q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, m, n, k, "f32", m % 2 == 0, True, None)
+    got = run_w4a8("f32", q, sa, zp, nib, sb, Cm, bias, clamp)
+    assert np.array_equal(got, want)
+
+
+def test_w4a8_decode_on_the_tensor_core_path(oracle, monkeypatch):
+    monkeypatch.setenv("TQT_B200_PATH", "umma")
+    rng = np.random.default_rng(77)
+    q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, 3, 300, 512, "bf16", False, True, None)
+    assert np.array_equal(run_w4a8("bf16", q, sa, zp, nib, sb, Cm, bias, clamp), want)
+
+
+def test_w4a8_tile_portions(oracle, path):
+    """A caller may compute any sub-rectangle whose origin is a multiple of (m_step, n_step); the params
+    arrays are indexed from the call's origin, so it passes offset pointers."""
+    rng = np.random.default_rng(5)
+    q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, 300, 520, 256, "bf16", True, True, None)
+    for tile in ((128, 128), (256, 384), (128, 512)):
+        got = run_w4a8("bf16", q, sa, zp, nib, sb, Cm, bias, clamp, tile=tile)
+        assert np.array_equal(got, want), tile
+
+
+# ---- W4A16 (configuration 5) -----------------------------------------------------------------------------
+def _check_w4a16(got, want, td):
+    g = f16_bits_to_f32(got) if td == "f16" else got
+    w = f16_bits_to_f32(want) if td == "f16" else want
+    assert rel_err(g, w) <= 2e-2                     # the stated bar, RMS floor against 0/0
+    assert np.max(np.abs(g - w)) <= 1.0 and cosine(g, w) >= 0.9999   # the reference's own thresholds
+
+
+def test_w4a16_golden(golden, path):
+    for idx, (m, n, k, bl, has_bias, has_c, has_clamp) in enumerate(golden["w4a16_cases"]):
+        A = golden[f"w4a16_{idx}_A"].view(np.uint16)
+        nib, sc = golden[f"w4a16_{idx}_nib"], golden[f"w4a16_{idx}_scale"]
+        for td in ("f16", "f32"):
+            Cm = golden[f"w4a16_{idx}_C_{td}"] if has_c else None
+            bias = golden[f"w4a16_{idx}_bias_{td}"] if has_bias else None
+            if td == "f16":
+                Cm = None if Cm is None else Cm.view(np.uint16)
+                bias = None if bias is None else bias.view(np.uint16)
+            clamp = (-0.5, 0.5) if has_clamp else None
+            got = run_w4a16(td, A, nib, sc, int(bl), Cm, bias, clamp)
+            want = golden[f"w4a16_{idx}_D_{td}"]
+            _check_w4a16(got, want.view(np.uint16) if td == "f16" else want, td)
+
+
+@pytest.mark.parametrize("m,n,k,bl", [(129, 257, 192, 32), (256, 512, 512, 32), (200, 300, 448, 64), (130, 140, 256, 128),
+                                      (70, 260, 320, 8)])
+def test_w4a16_big(oracle, path, m, n, k, bl):
+    rng = np.random.default_rng(m + n + k + bl)
+    A = rng.normal(0, 1, (m, k)).astype(np.float16)
+    W = rng.normal(0, 0.02, (n, k)).astype(np.float16)
+    nib, sc = oracle.quantize_fp16_to_int4(W.view(np.uint16), bl)
+    bias = rng.normal(0, 0.1, n).astype(np.float16).view(np.uint16)
+    want = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, bl, TD_F16, None, bias)
+    got = run_w4a16("f16", A.view(np.uint16), nib, sc, bl, None, bias)
+    _check_w4a16(got, want, "f16")

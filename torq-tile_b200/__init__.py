@@ -1,0 +1,360 @@
+"""Host-side mirror of the TORQ-Tile micro-kernel interface for the B200 library.
+
+The product is ``libtorq_tile_b200.so`` (C ABI declared in ``include/*.h``).  This module binds it
+with ctypes and offers, per kernel type, an object with the same members as the reference's
+``struct tqt_<kernel-type>_ukernel`` function-pointer tables (``get_m_step``, ``get_n_step``, the
+offset/size helpers, ``run_a_pack``, ``run_b[t]_pack``, ``run_gemm``), taking torch CUDA tensors (or
+raw device addresses) where the C API takes device pointers.  PyTorch is used only for device
+memory and streams.  There is no CPU fallback: importing works without a GPU (so that symbols and
+host helpers can be checked), but every ``run_*`` call needs the CUDA library and a device.
+
+The directory name contains a hyphen, so the package is loaded by path; see ``load()`` in
+``__graft_entry__.py`` at the repository root.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import struct
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libtorq_tile_b200.so")
+VARIANT = "128x128_sm100a"
+
+_sz, _vp = C.c_size_t, C.c_void_p
+
+STATUS_NAMES = {0: "OK", 1: "INVALID_ARGUMENT", 2: "LAUNCH_FAILED", 3: "UNSUPPORTED"}
+
+
+class TqtError(RuntimeError):
+    pass
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise TqtError(f"{LIB_PATH} is missing: build it with `python torq-tile_b200/build.py` "
+                       "(there is no CPU fallback)")
+    return C.CDLL(LIB_PATH)
+
+
+_lib = None
+
+
+def lib():
+    """The loaded shared library (raises TqtError if it has not been built)."""
+    global _lib
+    if _lib is None:
+        _lib = _load()
+        _lib.tqt_cuda_set_stream.argtypes = [_vp]
+        _lib.tqt_cuda_get_stream.restype = _vp
+        _lib.tqt_cuda_get_last_status.restype = C.c_int
+        _lib.tqt_cuda_get_last_cuda_error.restype = C.c_int
+        _lib.tqt_cuda_read_device_fault.restype = C.c_int
+        _lib.tqt_cuda_version.restype = C.c_char_p
+        _lib.tqt_shard_plan_n.argtypes = [_sz, _sz, _sz, C.POINTER(_sz), C.POINTER(_sz)]
+        _lib.tqt_cuda_kernel_choice_w4a8.argtypes = [_sz, _sz, _sz]
+        _lib.tqt_cuda_kernel_choice_w4a8.restype = C.c_int
+    return _lib
+
+
+def _addr(x):
+    """Device address of a torch tensor, or the integer itself, or NULL for None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()
+
+
+def half_arg(bits: int):
+    """A 16-bit float (given as its bit pattern) passed by value.
+
+    The x86-64 SysV ABI passes ``_Float16`` / ``__bf16`` in the low 16 bits of an SSE register,
+    which is where the low half of a C ``float`` argument travels too, so a ``c_float`` whose low
+    16 bits hold the pattern is received unchanged (no arithmetic touches it on the way).
+    """
+    return C.c_float.from_buffer_copy(struct.pack("<HH", bits & 0xFFFF, 0))
+
+
+def f16_bits(v: float) -> int:
+    return struct.unpack("<H", struct.pack("<e", v))[0]
+
+
+def bf16_bits(v: float) -> int:
+    u = struct.unpack("<I", struct.pack("<f", v))[0]
+    if (u & 0x7FFFFFFF) > 0x7F800000:
+        return (u >> 16) | 0x40
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) & 0xFFFF
+
+
+def check(what: str = "call"):
+    """Raise if the calling thread's last run_* call was refused."""
+    st = lib().tqt_cuda_get_last_status()
+    if st != 0:
+        raise TqtError(f"{what}: status {STATUS_NAMES.get(st, st)} "
+                       f"(cudaError {lib().tqt_cuda_get_last_cuda_error()})")
+
+
+def set_stream(stream) -> None:
+    """Use a torch.cuda.Stream (or a raw cudaStream_t integer, or None) for this thread's calls."""
+    h = None if stream is None else (stream if isinstance(stream, int) else stream.cuda_stream)
+    lib().tqt_cuda_set_stream(h)
+
+
+def use_current_torch_stream() -> None:
+    import torch
+    set_stream(torch.cuda.current_stream())
+
+
+def read_device_fault() -> int:
+    return int(lib().tqt_cuda_read_device_fault())
+
+
+def shard_plan_n(n: int, world: int, rank: int):
+    b, c = _sz(), _sz()
+    lib().tqt_shard_plan_n(n, world, rank, C.byref(b), C.byref(c))
+    return int(b.value), int(c.value)
+
+
+_PACK_SIG = [_sz, _sz, _sz, _sz, _sz, _vp, _vp]
+
+
+class _UKernel:
+    """Common part of the per-kernel-type tables."""
+
+    type_name = ""
+    helpers_size = ()      # names returning size_t with their argument counts
+    td_size = 4
+
+    def __init__(self):
+        self._l = lib()
+        for name, nargs in self.helpers_size:
+            f = self._sym(name)
+            f.argtypes = [_sz] * nargs
+            f.restype = _sz
+            setattr(self, name, f)
+
+    def _name(self, action: str) -> str:
+        # tqt_<action>_<kernel-type>_<variant>; the kernel type itself starts with "gemm", so the
+        # GEMM entry point is tqt_run_<kernel-type>_<variant>
+        if action == "run_gemm":
+            return f"tqt_run_{self.type_name}_{VARIANT}"
+        return f"tqt_{action}_{self.type_name}_{VARIANT}"
+
+    def _sym(self, action: str):
+        return getattr(self._l, self._name(action))
+
+    def symbol_names(self):
+        return [self._name(a) for a in self.actions]
+
+    def _pack(self, action, rows, k, ld, ld_packed, k_idx, src, dst):
+        f = self._sym(action)
+        f.argtypes = _PACK_SIG
+        f.restype = None
+        f(rows, k, ld, ld_packed, k_idx, _addr(src), _addr(dst))
+        check(f"{action} {self.type_name}")
+
+
+_PACKED_HELPERS = (("get_m_step", 0), ("get_n_step", 0), ("get_a_packed_offset", 4), ("get_b_packed_offset", 4),
+                   ("get_c_offset", 3), ("get_d_offset", 3), ("get_d_size", 2), ("get_a_packed_size", 2),
+                   ("get_b_packed_size", 2))
+
+
+class GemmClampI32I8I8(_UKernel):
+    """gemm_clamp_i32_i8_i8: D = clamp(C + A*B), unpacked int8 operands, int32 output."""
+    type_name = "gemm_clamp_i32_i8_i8"
+    helpers_size = (("get_m_step", 0), ("get_n_step", 0), ("get_a_offset", 3), ("get_b_offset", 3),
+                    ("get_c_offset", 3), ("get_d_offset", 3), ("get_d_size", 2))
+    actions = [h[0] for h in helpers_size] + ["run_gemm"]
+
+    def run_gemm(self, m, n, k, A, lda, k_idx_a, B, ldb, k_idx_b, Cm, ldc, D, ldd, clamp_min, clamp_max):
+        f = self._sym("run_gemm")
+        f.argtypes = [_sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int32, C.c_int32]
+        f.restype = None
+        f(m, n, k, _addr(A), lda, k_idx_a, _addr(B), ldb, k_idx_b, _addr(Cm), ldc, _addr(D), ldd, clamp_min, clamp_max)
+        check("run_gemm " + self.type_name)
+
+
+class GemmClampI32I8pI8p(_UKernel):
+    """gemm_clamp_i32_i8p_i8p: same result from packed operands (tensor cores)."""
+    type_name = "gemm_clamp_i32_i8p_i8p"
+    helpers_size = _PACKED_HELPERS
+    actions = [h[0] for h in helpers_size] + ["run_a_pack", "run_b_pack", "run_bt_pack", "run_gemm"]
+
+    def run_a_pack(self, m, k, lda, lda_packed, k_idx, A, A_packed):
+        self._pack("run_a_pack", m, k, lda, lda_packed, k_idx, A, A_packed)
+
+    def run_b_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_b_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def run_bt_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_bt_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def run_gemm(self, m, n, k, A_packed, lda, k_idx_a, B_packed, ldb, k_idx_b, Cm, ldc, D, ldd, clamp_min, clamp_max):
+        f = self._sym("run_gemm")
+        f.argtypes = [_sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int32, C.c_int32]
+        f.restype = None
+        f(m, n, k, _addr(A_packed), lda, k_idx_a, _addr(B_packed), ldb, k_idx_b, _addr(Cm), ldc, _addr(D), ldd,
+          clamp_min, clamp_max)
+        check("run_gemm " + self.type_name)
+
+
+class QaI8QaI8QsI8CxParams(C.Structure):
+    """struct tqt_qai8_qai8_qsi8cx_params (host struct; scale_b is a device array)."""
+    _fields_ = [("scale_a", C.c_float), ("zero_point_a", C.c_int32), ("scale_b", _vp),
+                ("quant_channel_b", C.c_int32), ("scale_d", C.c_float), ("zero_point_d", C.c_int32)]
+
+
+class GemmReqI8(GemmClampI32I8pI8p):
+    """gemm_1xnbias_reqi32toi8_clamp_qai8_qai8p_qsi8cxp: static W8A8 with int8 requantised output."""
+    type_name = "gemm_1xnbias_reqi32toi8_clamp_qai8_qai8p_qsi8cxp"
+    helpers_size = _PACKED_HELPERS + (("get_bias_offset", 1),)
+    actions = [h[0] for h in helpers_size] + ["run_a_pack", "run_b_pack", "run_bt_pack", "run_gemm"]
+
+    def run_gemm(self, m, n, k, A_packed, lda, k_idx_a, B_packed, ldb, k_idx_b, Cm, ldc, D, ldd, bias, clamp_min,
+                 clamp_max, params):
+        f = self._sym("run_gemm")
+        f.argtypes = [_sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, C.c_int8, C.c_int8,
+                      C.POINTER(QaI8QaI8QsI8CxParams)]
+        f.restype = None
+        f(m, n, k, _addr(A_packed), lda, k_idx_a, _addr(B_packed), ldb, k_idx_b, _addr(Cm), ldc, _addr(D), ldd,
+          _addr(bias), clamp_min, clamp_max, None if params is None else C.byref(params))
+        check("run_gemm " + self.type_name)
+
+
+class QaI8DxQsI4CxParams(C.Structure):
+    """struct tqt_qai8dx_qsi4cx_params (host struct holding three device arrays)."""
+    _fields_ = [("scale_a", _vp), ("zero_point_a", _vp), ("scale_b", _vp)]
+
+
+class GemmW4A8(_UKernel):
+    """gemm_1xnbias_clamp_<td>_qai8dxp_qsi4cxp, td in {"f32", "f16", "bf16"}."""
+    helpers_size = _PACKED_HELPERS + (("get_bias_offset", 1),)
+    actions = [h[0] for h in helpers_size] + ["run_a_pack", "run_bt_pack", "run_gemm"]
+
+    def __init__(self, td: str):
+        assert td in ("f32", "f16", "bf16")
+        self.td = td
+        self.td_size = 4 if td == "f32" else 2
+        self.type_name = f"gemm_1xnbias_clamp_{td}_qai8dxp_qsi4cxp"
+        super().__init__()
+
+    def clamp_arg(self, v: float):
+        if self.td == "f32":
+            return C.c_float(v)
+        return half_arg(f16_bits(v) if self.td == "f16" else bf16_bits(v))
+
+    def run_a_pack(self, m, k, lda, lda_packed, k_idx, A, A_packed):
+        self._pack("run_a_pack", m, k, lda, lda_packed, k_idx, A, A_packed)
+
+    def run_bt_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_bt_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def run_gemm(self, m, n, k, A_packed, lda, k_idx_a, B_packed, ldb, k_idx_b, Cm, ldc, D, ldd, bias, clamp_min,
+                 clamp_max, params):
+        f = self._sym("run_gemm")
+        f.argtypes = [_sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, C.c_float, C.c_float,
+                      C.POINTER(QaI8DxQsI4CxParams)]
+        f.restype = None
+        f(m, n, k, _addr(A_packed), lda, k_idx_a, _addr(B_packed), ldb, k_idx_b, _addr(Cm), ldc, _addr(D), ldd,
+          _addr(bias), self.clamp_arg(clamp_min), self.clamp_arg(clamp_max),
+          None if params is None else C.byref(params))
+        check("run_gemm " + self.type_name)
+
+
+class GemmW4A16(_UKernel):
+    """gemm_1xnbias_clamp_<td>_f16p_qsi4c2p, td in {"f16", "f32"}."""
+    helpers_size = _PACKED_HELPERS + (("get_bias_offset", 1), ("get_scale_b_offset", 3))
+    actions = [h[0] for h in helpers_size] + ["run_a_pack", "run_bt_pack", "run_gemm"]
+
+    def __init__(self, td: str = "f16"):
+        assert td in ("f16", "f32")
+        self.td = td
+        self.td_size = 4 if td == "f32" else 2
+        self.type_name = f"gemm_1xnbias_clamp_{td}_f16p_qsi4c2p"
+        super().__init__()
+
+    def clamp_arg(self, v: float):
+        return C.c_float(v) if self.td == "f32" else half_arg(f16_bits(v))
+
+    def run_a_pack(self, m, k, lda, lda_packed, k_idx, A, A_packed):
+        self._pack("run_a_pack", m, k, lda, lda_packed, k_idx, A, A_packed)
+
+    def run_bt_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_bt_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def run_gemm(self, m, n, k, bl, A_packed, lda, k_idx_a, B_packed, ldb, k_idx_b, scale_b, ldsb, Cm, ldc, D, ldd,
+                 bias, clamp_min, clamp_max):
+        f = self._sym("run_gemm")
+        f.argtypes = [_sz, _sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp,
+                      C.c_float, C.c_float]
+        f.restype = None
+        f(m, n, k, bl, _addr(A_packed), lda, k_idx_a, _addr(B_packed), ldb, k_idx_b, _addr(scale_b), ldsb,
+          _addr(Cm), ldc, _addr(D), ldd, _addr(bias), self.clamp_arg(clamp_min), self.clamp_arg(clamp_max))
+        check("run_gemm " + self.type_name)
+
+
+# ---- extensions ------------------------------------------------------------------------------------
+_TA_NAMES = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}
+
+
+def quant_pack_qai8dxp(A, A_packed, scale_a, zero_point_a, m=None, k=None, lda=None):
+    """Dynamic per-row asymmetric int8 quantisation of A (f32 / f16 / bf16) into the packed LHS layout."""
+    ta = _TA_NAMES[str(A.dtype).replace("torch.", "")]
+    f = getattr(lib(), f"tqt_run_quant_pack_qai8dxp_{ta}_{VARIANT}")
+    f.argtypes = [_sz, _sz, _vp, _sz, _vp, _vp, _vp]
+    f.restype = None
+    m = A.shape[0] if m is None else m
+    k = A.shape[1] if k is None else k
+    lda = A.stride(0) if lda is None else lda
+    f(m, k, _addr(A), lda, _addr(A_packed), _addr(scale_a), _addr(zero_point_a))
+    check("quant_pack_qai8dxp")
+
+
+def quant_qai8dx(A, A_q, scale_a, zero_point_a):
+    """Same quantiser with a plain row-major int8 result."""
+    ta = _TA_NAMES[str(A.dtype).replace("torch.", "")]
+    f = getattr(lib(), f"tqt_run_quant_qai8dx_{ta}_sm100a")
+    f.argtypes = [_sz, _sz, _vp, _sz, _vp, _sz, _vp, _vp]
+    f.restype = None
+    f(A.shape[0], A.shape[1], _addr(A), A.stride(0), _addr(A_q), A_q.stride(0), _addr(scale_a), _addr(zero_point_a))
+    check("quant_qai8dx")
+
+
+def _unpack(name, rows, k, src, ld_packed, dst, ld):
+    f = getattr(lib(), f"tqt_run_{name}_{VARIANT}")
+    f.argtypes = [_sz, _sz, _vp, _sz, _vp, _sz]
+    f.restype = None
+    f(rows, k, _addr(src), ld_packed, _addr(dst), ld)
+    check(name)
+
+
+def a_unpack_i8(m, k, A_packed, lda_packed, A, lda):
+    _unpack("a_unpack_i8", m, k, A_packed, lda_packed, A, lda)
+
+
+def a_unpack_f16(m, k, A_packed, lda_packed, A, lda):
+    _unpack("a_unpack_f16", m, k, A_packed, lda_packed, A, lda)
+
+
+def bt_unpack_qsi4cxp(n, k, B_packed, ldb_packed, B, ldb):
+    _unpack("bt_unpack_qsi4cxp", n, k, B_packed, ldb_packed, B, ldb)
+
+
+def bt_unpack_qsi4c2p(n, k, B_packed, ldb_packed, B, ldb):
+    _unpack("bt_unpack_qsi4c2p", n, k, B_packed, ldb_packed, B, ldb)
+
+
+EXTENSION_SYMBOLS = (
+    ["tqt_cuda_set_stream", "tqt_cuda_get_stream", "tqt_cuda_get_last_status", "tqt_cuda_get_last_cuda_error",
+     "tqt_cuda_read_device_fault", "tqt_cuda_version", "tqt_shard_plan_n", "tqt_cuda_kernel_choice_w4a8",
+     "tqt_cuda_debug_f16_bits", "tqt_cuda_debug_bf16_bits"]
+    + [f"tqt_run_quant_pack_qai8dxp_{t}_{VARIANT}" for t in ("f32", "f16", "bf16")]
+    + [f"tqt_run_quant_qai8dx_{t}_sm100a" for t in ("f32", "f16", "bf16")]
+    + [f"tqt_run_{n}_{VARIANT}" for n in ("a_unpack_i8", "a_unpack_f16", "bt_unpack_qsi4cxp", "bt_unpack_qsi4c2p")]
+)
+
+
+def all_ukernels():
+    return [GemmClampI32I8I8(), GemmClampI32I8pI8p(), GemmReqI8(), GemmW4A8("f32"), GemmW4A8("f16"),
+            GemmW4A8("bf16"), GemmW4A16("f16"), GemmW4A16("f32")]

@@ -1,0 +1,88 @@
+// Kernel choice for each run_gemm call.  Host-only logic (no CUDA headers).
+//
+//   packed kernel types : tcgen05 tensor-core GEMM (kernels_umma.cu); W4A8 with m <= 16 goes to the
+//                         HBM-streaming GEMV (kernels_gemv.cu)
+//   unpacked kernel types and k == 0 : generic CUDA-core kernel (kernels_simt.cu)
+// TQT_B200_PATH=simt|umma|gemv forces a path (used by the tests to cross-check the kernels against
+// each other); a forced path that cannot take the call reports TQT_CUDA_UNSUPPORTED.
+#include <cstdlib>
+#include <cstring>
+
+#include "tqt_internal.h"
+
+namespace tqt {
+
+Result simt_gemm_i32(const GemmCommon &g, bool packed, int32_t cmin, int32_t cmax);
+Result simt_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmin, int cmax);
+Result simt_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax);
+Result simt_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td, float cmin,
+                       float cmax);
+Result umma_gemm_i32(const GemmCommon &g, int32_t cmin, int32_t cmax);
+Result umma_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmin, int cmax);
+Result umma_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax);
+Result umma_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td, float cmin,
+                       float cmax);
+Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax);
+
+Path env_path()
+{
+    const char *e = std::getenv("TQT_B200_PATH");
+    if (!e) return Path::Auto;
+    if (!std::strcmp(e, "simt")) return Path::Simt;
+    if (!std::strcmp(e, "umma")) return Path::Umma;
+    if (!std::strcmp(e, "gemv")) return Path::Gemv;
+    return Path::Auto;
+}
+
+static inline bool empty_problem(const GemmCommon &g) { return g.m == 0 || g.n == 0; }
+
+Result launch_gemm_i32(const GemmCommon &g, bool packed, int32_t cmin, int32_t cmax, Path path)
+{
+    if (empty_problem(g)) return Result{kOk, 0};
+    if (path == Path::Gemv) return Result{kUnsupported, 0};
+    if (!packed || g.k == 0 || path == Path::Simt) {
+        if (path == Path::Umma) return Result{kUnsupported, 0};
+        return simt_gemm_i32(g, packed, cmin, cmax);
+    }
+    return umma_gemm_i32(g, cmin, cmax);
+}
+
+Result launch_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmin, int cmax, Path path)
+{
+    if (empty_problem(g)) return Result{kOk, 0};
+    if (path == Path::Gemv) return Result{kUnsupported, 0};
+    if (g.k == 0 || path == Path::Simt) {
+        if (path == Path::Umma) return Result{kUnsupported, 0};
+        return simt_gemm_requant_i8(g, p, cmin, cmax);
+    }
+    return umma_gemm_requant_i8(g, p, cmin, cmax);
+}
+
+Result launch_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax, Path path)
+{
+    if (empty_problem(g)) return Result{kOk, 0};
+    if (g.k == 0 || path == Path::Simt) {
+        if (path == Path::Umma || path == Path::Gemv) return Result{kUnsupported, 0};
+        return simt_gemm_w4a8(g, p, td, cmin, cmax);
+    }
+    if (path == Path::Gemv) return gemv_w4a8(g, p, td, cmin, cmax);
+    if (path == Path::Auto && g.m <= 16) {
+        Result r = gemv_w4a8(g, p, td, cmin, cmax);
+        if (r.status != kUnsupported) return r;  // shapes the GEMV cannot hold fall through to the GEMM
+    }
+    return umma_gemm_w4a8(g, p, td, cmin, cmax);
+}
+
+Result launch_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td, float cmin,
+                         float cmax, Path path)
+{
+    if (empty_problem(g)) return Result{kOk, 0};
+    if (path == Path::Gemv) return Result{kUnsupported, 0};
+    if (g.k == 0 || path == Path::Simt) {
+        if (path == Path::Umma) return Result{kUnsupported, 0};
+        return simt_gemm_w4a16(g, bl, scale_b, ldsb, td, cmin, cmax);
+    }
+    return umma_gemm_w4a16(g, bl, scale_b, ldsb, td, cmin, cmax);
+}
+
+}  // namespace tqt

@@ -1,0 +1,100 @@
+// Internal interface between the C-ABI shim (abi.cpp, compiled by g++) and the CUDA launchers
+// (*.cu, compiled by nvcc).  Plain C++ types only: no half types, no CUDA headers.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+namespace tqt {
+
+// ---- packed layouts --------------------------------------------------------------------------
+// Every packed operand is an array of blocks [ceil(rows/128)][ceil(k/KB)] of fixed size.
+constexpr size_t kTileRows = 128;
+constexpr size_t kI8BlockK = 128;        // int8 elements per block row (128 bytes)
+constexpr size_t kI8BlockBytes = 16384;  // 128 rows x 128 B, 128-byte-swizzled
+constexpr size_t kF16BlockK = 64;        // f16 elements per block row (128 bytes)
+constexpr size_t kF16BlockBytes = 16384;
+constexpr size_t kI4BlockK = 128;        // int4 elements per block row (64 bytes)
+constexpr size_t kI4NibBytes = 8192;     // 128 rows x 64 B
+constexpr size_t kI4CxBlockBytes = kI4NibBytes + 256;  // + 128 int16 partial row sums
+constexpr size_t kI4C2BlockBytes = kI4NibBytes;
+
+inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }
+
+enum class Dtype : int { F32 = 0, F16 = 1, BF16 = 2 };
+
+enum Status : int { kOk = 0, kInvalid = 1, kLaunchFailed = 2, kUnsupported = 3 };
+
+// Result of a launcher: status + raw cudaError_t (0 when none).
+struct Result {
+    int status;
+    int cuda_error;
+};
+
+// ---- pack / unpack / quantise ---------------------------------------------------------------
+// elem_size 1 (int8) or 2 (f16).  transposed_src: source is [k, rows] row-major (run_b_pack).
+Result launch_pack_rows(void *stream, size_t rows, size_t k, size_t ld_src, size_t ld_packed, const void *src,
+                        void *dst, int elem_size, bool transposed_src);
+Result launch_unpack_rows(void *stream, size_t rows, size_t k, size_t ld_packed, const void *src, void *dst,
+                          size_t ld_dst, int elem_size);
+// int4: src [n, k/2] bytes, row stride ld_src_bytes.  c2 = qsi4c2 ordering (no row sums).
+Result launch_pack_i4(void *stream, size_t n, size_t k, size_t ld_src_bytes, size_t ld_packed, const void *src,
+                      void *dst, bool c2);
+Result launch_unpack_i4(void *stream, size_t n, size_t k, size_t ld_packed, const void *src, void *dst,
+                        size_t ld_dst_bytes, bool c2);
+// qai8dx quantiser.  packed: write the swizzled block layout, else row-major with stride ldq.
+Result launch_quant_qai8dx(void *stream, size_t m, size_t k, const void *A, size_t lda, Dtype ta, void *out,
+                           size_t ldq, bool packed, float *scale_a, int32_t *zp_a);
+
+// ---- GEMM ------------------------------------------------------------------------------------
+struct GemmCommon {
+    size_t m, n, k;
+    const void *A;
+    size_t lda;  // row-major A: elements; packed A: k extent the buffer was packed with
+    const void *B;
+    size_t ldb;  // same for B
+    const void *C;
+    size_t ldc;
+    void *D;
+    size_t ldd;
+    const void *bias;
+    void *stream;
+};
+
+enum class Path : int { Auto = 0, Umma = 1, Gemv = 2, Simt = 3 };
+
+// D(int32) = clamp(C + A*B).  packed: both operands in the int8 block layout; else A [m,k], B [k,n].
+Result launch_gemm_i32(const GemmCommon &g, bool packed, int32_t clamp_min, int32_t clamp_max, Path path);
+
+struct RequantParams {
+    float scale_a;
+    const float *scale_b;  // device
+    int quant_channel_b;
+    float scale_d;
+    int32_t zero_point_d;
+};
+// Static W8A8 with int8 output (packed operands).
+Result launch_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int clamp_min, int clamp_max,
+                              Path path);
+
+struct W4A8Params {
+    const float *scale_a;  // device [m]
+    const int32_t *zp_a;   // device [m]
+    const float *scale_b;  // device [n]
+};
+// W4A8, float output of type td (C, bias typed like D).
+Result launch_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float clamp_min, float clamp_max,
+                        Path path);
+
+// W4A16 block-quant; A f16 packed, B qsi4c2 packed; td F16 or F32.
+Result launch_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td,
+                         float clamp_min, float clamp_max, Path path);
+
+// Reads (and clears) the device-side watchdog word of the current device after synchronising
+// the stream.  0 = no fault.
+int read_device_fault(void *stream);
+
+// Path override from the environment (TQT_B200_PATH = auto|umma|gemv|simt), for tests.
+Path env_path();
+
+}  // namespace tqt
