@@ -210,8 +210,16 @@ static Result launch_gemv_t(const GemvArgs &a, uint32_t csize, uint32_t ntiles, 
     const size_t smem = (size_t)a.slots * kI4CxBlockBytes + (size_t)a.kb_per_cta * MR * 128u + (size_t)(MR + 1) * 128 * 4 +
                         (size_t)a.slots * 8 + 64;
     auto kern = gemv_w4a8_kernel<MR, TD>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
+    cudaError_t e;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        // once per device: allow the largest footprint any call may need
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
+        attr_set[dev] = true;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(csize, ntiles, 1);
     cfg.blockDim = dim3(kGemvThreads, 1, 1);

@@ -453,10 +453,15 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                             rsum[j] += (int32_t) reinterpret_cast<const int16_t *>(raw + j * Cfg::kBBlock + kI4NibBytes)[r];
                         } else {
                             // 64 k of this sub-step = segments 2h, 2h+1; each word holds 8 k as
-                            // nibbles (k0,k2,k4,k6,k1,k3,k5,k7) so that (w >> 4t) & 0x000F000F = (k2t, k2t+1)
+                            // nibbles (k0,k2,k4,k6,k1,k3,k5,k7) so that (w >> 4t) & 0x000F000F = (k2t, k2t+1).
+                            // nibble u = q + 8; 0x6400 | u is the f16 1024 + u, so q = that - 1032 exactly,
+                            // and q * scale is rounded once, like the RVV kernel's f16 multiply.
                             const size_t nrow = (size_t)(tn * 2 + j) * 128u + r;
                             const bool n_ok = nrow < args.n;
                             const uint32_t kbase = kb * 128u + h * 64u;
+                            const __half *srow = args.scale_blk + nrow * args.ldsb;
+                            const __half2 k1032 = __float2half2_rn(1032.0f);
+                            const bool word_scale = (args.bl & 7u) == 0u;   // one scale per 8-k word
 #pragma unroll
                             for (uint32_t sg = 0; sg < 2; ++sg) {
                                 const uint32_t seg = 2 * h + sg;
@@ -466,15 +471,26 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                                 for (uint32_t wi = 0; wi < 4; ++wi) {
                                     const uint32_t k0 = kbase + sg * 32u + wi * 8u;   // first k of this word
                                     uint32_t o[4];
+                                    if (word_scale) {
+                                        __half sc = __ushort_as_half((unsigned short)0);
+                                        if (n_ok && k0 < args.k) sc = __ldg(srow + k0 / args.bl);
+                                        const __half2 sc2 = __half2half2(sc);
 #pragma unroll
-                                    for (uint32_t tt = 0; tt < 4; ++tt) {
-                                        const uint32_t kk = k0 + 2 * tt;
-                                        __half sc = __float2half_rn(0.0f);
-                                        if (n_ok && kk < args.k) sc = args.scale_blk[nrow * args.ldsb + kk / args.bl];
-                                        const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
-                                        __half2 q = __hsub2(*reinterpret_cast<const __half2 *>(&bits), __float2half2_rn(1032.0f));
-                                        const __half2 v = __hmul2(q, __half2half2(sc));
-                                        o[tt] = *reinterpret_cast<const uint32_t *>(&v);
+                                        for (uint32_t tt = 0; tt < 4; ++tt) {
+                                            const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
+                                            const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032), sc2);
+                                            o[tt] = *reinterpret_cast<const uint32_t *>(&v);
+                                        }
+                                    } else {
+#pragma unroll
+                                        for (uint32_t tt = 0; tt < 4; ++tt) {
+                                            const uint32_t kk = k0 + 2 * tt;   // bl is even: a pair never straddles blocks
+                                            __half sc = __ushort_as_half((unsigned short)0);
+                                            if (n_ok && kk < args.k) sc = __ldg(srow + kk / args.bl);
+                                            const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
+                                            const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032), __half2half2(sc));
+                                            o[tt] = *reinterpret_cast<const uint32_t *>(&v);
+                                        }
                                     }
                                     const uint32_t chunk = sg * 4u + wi;
                                     *reinterpret_cast<uint4 *>(exprow + ((chunk ^ swz_out) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
