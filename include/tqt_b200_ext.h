@@ -62,6 +62,11 @@ void tqt_shard_plan_n(size_t n, size_t world, size_t rank, size_t *n_begin, size
  * GEMM, 1 = HBM-streaming GEMV (m <= 16), 2 = generic CUDA-core kernel (unpacked operands). */
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k);
 
+/* Diagnostic: install a caller-owned device buffer of 16 int64 per CTA (148 CTAs at most) that the
+ * tensor-core GEMM fills with the cycles each warp role spent waiting (producer, MMA issuer, one
+ * epilogue warp, one converter warp: {wait0, wait1, wait2, total} each).  NULL switches it off. */
+void tqt_cuda_debug_set_timing_buffer(void *dev_ptr);
+
 #if !defined(TQT_B200_NO_HALF_TYPES)
 /* Return the bit pattern of a 16-bit float received by value: lets a foreign-function binding
  * verify how it passes the clamp arguments of the f16 / bf16 kernel types. */

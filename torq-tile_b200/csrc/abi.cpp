@@ -450,6 +450,8 @@ uint16_t tqt_cuda_debug_bf16_bits(bfloat16_t v)
     return u;
 }
 
+void tqt_cuda_debug_set_timing_buffer(void *dev_ptr) { set_timing_buffer(dev_ptr); }
+
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k)
 {
     (void)n;

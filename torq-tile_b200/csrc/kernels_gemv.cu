@@ -216,7 +216,7 @@ static Result launch_gemv_t(const GemvArgs &a, uint32_t csize, uint32_t ntiles, 
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         // once per device: allow the largest footprint any call may need
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
         if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
         attr_set[dev] = true;
     }

@@ -27,6 +27,20 @@
 
 namespace tqt {
 
+// Diagnostic: when a timing buffer is installed (tqt_cuda_debug_set_timing_buffer) each role adds up
+// the cycles it spends inside its waits; slot meaning is listed where the buffer is written.
+#define TQT_TIMED(slot, call)                                   \
+    ([&]() -> bool {                                            \
+        if (!args.dbg) return (call);                           \
+        const long long _t0 = clock64();                        \
+        const bool _r = (call);                                 \
+        wcyc[slot] += clock64() - _t0;                          \
+        return _r;                                              \
+    }())
+
+static long long *g_timing_buffer = nullptr;
+void set_timing_buffer(void *p) { g_timing_buffer = static_cast<long long *>(p); }
+
 enum class BMode : int { I8 = 0, I4Cx = 1, I4C2 = 2 };
 enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3 };
 
@@ -58,6 +72,7 @@ struct UmmaArgs {
     size_t ldsb;
     uint32_t bl;
     unsigned int *fault;
+    long long *dbg;  // optional per-CTA role timing (diagnostic), 16 slots per CTA
 };
 
 template <BMode BM>
@@ -173,6 +188,8 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *sTmemBase;
+    long long wcyc[3] = {0, 0, 0};
+    const long long t_role0 = args.dbg ? clock64() : 0;
 
     if (warp == 0) {
         // ===================== producer =====================
@@ -183,7 +200,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             const uint32_t nblk = min(2u, nblocks - tn * 2);
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!ptx::mbar_wait(BAR(kEmpty + s), ph ^ 1u, sAbort, args.fault, kFaultProducerWait)) {
+                if (!TQT_TIMED(0, ptx::mbar_wait(BAR(kEmpty + s), ph ^ 1u, sAbort, args.fault, kFaultProducerWait))) {
                     ok = false;
                     break;
                 }
@@ -237,7 +254,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             const uint32_t nblk = min(2u, nblocks - tn * 2);
             const uint32_t idesc = nblk == 2 ? idesc256 : idesc128;
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
-            if (!ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem)) {
+            if (!TQT_TIMED(0, ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
                 ok = false;
                 break;
             }
@@ -245,7 +262,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             const uint32_t d_tmem = tmem_base + acc * 256u;
             for (uint32_t kb = 0; kb < KB && ok; ++kb, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull)) {
+                if (!TQT_TIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull))) {
                     ok = false;
                     break;
                 }
@@ -256,7 +273,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                     if (kConv) {
                         e = xit % 2u;
                         const uint32_t phe = (xit / 2u) & 1u;
-                        if (!ptx::mbar_wait(BAR(kConvFull + e), phe, sAbort, args.fault, kFaultMmaWaitFull)) {
+                        if (!TQT_TIMED(2, ptx::mbar_wait(BAR(kConvFull + e), phe, sAbort, args.fault, kFaultMmaWaitFull))) {
                             ok = false;
                             break;
                         }
@@ -337,12 +354,12 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                     zp = args.zp_a[mrow];
                 }
             }
-            if (!ptx::mbar_wait(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)) {
+            if (!TQT_TIMED(0, ptx::mbar_wait(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait))) {
                 ok = false;
                 break;
             }
             if constexpr (EK == EpiKind::W4A8) {
-                if (!ptx::mbar_wait(BAR(kRsumFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)) {
+                if (!TQT_TIMED(1, ptx::mbar_wait(BAR(kRsumFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait))) {
                     ok = false;
                     break;
                 }
@@ -422,7 +439,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             int32_t rsum[2] = {0, 0};
             for (uint32_t kb = 0; kb < KB && ok; ++kb, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultConverterWait)) {
+                if (!TQT_TIMED(0, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultConverterWait))) {
                     ok = false;
                     break;
                 }
@@ -430,7 +447,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                 const uint32_t nsub = kF16 ? min(2u, a_blocks_k - kb * 2) : 1u;
                 for (uint32_t h = 0; h < nsub; ++h, ++xit) {
                     const uint32_t e = xit % 2u, phe = (xit / 2u) & 1u;
-                    if (!ptx::mbar_wait(BAR(kConvEmpty + e), phe ^ 1u, sAbort, args.fault, kFaultConverterWait)) {
+                    if (!TQT_TIMED(1, ptx::mbar_wait(BAR(kConvEmpty + e), phe ^ 1u, sAbort, args.fault, kFaultConverterWait))) {
                         ok = false;
                         break;
                     }
@@ -509,7 +526,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             if (!ok) break;
             if constexpr (EK == EpiKind::W4A8) {
                 // hand the row sums of this tile to the epilogue once accumulator `acc` is free again
-                if (!ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultConverterWait)) {
+                if (!TQT_TIMED(2, ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultConverterWait))) {
                     ok = false;
                     break;
                 }
@@ -521,6 +538,14 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
         }
     }
 
+    if (args.dbg && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 6)) {
+        // slots per CTA: producer 0-3, MMA 4-7, epilogue warp 8-11, converter warp 12-15; each {wait0, wait1, wait2, total}
+        long long *d = args.dbg + (size_t)blockIdx.x * 16 + (warp == 0 ? 0 : warp == 1 ? 4 : warp == 2 ? 8 : 12);
+        d[0] = wcyc[0];
+        d[1] = wcyc[1];
+        d[2] = wcyc[2];
+        d[3] = clock64() - t_role0;
+    }
     // ---- teardown: everyone arrives, then the allocating warp frees tensor memory ----
     ptx::tc_fence_before();
     __syncthreads();
@@ -583,6 +608,7 @@ static bool fill_common(UmmaArgs &a, const GemmCommon &g, size_t out_elem, size_
     a.bias = g.bias;
     a.vec_store = ((reinterpret_cast<uintptr_t>(g.D) & 15) == 0 && ((g.ldd * out_elem) & 15) == 0) ? 1 : 0;
     a.fault = fault_word_device_ptr();
+    a.dbg = g_timing_buffer;
     // bulk copies need 16-byte aligned sources; block sizes are multiples of 16
     if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15)) return false;
     return true;

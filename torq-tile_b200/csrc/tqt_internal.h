@@ -94,6 +94,10 @@ Result launch_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, si
 // the stream.  0 = no fault.
 int read_device_fault(void *stream);
 
+// Diagnostic: device buffer of 16 int64 per CTA that the tensor-core GEMM fills with per-role wait cycles
+// (nullptr switches it off).  Owned by the caller.
+void set_timing_buffer(void *dev_ptr);
+
 // Path override from the environment (TQT_B200_PATH = auto|umma|gemv|simt), for tests.
 Path env_path();
 
