@@ -59,7 +59,7 @@ void tqt_run_a_unpack_f16_128x128_sm100a(size_t m, size_t k, const void *A_packe
 void tqt_shard_plan_n(size_t n, size_t world, size_t rank, size_t *n_begin, size_t *n_count);
 
 /* Which device kernel a run_gemm call of the given shape would launch: 0 = tcgen05 tensor-core
- * GEMM, 1 = HBM-streaming GEMV (m <= 16), 2 = generic CUDA-core kernel (unpacked operands). */
+ * GEMM, 1 = HBM-streaming GEMV (m <= 8), 2 = generic CUDA-core kernel (unpacked operands). */
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k);
 
 /* Diagnostic: install a caller-owned device buffer of 16 int64 per CTA (148 CTAs at most) that the

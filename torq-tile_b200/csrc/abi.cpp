@@ -456,7 +456,7 @@ int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k)
 {
     (void)n;
     if (k == 0) return 2;
-    return m <= 16 ? 1 : 0;
+    return m <= 8 ? 1 : 0;
 }
 
 }  // extern "C"

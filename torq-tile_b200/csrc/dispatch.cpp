@@ -1,6 +1,6 @@
 // Kernel choice for each run_gemm call.  Host-only logic (no CUDA headers).
 //
-//   packed kernel types : tcgen05 tensor-core GEMM (kernels_umma.cu); W4A8 with m <= 16 goes to the
+//   packed kernel types : tcgen05 tensor-core GEMM (kernels_umma.cu); W4A8 with m <= 8 goes to the
 //                         HBM-streaming GEMV (kernels_gemv.cu)
 //   unpacked kernel types and k == 0 : generic CUDA-core kernel (kernels_simt.cu)
 // TQT_B200_PATH=simt|umma|gemv forces a path (used by the tests to cross-check the kernels against
@@ -66,7 +66,7 @@ Result launch_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, floa
         return simt_gemm_w4a8(g, p, td, cmin, cmax);
     }
     if (path == Path::Gemv) return gemv_w4a8(g, p, td, cmin, cmax);
-    if (path == Path::Auto && g.m <= 16) {
+    if (path == Path::Auto && g.m <= 8) {
         Result r = gemv_w4a8(g, p, td, cmin, cmax);
         if (r.status != kUnsupported) return r;  // shapes the GEMV cannot hold fall through to the GEMM
     }

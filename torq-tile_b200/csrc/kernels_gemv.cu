@@ -1,34 +1,45 @@
-// HBM-streaming W4A8 GEMV for decode (m <= 16): no tensor cores, the whole weight matrix is put in
-// flight at once.
+// HBM-streaming W4A8 GEMV for decode (m <= 8; 9..16 rows run on the tensor-core kernel): no tensor cores, no clusters, no scratch memory.
 //
-// One thread-block cluster per 128 output columns (one row-tile of B_packed); the CTAs of a cluster
-// split K.  Each CTA issues bulk copies (TMA, untiled) for all of its weight blocks at entry, one
-// mbarrier per block, so that ~N*K/2 bytes are outstanding across the GPU before any arithmetic
-// starts; it stages the few activation rows in shared memory meanwhile.  Thread (row, half) expands
-// its row's nibbles with two logic ops per 8 weights (operands 16*q, as in the tensor-core kernel)
-// and accumulates with dp4a against broadcast activation words.  Partial sums are combined with
-// integer atomics into the cluster leader's shared memory (distributed shared memory), so the
-// result is exact and independent of the split, and the leader applies the same epilogue as the
-// GEMM (reference: src/gemm/gemm_i8_i4/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp/..._4x1vl_rvv.cpp:118-177).
+// One CTA per 32 output columns (32 consecutive rows of one 128-row block tile of B_packed) over
+// the whole K.  Warp w owns rows 4w..4w+3; inside a warp lane = (row, kgroup): the eight kgroups
+// split the K blocks.  Every thread issues the 128-bit loads of its share of the weights straight
+// into registers at kernel entry (16 loads = 256 B per thread per round of 32 K blocks, 64 KiB per
+// CTA), so the whole weight matrix is in flight across the GPU before any arithmetic starts and no
+// single thread serialises the requests.  Nibbles are expanded with two logic ops per 8 weights
+// (operands 16*q, as in the tensor-core kernel), accumulated with dp4a against activation words
+// staged in shared memory, and the eight kgroups are combined with warp shuffles: integer sums, so
+// the result is exact and independent of the split.  The epilogue is the GEMM's (reference:
+// src/gemm/gemm_i8_i4/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp/..._4x1vl_rvv.cpp:118-177).
 //
-// No global scratch memory is used.
-#include <cooperative_groups.h>
+// Programmatic dependent launch: the kernel lets its successor start at once and requests its
+// weights before waiting for its predecessor, so back-to-back GEMVs (the layers of a decode step)
+// overlap their memory phases; activations, C and D are touched only after the wait.
+// TQT_B200_PDL=0 switches this off.
+#include <cstdlib>
 
 #include "epilogues.cuh"
 #include "ptx_sm100.cuh"
 
-namespace cg = cooperative_groups;
-
 namespace tqt {
 
+long long *timing_buffer();
+
+__device__ __forceinline__ long long gtime_ns()
+{
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
 constexpr uint32_t kGemvThreads = 256;
-constexpr uint32_t kGemvMaxSlots = 20;  // weight blocks resident per CTA (20 x 8448 B = 165 KiB)
+constexpr uint32_t kGemvRows = 32;      // output columns per CTA
+constexpr uint32_t kGemvRoundKB = 32;   // K blocks per round: 8 kgroups x 4 blocks per thread
 
 struct GemvArgs {
     uint32_t m, n, k;
     const uint8_t *A;  // packed int8 blocks (row-tile 0 only: m <= 16)
     const uint8_t *B;  // packed qsi4cx blocks
-    uint32_t a_kblocks_total, b_kblocks_total;
+    uint32_t b_kblocks_total;
     const void *C;
     size_t ldc;
     void *D;
@@ -38,219 +49,191 @@ struct GemvArgs {
     const int32_t *zp_a;
     const float *scale_b;
     float cmin, cmax;
-    uint32_t kb_per_cta;  // K blocks handled by each CTA of a cluster
-    uint32_t slots;       // resident weight blocks per round
-    unsigned int *fault;
+    int pdl;
+    long long *dbg;  // optional per-CTA phase timestamps (diagnostic), 16 slots per CTA
 };
 
-template <int MR, Dtype TD>
-__global__ void __launch_bounds__(kGemvThreads) gemv_w4a8_kernel(const GemvArgs args)
+// 128-bit streaming load: read-only path, do not keep the line in L1.
+__device__ __forceinline__ uint4 ldg_stream(const void *p)
 {
-    extern __shared__ __align__(128) uint8_t smem[];
-    cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t crank = cluster.block_rank();
-    const uint32_t csize = cluster.num_blocks();
-    const uint32_t ntile = blockIdx.y;
-    const uint32_t tid = threadIdx.x;
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
 
+template <int MR, Dtype TD>
+__global__ void __launch_bounds__(kGemvThreads, (MR <= 4 ? 2 : 1)) gemv_w4a8_kernel(const GemvArgs args)
+{
+    // activations of one round, de-swizzled: [32 K blocks][MR rows][128 B] (+16 B per block against bank conflicts)
+    constexpr uint32_t kActStride = MR * 128u + 16u;
+    __shared__ __align__(16) uint8_t sAct[kGemvRoundKB * kActStride];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t tile = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
     const uint32_t KB = (args.k + 127) / 128;
-    const uint32_t kb_begin = min(KB, crank * args.kb_per_cta);
-    const uint32_t kb_end = min(KB, kb_begin + args.kb_per_cta);
-    const uint32_t nkb = kb_end - kb_begin;
-    const uint32_t slots = args.slots;
+    const uint32_t row_l = lane >> 3, kg = lane & 7u;
+    const uint32_t r_blk = quarter * kGemvRows + warp * 4u + row_l;   // row inside the 128-row block
+    const uint32_t swz = (r_blk >> 1) & 3u;
 
-    // shared memory: [slots] weight blocks | activations [nkb][MR][128] | reduce [(MR+1)][128] int32 | barriers
-    uint8_t *sW = smem;
-    uint8_t *sAct = sW + slots * kI4CxBlockBytes;
-    int32_t *sRed = reinterpret_cast<int32_t *>(sAct + (size_t)args.kb_per_cta * MR * 128u);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sRed + (MR + 1) * 128);
-    __shared__ int sAbort;
+    long long ts[5] = {0, 0, 0, 0, 0};
+    const bool dbg = args.dbg != nullptr && tid == 0;
+    if (dbg) ts[0] = gtime_ns();
+    if (args.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    if (tid == 0) {
-        for (uint32_t i = 0; i < slots; ++i) ptx::mbar_init(ptx::smem_u32(bars + i), 1);
-        sAbort = 0;
-        ptx::fence_mbar_init();
-    }
-    for (uint32_t i = tid; i < (MR + 1) * 128; i += kGemvThreads) sRed[i] = 0;
-    __syncthreads();
-
-    // put the first round of weight blocks in flight
-    const uint8_t *wsrc = args.B + ((size_t)ntile * args.b_kblocks_total + kb_begin) * kI4CxBlockBytes;
-    if (tid == 0) {
-        const uint32_t first = min(nkb, slots);
-        for (uint32_t i = 0; i < first; ++i) {
-            const uint32_t bar = ptx::smem_u32(bars + i);
-            ptx::mbar_arrive_expect_tx(bar, (uint32_t)kI4CxBlockBytes);
-            ptx::bulk_g2s(ptx::smem_u32(sW + i * kI4CxBlockBytes), wsrc + (size_t)i * kI4CxBlockBytes,
-                          (uint32_t)kI4CxBlockBytes, bar);
+    const uint8_t *wbase = args.B + (size_t)tile * args.b_kblocks_total * kI4CxBlockBytes + r_blk * 64u;
+    uint4 wcur[16];
+    auto load_round = [&](uint32_t base, uint4(&w)[16]) {
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            const uint32_t kb = base + kg + 8u * i;
+            if (kb < KB) {
+                const uint8_t *p = wbase + (size_t)kb * kI4CxBlockBytes;
+#pragma unroll
+                for (uint32_t seg = 0; seg < 4; ++seg) w[i * 4 + seg] = ldg_stream(p + ((seg ^ swz) << 4));
+            } else {
+#pragma unroll
+                for (uint32_t seg = 0; seg < 4; ++seg) w[i * 4 + seg] = make_uint4(0, 0, 0, 0);
+            }
         }
-    }
-    // stage the activation rows of this CTA's K range, de-swizzled: sAct[kb][row][128]
-    for (uint32_t i = tid; i < nkb * MR * 8u; i += kGemvThreads) {
-        const uint32_t c = i & 7u, row = (i >> 3) % MR, kbl = (i >> 3) / MR;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < args.m)
-            v = __ldg(reinterpret_cast<const uint4 *>(args.A + (size_t)(kb_begin + kbl) * kI8BlockBytes +
-                                                      sw128_byte(row, c * 16u)));
-        *reinterpret_cast<uint4 *>(sAct + ((size_t)kbl * MR + row) * 128u + c * 16u) = v;
-    }
-    __syncthreads();
-    cluster.sync();  // every CTA of the cluster is running and has zeroed its reduce buffer
+    };
+    load_round(0, wcur);
+    if (dbg) ts[1] = gtime_ns();
+    // weights are static; everything else may have been produced by the preceding kernel
+    if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (dbg) ts[2] = gtime_ns();
 
-    const uint32_t r = tid & 127u, half = tid >> 7;
-    const uint32_t swz = (r >> 1) & 3u;
     int32_t acc[MR], acc2[MR];
 #pragma unroll
     for (int i = 0; i < MR; ++i) acc[i] = acc2[i] = 0;
-    int32_t rsum = 0;
-    bool ok = true;
-    volatile int *abort_flag = &sAbort;
+    int32_t rs16 = 0;   // 16 * sum of q over this thread's K blocks
 
-    // Every thread runs the same number of rounds (the refill below uses __syncthreads); after a
-    // failed wait the abort flag makes all remaining waits return at once.
-    uint32_t last_base = 0;
-    for (uint32_t base = 0; base < nkb; base += slots) {
-        last_base = base;
-        const uint32_t cnt = min(slots, nkb - base);
-        const uint32_t parity = (base / slots) & 1u;
-        for (uint32_t i = half; i < cnt && ok; i += 2) {
-            if (!ptx::mbar_wait(ptx::smem_u32(bars + i), parity, abort_flag, args.fault, kFaultGemvWait)) {
-                ok = false;
-                break;
-            }
-            const uint8_t *blk = sW + i * kI4CxBlockBytes;
-            const uint8_t *act = sAct + (size_t)(base + i) * MR * 128u;
-            rsum += (int32_t) reinterpret_cast<const int16_t *>(blk + kI4NibBytes)[r];
+    for (uint32_t base = 0; base < KB; base += kGemvRoundKB) {
+        const uint32_t cnt = min(kGemvRoundKB, KB - base);
+        if (base) __syncthreads();   // previous round's activations are no longer needed
+        for (uint32_t i = tid; i < cnt * MR * 8u; i += kGemvThreads) {
+            const uint32_t c = i & 7u, row = (i >> 3) % MR, kbl = (i >> 3) / MR;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < args.m)
+                v = __ldg(reinterpret_cast<const uint4 *>(args.A + (size_t)(base + kbl) * kI8BlockBytes +
+                                                          sw128_byte(row, c * 16u)));
+            *reinterpret_cast<uint4 *>(sAct + kbl * kActStride + row * 128u + c * 16u) = v;
+        }
+        if (base) load_round(base, wcur);
+        __syncthreads();
+        if (dbg && base == 0) ts[3] = gtime_ns();
 #pragma unroll
-            for (uint32_t seg = 0; seg < 4; ++seg) {
-                const uint4 w = *reinterpret_cast<const uint4 *>(blk + r * 64u + ((seg ^ swz) << 4));
-                const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        for (uint32_t i = 0; i < 4; ++i) {
+            const uint32_t s = kg + 8u * i;
+            if (s < cnt) {
+                const uint8_t *act = sAct + s * kActStride;
 #pragma unroll
-                for (int mi = 0; mi < MR; ++mi) {
-                    // activation words for k = 32*seg .. +31 of row mi (same address for the whole warp: broadcast)
-                    const uint4 a0 = *reinterpret_cast<const uint4 *>(act + mi * 128u + seg * 32u);
-                    const uint4 a1 = *reinterpret_cast<const uint4 *>(act + mi * 128u + seg * 32u + 16u);
-                    const uint32_t al[4] = {a0.x, a0.y, a0.z, a0.w};
-                    const uint32_t ah[4] = {a1.x, a1.y, a1.z, a1.w};
+                for (uint32_t seg = 0; seg < 4; ++seg) {
+                    const uint4 w = wcur[i * 4 + seg];
+                    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+                    uint32_t lo[4], hi[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        acc[mi] = __dp4a((int)al[j], (int)((ws[j] << 4) & 0xF0F0F0F0u), acc[mi]);
-                        acc2[mi] = __dp4a((int)ah[j], (int)(ws[j] & 0xF0F0F0F0u), acc2[mi]);
+                        lo[j] = (ws[j] << 4) & 0xF0F0F0F0u;   // 16*q for k = 32*seg + 4j .. +3
+                        hi[j] = ws[j] & 0xF0F0F0F0u;          // 16*q for k = 32*seg + 16 + 4j .. +3
+                        rs16 = __dp4a((int)lo[j], 0x01010101, rs16);
+                        rs16 = __dp4a((int)hi[j], 0x01010101, rs16);
+                    }
+#pragma unroll
+                    for (int mi = 0; mi < MR; ++mi) {
+                        const uint4 a0 = *reinterpret_cast<const uint4 *>(act + mi * 128u + seg * 32u);
+                        const uint4 a1 = *reinterpret_cast<const uint4 *>(act + mi * 128u + seg * 32u + 16u);
+                        const uint32_t al[4] = {a0.x, a0.y, a0.z, a0.w};
+                        const uint32_t ah[4] = {a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc[mi] = __dp4a((int)al[j], (int)lo[j], acc[mi]);
+                            acc2[mi] = __dp4a((int)ah[j], (int)hi[j], acc2[mi]);
+                        }
                     }
                 }
             }
         }
-        if (base + slots < nkb) {
-            // next round re-uses the slots: everyone must be done reading them
-            __syncthreads();
-            if (tid == 0 && !*abort_flag) {
-                const uint32_t next = min(slots, nkb - (base + slots));
-                for (uint32_t i = 0; i < next; ++i) {
-                    const uint32_t bar = ptx::smem_u32(bars + i);
-                    ptx::mbar_arrive_expect_tx(bar, (uint32_t)kI4CxBlockBytes);
-                    ptx::bulk_g2s(ptx::smem_u32(sW + i * kI4CxBlockBytes),
-                                  wsrc + (size_t)(base + slots + i) * kI4CxBlockBytes, (uint32_t)kI4CxBlockBytes, bar);
-                }
-                last_base = base + slots;
-            }
-            __syncthreads();
-        }
     }
-    __syncthreads();
-    const bool aborted = *abort_flag != 0;
 
-    // combine: integer atomics into the leader's reduce buffer (exact, order-independent)
-    int32_t *leader = cluster.map_shared_rank(sRed, 0);
-    if (!aborted) {
+    // combine the eight K groups of each row (lanes that differ in their low three bits)
+#pragma unroll
+    for (int mi = 0; mi < MR; ++mi) {
+        int32_t v = acc[mi] + acc2[mi];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        acc[mi] = v;
+    }
+    rs16 += __shfl_xor_sync(0xffffffffu, rs16, 1);
+    rs16 += __shfl_xor_sync(0xffffffffu, rs16, 2);
+    rs16 += __shfl_xor_sync(0xffffffffu, rs16, 4);
+    if (dbg) {
+        ts[4] = gtime_ns();
+        for (int i = 0; i < 5; ++i) args.dbg[(size_t)blockIdx.x * 16 + i] = ts[i];
+    }
+
+    const uint32_t n = tile * 128u + r_blk;
+    if (kg == 0 && n < args.n) {
+        const int32_t rs = rs16 >> 4;
+        const float sb = args.scale_b[n];
+        const float bv = args.bias ? TdTraits<TD>::load(args.bias, n) : 0.0f;
 #pragma unroll
         for (int mi = 0; mi < MR; ++mi) {
-            const int32_t v = acc[mi] + acc2[mi];
-            if (v != 0) atomicAdd(leader + mi * 128 + r, v);
-        }
-        if (rsum != 0) atomicAdd(leader + MR * 128 + r, rsum);
-    } else if (tid == 0) {
-        // bail-out: wait (bounded) for the copies of the last round issued before leaving
-        const uint32_t cnt = nkb > last_base ? min(slots, nkb - last_base) : 0u;
-        const uint32_t parity = (last_base / slots) & 1u;
-        for (uint32_t i = 0; i < cnt; ++i) {
-            const long long t0 = clock64();
-            while (!ptx::mbar_try_wait(ptx::smem_u32(bars + i), parity)) {
-                if (clock64() - t0 > ptx::kWaitLimitCycles) {
-                    if (args.fault) atomicCAS(args.fault, 0u, (unsigned)kFaultDrainWait);
-                    break;
-                }
-            }
-        }
-    }
-    cluster.sync();
-    if (crank == 0 && tid < 128u && !aborted) {
-        const uint32_t n = ntile * 128u + r;
-        if (n < args.n) {
-            const int32_t rs = sRed[MR * 128 + r];
-            const float sb = args.scale_b[n];
-            const float bv = args.bias ? TdTraits<TD>::load(args.bias, n) : 0.0f;
-#pragma unroll
-            for (int mi = 0; mi < MR; ++mi) {
-                if ((uint32_t)mi < args.m) {
-                    int32_t a = sRed[mi * 128 + r] >> 4;  // operands were 16*q
-                    a -= args.zp_a[mi] * rs;
-                    const float cv = args.C ? TdTraits<TD>::load(args.C, (size_t)mi * args.ldc + n) : 0.0f;
-                    const float v = w4a8_epilogue(a, args.scale_a[mi], sb, args.C != nullptr, cv, args.bias != nullptr, bv,
-                                                  args.cmin, args.cmax);
-                    TdTraits<TD>::store(args.D, (size_t)mi * args.ldd + n, v);
-                }
+            if ((uint32_t)mi < args.m) {
+                int32_t a = acc[mi] >> 4;   // operands were 16*q
+                a -= args.zp_a[mi] * rs;
+                const float cv = args.C ? TdTraits<TD>::load(args.C, (size_t)mi * args.ldc + n) : 0.0f;
+                const float v = w4a8_epilogue(a, args.scale_a[mi], sb, args.C != nullptr, cv, args.bias != nullptr, bv,
+                                              args.cmin, args.cmax);
+                TdTraits<TD>::store(args.D, (size_t)mi * args.ldd + n, v);
             }
         }
     }
 }
 
-template <int MR, Dtype TD>
-static Result launch_gemv_t(const GemvArgs &a, uint32_t csize, uint32_t ntiles, cudaStream_t st)
+static bool pdl_enabled()
 {
-    const size_t smem = (size_t)a.slots * kI4CxBlockBytes + (size_t)a.kb_per_cta * MR * 128u + (size_t)(MR + 1) * 128 * 4 +
-                        (size_t)a.slots * 8 + 64;
-    auto kern = gemv_w4a8_kernel<MR, TD>;
-    cudaError_t e;
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        // once per device: allow the largest footprint any call may need
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448 - 1024);
-        if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
-        attr_set[dev] = true;
+    static int cached = -1;
+    if (cached < 0) {
+        const char *e = std::getenv("TQT_B200_PDL");
+        cached = (e && e[0] == '0') ? 0 : 1;
     }
+    return cached != 0;
+}
+
+template <int MR, Dtype TD>
+static Result launch_gemv_t(GemvArgs a, uint32_t ctas, cudaStream_t st)
+{
+    a.pdl = pdl_enabled() ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(csize, ntiles, 1);
+    cfg.gridDim = dim3(ctas, 1, 1);
     cfg.blockDim = dim3(kGemvThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
+    cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = csize;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, kern, a);
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a8_kernel<MR, TD>, a);
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
     return Result{kOk, 0};
 }
 
 template <Dtype TD>
-static Result launch_gemv_m(const GemvArgs &a, uint32_t csize, uint32_t ntiles, cudaStream_t st)
+static Result launch_gemv_m(const GemvArgs &a, uint32_t ctas, cudaStream_t st)
 {
-    if (a.m <= 1) return launch_gemv_t<1, TD>(a, csize, ntiles, st);
-    if (a.m <= 2) return launch_gemv_t<2, TD>(a, csize, ntiles, st);
-    if (a.m <= 4) return launch_gemv_t<4, TD>(a, csize, ntiles, st);
-    if (a.m <= 8) return launch_gemv_t<8, TD>(a, csize, ntiles, st);
-    return launch_gemv_t<16, TD>(a, csize, ntiles, st);
+    if (a.m <= 1) return launch_gemv_t<1, TD>(a, ctas, st);
+    if (a.m <= 2) return launch_gemv_t<2, TD>(a, ctas, st);
+    if (a.m <= 4) return launch_gemv_t<4, TD>(a, ctas, st);
+    return launch_gemv_t<8, TD>(a, ctas, st);
 }
 
 Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
 {
     if (g.m == 0 || g.n == 0) return Result{kOk, 0};
-    if (g.m > 16 || g.k == 0 || g.k > 65536 || g.n > 0x7fffff00ull) return Result{kUnsupported, 0};
+    if (g.m > 8 || g.k == 0 || g.k > 65536 || g.n > 0x3fffff00ull) return Result{kUnsupported, 0};
     if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15)) return Result{kUnsupported, 0};
     GemvArgs a{};
     a.m = (uint32_t)g.m;
@@ -258,7 +241,6 @@ Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin,
     a.k = (uint32_t)g.k;
     a.A = (const uint8_t *)g.A;
     a.B = (const uint8_t *)g.B;
-    a.a_kblocks_total = (uint32_t)ceil_div(g.lda, 128);
     a.b_kblocks_total = (uint32_t)ceil_div(g.ldb, 128);
     a.C = g.C;
     a.ldc = g.ldc;
@@ -270,26 +252,13 @@ Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin,
     a.scale_b = p.scale_b;
     a.cmin = cmin;
     a.cmax = cmax;
-    a.fault = fault_word_device_ptr();
-    const uint32_t KB = (uint32_t)ceil_div(g.k, 128);
-    const uint32_t ntiles = (uint32_t)ceil_div(g.n, 128);
-    if (ntiles > 65535) return Result{kUnsupported, 0};
-    // split K across the cluster until the grid covers the GPU (portable cluster size <= 8)
-    uint32_t csize = 1;
-    while (csize < 8 && ntiles * csize < 120 && csize * 2 <= KB) csize *= 2;
-    a.kb_per_cta = (KB + csize - 1) / csize;
-    a.slots = a.kb_per_cta < kGemvMaxSlots ? a.kb_per_cta : kGemvMaxSlots;
-    {
-        const uint32_t mr = a.m <= 1 ? 1 : a.m <= 2 ? 2 : a.m <= 4 ? 4 : a.m <= 8 ? 8 : 16;
-        const size_t smem = (size_t)a.slots * kI4CxBlockBytes + (size_t)a.kb_per_cta * mr * 128u + (size_t)(mr + 1) * 512 +
-                            (size_t)a.slots * 8 + 64;
-        if (smem > 220 * 1024) return Result{kUnsupported, 0};
-    }
+    a.dbg = timing_buffer();
+    const uint32_t ctas = (uint32_t)ceil_div(g.n, kGemvRows);   // CTA c owns columns [32c, 32c + 32)
     cudaStream_t st = (cudaStream_t)g.stream;
     switch (td) {
-        case Dtype::F32: return launch_gemv_m<Dtype::F32>(a, csize, ntiles, st);
-        case Dtype::F16: return launch_gemv_m<Dtype::F16>(a, csize, ntiles, st);
-        default: return launch_gemv_m<Dtype::BF16>(a, csize, ntiles, st);
+        case Dtype::F32: return launch_gemv_m<Dtype::F32>(a, ctas, st);
+        case Dtype::F16: return launch_gemv_m<Dtype::F16>(a, ctas, st);
+        default: return launch_gemv_m<Dtype::BF16>(a, ctas, st);
     }
 }
 

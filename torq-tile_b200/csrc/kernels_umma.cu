@@ -40,6 +40,7 @@ namespace tqt {
 
 static long long *g_timing_buffer = nullptr;
 void set_timing_buffer(void *p) { g_timing_buffer = static_cast<long long *>(p); }
+long long *timing_buffer() { return g_timing_buffer; }
 
 enum class BMode : int { I8 = 0, I4Cx = 1, I4C2 = 2 };
 enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3 };
