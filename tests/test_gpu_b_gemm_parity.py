@@ -209,3 +209,43 @@ def test_w4a16_big(oracle, path, m, n, k, bl):
     want = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, bl, TD_F16, None, bias)
     got = run_w4a16("f16", A.view(np.uint16), nib, sc, bl, None, bias)
     _check_w4a16(got, want, "f16")
+
+
+# ---- the two tensor-core kernels against each other and the oracle ---------------------------------------
+@pytest.fixture(params=["single", "pair"])
+def umma_variant(request, monkeypatch):
+    """TQT_B200_UMMA forces the single-CTA or the CTA-pair (cta_group::2) kernel whatever the shape."""
+    monkeypatch.setenv("TQT_B200_PATH", "umma")
+    monkeypatch.setenv("TQT_B200_UMMA", request.param)
+    return request.param
+
+
+@pytest.mark.parametrize("m,n,k", I8_SHAPES + BIG_SHAPES + [(512, 384, 640), (1000, 1000, 264)])
+def test_i8_kernels_forced(oracle, umma_variant, m, n, k):
+    rng = np.random.default_rng(m + 2 * n + 3 * k)
+    A = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    W = rng.integers(-128, 128, (n, k), dtype=np.int8)
+    Cm = rng.integers(-100000, 100000, (m, n)).astype(np.int32)
+    assert np.array_equal(run_i32_packed(A, W, True, Cm, (-2**31, 2**31 - 1)), oracle.gemm_clamp_i32_i8_i8(A, W, True, Cm))
+    sb = rng.uniform(0.001, 0.01, n).astype(np.float32)
+    bias = rng.integers(-1000, 1001, n).astype(np.int32)
+    want = oracle.gemm_reqi32toi8(A, W, True, 0.05, sb, 20.0, -5, bias)
+    assert np.array_equal(run_requant(A, W, 0.05, sb, 20.0, -5, bias), want)
+
+
+@pytest.fixture(params=["single", "pair", "ts"])
+def w4a8_variant(request, monkeypatch):
+    """single: weights expanded in shared memory; pair / ts: weights expanded into tensor memory, on a
+    CTA pair or on one CTA."""
+    monkeypatch.setenv("TQT_B200_PATH", "umma")
+    monkeypatch.setenv("TQT_B200_UMMA", request.param)
+    return request.param
+
+
+@pytest.mark.parametrize("td", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("m,n,k", W4A8_SHAPES[3:] + BIG_SHAPES + [(192, 256, 128), (193, 257, 384), (500, 640, 1152), (97, 128, 256)])
+def test_w4a8_kernels_forced(oracle, w4a8_variant, td, m, n, k):
+    rng = np.random.default_rng(m * 5 + n * 3 + k)
+    q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, m, n, k, td, m % 2 == 1, True, None)
+    got = run_w4a8(td, q, sa, zp, nib, sb, Cm, bias, clamp)
+    assert np.array_equal(got, want)

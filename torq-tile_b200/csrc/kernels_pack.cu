@@ -301,6 +301,13 @@ __global__ void __launch_bounds__(256) quant_qai8dx_kernel(size_t m, size_t k, c
     const bool aligned = ((reinterpret_cast<uintptr_t>(A) + row_base * ES) & 15) == 0;
     const size_t nchunks = (k + 15) / 16;
 
+    // Rows of up to 16 * blockDim elements (K <= 4096 with 256 threads) are held in registers between
+    // the min/max pass and the quantise pass; longer rows are read again (from L2).
+    const size_t out_chunks_all = PACKED ? ((k + 127) / 128) * 8 : nchunks;
+    const bool in_regs = out_chunks_all <= blockDim.x;
+    float xr[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) xr[i] = 0.0f;
     float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
     for (size_t c = threadIdx.x; c < nchunks; c += blockDim.x) {
         float x[16];
@@ -312,6 +319,7 @@ __global__ void __launch_bounds__(256) quant_qai8dx_kernel(size_t m, size_t k, c
                 vmin = x[i] < vmin ? x[i] : vmin;
                 vmax = x[i] > vmax ? x[i] : vmax;
             }
+            if (in_regs) xr[i] = x[i];
         }
     }
 #pragma unroll
@@ -353,13 +361,18 @@ __global__ void __launch_bounds__(256) quant_qai8dx_kernel(size_t m, size_t k, c
     const size_t tile = row >> 7;
     const uint32_t r = (uint32_t)(row & 127);
     // packed rows are padded with zeros up to the block width
-    const size_t out_chunks = PACKED ? ((k + 127) / 128) * 8 : nchunks;
+    const size_t out_chunks = out_chunks_all;
     for (size_t c = threadIdx.x; c < out_chunks; c += blockDim.x) {
         const size_t k0 = c * 16;
         alignas(16) int8_t q[16];
         if (k0 < k && s != 0.0f) {
             float x[16];
-            load16<TA>(A, row_base + k0, k - k0, aligned, x);
+            if (in_regs) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) x[i] = xr[i];
+            } else {
+                load16<TA>(A, row_base + k0, k - k0, aligned, x);
+            }
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 float v = __fadd_rn(rintf(__fdiv_rn(x[i], s)), zpf);

@@ -22,8 +22,12 @@
 //
 // Every wait is bounded (ptx::mbar_wait); a wait that runs out records a code in the device fault
 // word, the CTA stops issuing work, drains its copies, frees tensor memory and returns.
+#include <cstdlib>
+#include <cstring>
+
 #include "epilogues.cuh"
 #include "ptx_sm100.cuh"
+#include "umma_args.cuh"
 
 namespace tqt {
 
@@ -41,40 +45,6 @@ namespace tqt {
 static long long *g_timing_buffer = nullptr;
 void set_timing_buffer(void *p) { g_timing_buffer = static_cast<long long *>(p); }
 long long *timing_buffer() { return g_timing_buffer; }
-
-enum class BMode : int { I8 = 0, I4Cx = 1, I4C2 = 2 };
-enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3 };
-
-struct UmmaArgs {
-    uint32_t m, n, k;
-    const uint8_t *A;
-    const uint8_t *B;
-    uint32_t a_kblocks_total;  // blocks per row-tile in the A buffer
-    uint32_t b_kblocks_total;  // blocks per row-tile in the B buffer
-    const void *C;
-    size_t ldc;
-    void *D;
-    size_t ldd;
-    const void *bias;
-    int vec_store;  // D rows are 16-byte aligned
-    // s32 / requant
-    int32_t cmin_i, cmax_i;
-    float rq_scale_a;
-    const float *scale_b;  // requant: per channel; W4A8: per channel
-    int rq_per_tensor;
-    float rq_scale_d;
-    int32_t rq_zp_d;
-    // W4A8
-    const float *scale_a;
-    const int32_t *zp_a;
-    float cmin_f, cmax_f;
-    // W4A16
-    const __half *scale_blk;
-    size_t ldsb;
-    uint32_t bl;
-    unsigned int *fault;
-    long long *dbg;  // optional per-CTA role timing (diagnostic), 16 slots per CTA
-};
 
 template <BMode BM>
 struct ModeCfg;
@@ -109,27 +79,6 @@ constexpr uint32_t umma_smem_bytes()
     return 1024 /* alignment slack */ + Cfg::kStages * Cfg::kABytes + Cfg::kExp * kExpBytes + Cfg::kStages * Cfg::kBStage +
            kColParamBytes + kRsumBytes + kBarrierBytes;
 }
-
-// ---- epilogue of one 32-column strip ------------------------------------------------------------
-template <EpiKind EK, Dtype TD>
-struct OutType;
-template <Dtype TD>
-struct OutType<EpiKind::S32, TD> { using type = int32_t; };
-template <Dtype TD>
-struct OutType<EpiKind::Req8, TD> { using type = int8_t; };
-template <Dtype TD>
-struct OutType<EpiKind::W4A8, TD> { using type = typename TdTraits<TD>::type; };
-template <Dtype TD>
-struct OutType<EpiKind::W4A16, TD> { using type = typename TdTraits<TD>::type; };
-
-template <typename T>
-__device__ __forceinline__ T cvt_out(float v);
-template <>
-__device__ __forceinline__ float cvt_out<float>(float v) { return v; }
-template <>
-__device__ __forceinline__ __half cvt_out<__half>(float v) { return __float2half_rn(v); }
-template <>
-__device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 template <BMode BM, EpiKind EK, Dtype TD>
 __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(const UmmaArgs args)
@@ -205,24 +154,24 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                     ok = false;
                     break;
                 }
+                // lane 0 arms the barrier; lanes 0..nblk issue one bulk copy each in the same instruction
+                uint32_t a_bytes = Cfg::kABytes;
+                const uint8_t *a_src;
+                if (kF16) {
+                    const uint32_t nsub = min(2u, a_blocks_k - kb * 2);
+                    a_bytes = nsub * 16384u;
+                    a_src = args.A + ((size_t)tm * args.a_kblocks_total + kb * 2) * kF16BlockBytes;
+                } else {
+                    a_src = args.A + ((size_t)tm * args.a_kblocks_total + kb) * kI8BlockBytes;
+                }
+                if (lane == 0) ptx::mbar_arrive_expect_tx(BAR(kFull + s), a_bytes + nblk * Cfg::kBBlock);
+                __syncwarp();
                 if (lane == 0) {
-                    uint32_t a_bytes = Cfg::kABytes;
-                    const uint8_t *a_src;
-                    if (kF16) {
-                        const uint32_t nsub = min(2u, a_blocks_k - kb * 2);
-                        a_bytes = nsub * 16384u;
-                        a_src = args.A + ((size_t)tm * args.a_kblocks_total + kb * 2) * kF16BlockBytes;
-                    } else {
-                        a_src = args.A + ((size_t)tm * args.a_kblocks_total + kb) * kI8BlockBytes;
-                    }
-                    ptx::mbar_arrive_expect_tx(BAR(kFull + s), a_bytes + nblk * Cfg::kBBlock);
                     ptx::bulk_g2s(ptx::smem_u32(sA + s * Cfg::kABytes), a_src, a_bytes, BAR(kFull + s));
-                    for (uint32_t j = 0; j < nblk; ++j) {
-                        const uint8_t *b_src =
-                            args.B + ((size_t)(tn * 2 + j) * args.b_kblocks_total + kb) * Cfg::kBBlock;
-                        ptx::bulk_g2s(ptx::smem_u32(sB + s * Cfg::kBStage + j * Cfg::kBBlock), b_src, Cfg::kBBlock,
-                                      BAR(kFull + s));
-                    }
+                } else if (lane <= nblk) {
+                    const uint32_t j = lane - 1;
+                    const uint8_t *b_src = args.B + ((size_t)(tn * 2 + j) * args.b_kblocks_total + kb) * Cfg::kBBlock;
+                    ptx::bulk_g2s(ptx::smem_u32(sB + s * Cfg::kBStage + j * Cfg::kBBlock), b_src, Cfg::kBBlock, BAR(kFull + s));
                 }
                 __syncwarp();
             }
@@ -263,7 +212,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             const uint32_t d_tmem = tmem_base + acc * 256u;
             for (uint32_t kb = 0; kb < KB && ok; ++kb, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!TQT_TIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull))) {
+                if (!TQT_TIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, true))) {
                     ok = false;
                     break;
                 }
@@ -274,7 +223,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                     if (kConv) {
                         e = xit % 2u;
                         const uint32_t phe = (xit / 2u) & 1u;
-                        if (!TQT_TIMED(2, ptx::mbar_wait(BAR(kConvFull + e), phe, sAbort, args.fault, kFaultMmaWaitFull))) {
+                        if (!TQT_TIMED(2, ptx::mbar_wait(BAR(kConvFull + e), phe, sAbort, args.fault, kFaultMmaWaitFull, true))) {
                             ok = false;
                             break;
                         }
@@ -557,7 +506,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
 }
 
 // ---- host side --------------------------------------------------------------------------------------
-static int sm_count()
+int sm_count_cached()
 {
     static int cache[64] = {0};
     int dev = 0;
@@ -584,7 +533,7 @@ static Result launch_umma(const UmmaArgs &a, cudaStream_t st)
         attr_set[dev] = true;
     }
     const uint32_t tiles = ((a.m + 127) / 128) * ((((a.n + 127) / 128) + 1) / 2);
-    const uint32_t grid = tiles < (uint32_t)sm_count() ? tiles : (uint32_t)sm_count();
+    const uint32_t grid = tiles < (uint32_t)sm_count_cached() ? tiles : (uint32_t)sm_count_cached();
     kern<<<grid, ModeCfg<BM>::kThreads, smem, st>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
@@ -615,12 +564,36 @@ static bool fill_common(UmmaArgs &a, const GemmCommon &g, size_t out_elem, size_
     return true;
 }
 
+Result pair_gemm_i8(const UmmaArgs &a, bool requant, cudaStream_t st);
+Result pair_gemm_w4a8(const UmmaArgs &a, Dtype td, cudaStream_t st);
+Result ts_gemm_w4a8(const UmmaArgs &a, Dtype td, cudaStream_t st);
+
+// TQT_B200_UMMA=single|pair forces one of the two tensor-core kernels (tests); default: CTA pairs
+// once the problem has more than one 128-row tile, the single-CTA kernel below that.
+static int umma_variant()
+{
+    const char *e = std::getenv("TQT_B200_UMMA");
+    if (!e) return 0;
+    if (!std::strcmp(e, "single")) return 1;
+    if (!std::strcmp(e, "pair")) return 2;
+    if (!std::strcmp(e, "ts")) return 3;
+    return 0;
+}
+static bool use_pair(uint32_t m, uint32_t min_m)
+{
+    const int v = umma_variant();
+    if (v == 1) return false;
+    if (v == 2) return true;
+    return m > min_m;
+}
+
 Result umma_gemm_i32(const GemmCommon &g, int32_t cmin, int32_t cmax)
 {
     UmmaArgs a{};
     if (!fill_common(a, g, 4, 128, 128)) return Result{kUnsupported, 0};
     a.cmin_i = cmin;
     a.cmax_i = cmax;
+    if (use_pair(a.m, 128)) return pair_gemm_i8(a, false, (cudaStream_t)g.stream);
     return launch_umma<BMode::I8, EpiKind::S32, Dtype::F32>(a, (cudaStream_t)g.stream);
 }
 
@@ -635,6 +608,7 @@ Result umma_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmi
     a.rq_per_tensor = p.quant_channel_b == 1;
     a.rq_scale_d = p.scale_d;
     a.rq_zp_d = p.zero_point_d;
+    if (use_pair(a.m, 128)) return pair_gemm_i8(a, true, (cudaStream_t)g.stream);
     return launch_umma<BMode::I8, EpiKind::Req8, Dtype::F32>(a, (cudaStream_t)g.stream);
 }
 
@@ -650,6 +624,8 @@ Result umma_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float 
     a.cmin_f = cmin;
     a.cmax_f = cmax;
     cudaStream_t st = (cudaStream_t)g.stream;
+    if (umma_variant() == 3) return ts_gemm_w4a8(a, td, st);
+    if (use_pair(a.m, 96)) return pair_gemm_w4a8(a, td, st);
     switch (td) {
         case Dtype::F32: return launch_umma<BMode::I4Cx, EpiKind::W4A8, Dtype::F32>(a, st);
         case Dtype::F16: return launch_umma<BMode::I4Cx, EpiKind::W4A8, Dtype::F16>(a, st);

@@ -1,0 +1,66 @@
+// Argument block and small helpers shared by the tensor-core GEMM kernels (single-CTA and CTA-pair).
+#pragma once
+
+#include "dev_common.cuh"
+
+namespace tqt {
+
+enum class BMode : int { I8 = 0, I4Cx = 1, I4C2 = 2 };
+enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3 };
+
+struct UmmaArgs {
+    uint32_t m, n, k;
+    const uint8_t *A;
+    const uint8_t *B;
+    uint32_t a_kblocks_total;  // blocks per row-tile in the A buffer
+    uint32_t b_kblocks_total;  // blocks per row-tile in the B buffer
+    const void *C;
+    size_t ldc;
+    void *D;
+    size_t ldd;
+    const void *bias;
+    int vec_store;  // D rows are 16-byte aligned
+    // s32 / requant
+    int32_t cmin_i, cmax_i;
+    float rq_scale_a;
+    const float *scale_b;  // requant: per channel; W4A8: per channel
+    int rq_per_tensor;
+    float rq_scale_d;
+    int32_t rq_zp_d;
+    // W4A8
+    const float *scale_a;
+    const int32_t *zp_a;
+    float cmin_f, cmax_f;
+    // W4A16
+    const __half *scale_blk;
+    size_t ldsb;
+    uint32_t bl;
+    unsigned int *fault;
+    long long *dbg;  // optional per-CTA role timing (diagnostic), 16 slots per CTA
+};
+
+// output element type of each epilogue
+template <EpiKind EK, Dtype TD>
+struct OutType;
+template <Dtype TD>
+struct OutType<EpiKind::S32, TD> { using type = int32_t; };
+template <Dtype TD>
+struct OutType<EpiKind::Req8, TD> { using type = int8_t; };
+template <Dtype TD>
+struct OutType<EpiKind::W4A8, TD> { using type = typename TdTraits<TD>::type; };
+template <Dtype TD>
+struct OutType<EpiKind::W4A16, TD> { using type = typename TdTraits<TD>::type; };
+
+template <typename T>
+__device__ __forceinline__ T cvt_out(float v);
+template <>
+__device__ __forceinline__ float cvt_out<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __half cvt_out<__half>(float v) { return __float2half_rn(v); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+long long *timing_buffer();
+int sm_count_cached();
+
+}  // namespace tqt
