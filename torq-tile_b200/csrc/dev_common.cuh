@@ -92,8 +92,9 @@ __device__ inline float w4a8_epilogue(int32_t acc, float sa, float sb, bool has_
     float r = __fmul_rn(__fmul_rn(__int2float_rn(acc), sa), sb);
     if (has_c) r = __fadd_rn(r, c);
     if (has_bias) r = __fadd_rn(r, bias);
-    r = r < cmin ? cmin : r;
-    r = r > cmax ? cmax : r;
+    // max / min as the RVV kernel's vfmax / vfmin (identical to the compare-and-select form for non-NaN r)
+    r = fmaxf(r, cmin);
+    r = fminf(r, cmax);
     return r;
 }
 

@@ -320,7 +320,11 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
     int32_t *sRsum = reinterpret_cast<int32_t *>(sRowAll + 8 * 192);      // [2 accumulators][2 converter sets][128]
     uint64_t *bars = reinterpret_cast<uint64_t *>(sRsum + 512);
     constexpr uint32_t T = kW4TStages;
-    constexpr uint32_t kFull = 0, kEmpty = S, kConvFull = 2 * S, kAEmpty = 2 * S + T, kTmemFull = 2 * S + 2 * T,
+    // K steps are committed in groups of two (it >> 1): tcgen05.commit after MMAs that take their M-side
+    // operand from tensor memory costs a pipeline drain, so one commit per group releases two
+    // shared-memory stages and two tensor-memory operand stages together.
+    constexpr uint32_t NG = S / 2;   // shared-memory stage groups; the tensor-memory stages form T / 2 = 2 groups
+    constexpr uint32_t kFull = 0, kGroupDone = S, kConvFull = 2 * S, kTmemFull = 2 * S + 2 * T,
                        kTmemEmpty = kTmemFull + 2, kRsumFull = kTmemFull + 4, kRsumEmpty = kTmemFull + 6;
     uint32_t *sTmemBase = reinterpret_cast<uint32_t *>(bars + kTmemFull + 8);
     volatile int *sAbort = reinterpret_cast<volatile int *>(sTmemBase + 1);
@@ -338,14 +342,9 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
     const uint32_t KB = (args.k + 127) / 128;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < S; ++s) {
-            ptx::mbar_init(BAR(kFull + s), 1);
-            ptx::mbar_init(BAR(kEmpty + s), 1);
-        }
-        for (uint32_t s = 0; s < T; ++s) {
-            ptx::mbar_init(BAR(kConvFull + s), PAIR ? 8 : 4);   // 4 converter warps write a stage, in each CTA
-            ptx::mbar_init(BAR(kAEmpty + s), 1);
-        }
+        for (uint32_t s = 0; s < S; ++s) ptx::mbar_init(BAR(kFull + s), 1);
+        for (uint32_t g = 0; g < NG; ++g) ptx::mbar_init(BAR(kGroupDone + g), 1);
+        for (uint32_t s = 0; s < T; ++s) ptx::mbar_init(BAR(kConvFull + s), PAIR ? 8 : 4);   // 4 converter warps per CTA
         for (uint32_t e = 0; e < 2; ++e) {
             ptx::mbar_init(BAR(kTmemFull + e), 1);
             ptx::mbar_init(BAR(kTmemEmpty + e), PAIR ? 16 : 8);
@@ -391,10 +390,13 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
             const uint8_t *act2 = args.A + (size_t)(blk1 + 1) * args.a_kblocks_total * kI8BlockBytes;
             const uint32_t tx = (nib_valid ? kW4NibBytes : 0u) + (v1 ? rows1 * 128u : 0u) + (v2 ? rows2 * 128u : 0u);
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
-                const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kEmpty + s), ph ^ 1u, sAbort, args.fault, kFaultProducerWait))) {
-                    ok = false;
-                    break;
+                const uint32_t s = it % S, G = it >> 1;
+                if ((it & 1u) == 0u) {   // first K step of a group: the group that used these two stages last is done
+                    if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kGroupDone + G % NG), ((G / NG) & 1u) ^ 1u, sAbort, args.fault,
+                                                              kFaultProducerWait))) {
+                        ok = false;
+                        break;
+                    }
                 }
                 if (lane == 0) ptx::mbar_arrive_expect_tx(BAR(kFull + s), tx);
                 __syncwarp();
@@ -461,13 +463,12 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
                             else
                                 ptx::mma_i8_ts(d_tmem, tmem_a + ts * 32u + j * 8u, b_desc + 2 * j, idesc, (kb | j) ? 1u : 0u);
                         }
+                        const uint32_t G = it >> 1;
                         if constexpr (PAIR) {
-                            ptx::tc_commit_pair(BAR(kEmpty + s), 3);
-                            ptx::tc_commit_pair(BAR(kAEmpty + ts), 3);
+                            if (it & 1u) ptx::tc_commit_pair(BAR(kGroupDone + G % NG), 3);
                             if (kb == KB - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
                         } else {
-                            ptx::tc_commit(BAR(kEmpty + s));
-                            ptx::tc_commit(BAR(kAEmpty + ts));
+                            if (it & 1u) ptx::tc_commit(BAR(kGroupDone + G % NG));
                             if (kb == KB - 1) ptx::tc_commit(BAR(kTmemFull + acc));
                         }
                     }
@@ -477,9 +478,10 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
         }
     } else if (warp < 10) {
         // ===================== epilogue (8 warps per CTA): D^T, lane = output channel ==================
+        // Per-channel values (scale_b, bias, row sum) are per-thread constants; the per-row values
+        // (scale_a, zero_point_a) of a 32-column strip are loaded one per lane and broadcast with
+        // shuffles, so the epilogue makes no shared-memory reads that would queue behind the MMA's.
         const uint32_t quad = warp & 3u, half = (warp - 2u) >> 2;
-        float *sSa = sRowAll + (warp - 2u) * 192u;
-        int32_t *sZp = reinterpret_cast<int32_t *>(sSa + 96);
         const uint32_t row = quad * 32u + lane;             // weight row inside this CTA's block
         uint32_t ti = 0;
         bool ok = true;
@@ -490,13 +492,6 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
             const bool n_ok = n < args.n;
             const uint32_t m0 = tm * kW4MT + half * 96u;
             const uint32_t mcols = args.m > m0 ? min(96u, args.m - m0) : 0u;
-            __syncwarp();
-            for (uint32_t c = lane; c < 96u; c += 32u) {
-                const bool cok = c < mcols;
-                sSa[c] = cok ? args.scale_a[m0 + c] : 0.0f;
-                sZp[c] = cok ? args.zp_a[m0 + c] : 0;
-            }
-            __syncwarp();
             const float sb = n_ok ? args.scale_b[n] : 0.0f;
             const float bv = (n_ok && args.bias) ? TdTraits<TD>::load(args.bias, n) : 0.0f;
             if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)) ||
@@ -509,28 +504,29 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
             const uint32_t t_addr = tmem_base + acc * kW4MT + half * 96u + ((quad * 32u) << 16);
             const uint32_t nchunks = (mcols + 31u) / 32u;
             for (uint32_t ch = 0; ch < nchunks; ++ch) {
+                const uint32_t c0 = ch * 32u;
+                const uint32_t nvalid = min(32u, mcols - c0);
+                const float sa_l = lane < nvalid ? __ldg(args.scale_a + m0 + c0 + lane) : 0.0f;
+                const int32_t zp_l = lane < nvalid ? __ldg(args.zp_a + m0 + c0 + lane) : 0;
                 uint32_t r[32];
                 __syncwarp();
                 const long long tl0 = args.dbg ? clock64() : 0;
-                ptx::tmem_ld_32x32b_x32(t_addr + ch * 32u, r);
+                ptx::tmem_ld_32x32b_x32(t_addr + c0, r);
                 ptx::tmem_wait_ld();
                 if (args.dbg) wcyc[2] += clock64() - tl0;
-                if (n_ok) {
-                    const uint32_t c0 = ch * 32u;
-                    const uint32_t nvalid = min(32u, mcols - c0);
-                    OutT *dcol = static_cast<OutT *>(args.D) + (size_t)(m0 + c0) * args.ldd + n;
+                OutT *dcol = static_cast<OutT *>(args.D) + (size_t)(m0 + c0) * args.ldd + n;
 #pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) {
-                        if (j < nvalid) {
-                            // operands were 16*q: the accumulator is an exact multiple of 16
-                            int32_t a = ((int32_t)r[j]) >> 4;
-                            a -= sZp[c0 + j] * rs;
-                            float cv = 0.0f;
-                            if (args.C) cv = TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n);
-                            const float v = w4a8_epilogue(a, sSa[c0 + j], sb, args.C != nullptr, cv, args.bias != nullptr, bv,
-                                                          args.cmin_f, args.cmax_f);
-                            dcol[(size_t)j * args.ldd] = cvt_out<OutT>(v);   // the warp writes 32 consecutive channels
-                        }
+                for (uint32_t j = 0; j < 32; ++j) {
+                    const float sa = __shfl_sync(0xffffffffu, sa_l, j);
+                    const int32_t zp = __shfl_sync(0xffffffffu, zp_l, j);
+                    // operands were 16*q: the accumulator is an exact multiple of 16
+                    const int32_t a = (((int32_t)r[j]) >> 4) - zp * rs;
+                    if (n_ok && j < nvalid) {
+                        float cv = 0.0f;
+                        if (args.C) cv = TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n);
+                        const float v = w4a8_epilogue(a, sa, sb, args.C != nullptr, cv, args.bias != nullptr, bv, args.cmin_f,
+                                                      args.cmax_f);
+                        dcol[(size_t)j * args.ldd] = cvt_out<OutT>(v);   // the warp writes 32 consecutive channels
                     }
                 }
             }
@@ -574,7 +570,7 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
             int32_t rsum = 0;
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
                 if ((it & 1u) != cset) continue;
-                const uint32_t s = it % S, ph = (it / S) & 1u, ts = it % T, pht = (it / T) & 1u;
+                const uint32_t s = it % S, ph = (it / S) & 1u, ts = it % T;
                 if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultConverterWait))) {
                     ok = false;
                     break;
@@ -593,10 +589,15 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
                 }
                 rsum += (int32_t) reinterpret_cast<const int16_t *>(sNib + s * kW4NibBytes + kI4NibBytes)[row];
                 if (pending) announce(pending_s);
-                // the MMAs that read operand stage ts four steps ago must be done before it is overwritten
-                if (!TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kAEmpty + ts), pht ^ 1u, sAbort, args.fault, kFaultConverterWait))) {
-                    ok = false;
-                    break;
+                // the MMAs of the group two groups back read this tensor-memory stage: they must be done
+                const uint32_t G = it >> 1;
+                if (G >= 2u) {
+                    const uint32_t Gp = G - 2u;
+                    if (!TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
+                                                              kFaultConverterWait))) {
+                        ok = false;
+                        break;
+                    }
                 }
                 __syncwarp();
                 ptx::tmem_st_32x32b_x32(tmem_a + ts * 32u + ((quad * 32u) << 16), regs);
