@@ -249,3 +249,22 @@ def test_w4a8_kernels_forced(oracle, w4a8_variant, td, m, n, k):
     q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, m, n, k, td, m % 2 == 1, True, None)
     got = run_w4a8(td, q, sa, zp, nib, sb, Cm, bias, clamp)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("m,n,k,bl", [(129, 257, 192, 32), (256, 512, 512, 32), (200, 300, 448, 64), (130, 140, 256, 128),
+                                      (70, 260, 320, 8), (192, 128, 64, 2), (400, 384, 1088, 32), (33, 19, 24, 4)])
+def test_w4a16_kernels_forced(oracle, w4a8_variant, m, n, k, bl):
+    """W4A16 on the three tensor-core kernels (weights expanded in shared memory / in tensor memory on a
+    CTA pair / in tensor memory on one CTA); odd numbers of 64-element K steps included."""
+    rng = np.random.default_rng(m + n + k + bl)
+    A = rng.normal(0, 1, (m, k)).astype(np.float16)
+    W = rng.normal(0, 0.02, (n, k)).astype(np.float16)
+    nib, sc = oracle.quantize_fp16_to_int4(W.view(np.uint16), bl)
+    bias = rng.normal(0, 0.1, n).astype(np.float16).view(np.uint16)
+    Cm = rng.normal(0, 1, (m, n)).astype(np.float16).view(np.uint16) if m % 2 else None
+    want = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, bl, TD_F16, Cm, bias)
+    got = run_w4a16("f16", A.view(np.uint16), nib, sc, bl, Cm, bias)
+    _check_w4a16(got, want, "f16")
+    want32 = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, bl, TD_F32, None, None, (-FMAX, FMAX))
+    got32 = run_w4a16("f32", A.view(np.uint16), nib, sc, bl, None, None)
+    _check_w4a16(got32, want32, "f32")

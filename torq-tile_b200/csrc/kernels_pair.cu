@@ -292,40 +292,48 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
 }
 
 // ======================================================================================================
-// W4A8, weights through tensor memory
+// int4 weights through tensor memory: W4A8 (kind::i8) and W4A16 (kind::f16)
 // ======================================================================================================
-constexpr uint32_t kW4Stages = 8;          // shared-memory stages (bulk copies run this far ahead)
-constexpr uint32_t kW4StagesSingle = 6;    // single-CTA variant: 24 KiB of activations per stage
-constexpr uint32_t kW4TStages = 4;         // tensor-memory operand stages (4 x 32 columns)
-constexpr uint32_t kW4MT = 192;            // activation rows per pair tile (MMA N), 96 per CTA
-constexpr uint32_t kW4Threads = 576;       // warp 0 producer, 1 MMA, 2..9 epilogue, 10..17 converters
-constexpr uint32_t kW4NibBytes = 8448, kW4ActBytes = 96 * 128;
-// (padded to more than half of an SM's shared memory: one CTA per SM, each owns all 512 TMEM columns)
-constexpr uint32_t kW4SmemUsed = 1024 + kW4Stages * (kW4ActBytes + kW4NibBytes) + 8 * 2 * 96 * 4 + 2 * 2 * 128 * 4 + 512;
-constexpr uint32_t kW4Smem = kW4SmemUsed > 120 * 1024 ? kW4SmemUsed : 120 * 1024;
-constexpr uint32_t kW4SmemSingle = 1024 + kW4StagesSingle * (192 * 128 + kW4NibBytes) + 8 * 2 * 96 * 4 + 2 * 2 * 128 * 4 + 512;
+enum class TsKind : int { W4A8 = 0, W4A16 = 1 };
 
-template <Dtype TD, bool PAIR>
-__device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
+constexpr uint32_t kTsMT = 192;            // activation rows per tile (MMA N); 96 per CTA in a pair
+constexpr uint32_t kTsThreads = 576;       // warp 0 producer, 1 MMA, 2..9 epilogue, 10..17 converters
+constexpr uint32_t kTsT = 4;               // tensor-memory operand stages (4 x 32 columns)
+
+template <TsKind KD, bool PAIR>
+struct TsCfg {
+    static constexpr bool kF16 = KD == TsKind::W4A16;
+    static constexpr uint32_t NG = PAIR ? 4u : 3u;                 // shared-memory stage groups (two K steps each)
+    static constexpr uint32_t S = NG * 2u;
+    static constexpr uint32_t kActRows = PAIR ? 96u : 192u;        // activation rows this CTA stages per K step
+    static constexpr uint32_t kActBytes = kActRows * 128u;
+    static constexpr uint32_t kNibGroupBytes = kF16 ? 8192u : 2u * 8448u;   // int4 bytes per group of two K steps
+    static constexpr uint32_t kUsed = 1024u + S * kActBytes + NG * kNibGroupBytes + 2u * 2u * 128u * 4u + 512u;
+    // more than half of an SM's shared memory: one CTA per SM, which owns all 512 tensor-memory columns
+    static constexpr uint32_t kSmem = kUsed > 120u * 1024u ? kUsed : 120u * 1024u;
+};
+
+// A K step is 128 int8 (W4A8) or 64 f16 (W4A16): 128 bytes per activation row and 32 tensor-memory
+// columns per weight row either way.  Steps are handled in groups of two: one tcgen05.commit per group
+// releases two shared-memory stages and two tensor-memory operand stages (a commit after MMAs that
+// read their M-side operand from tensor memory drains the MMA pipeline, so they are kept rare).
+template <TsKind KD, Dtype TD, bool PAIR>
+__device__ __forceinline__ void ts_body(const UmmaArgs &args)
 {
+    using Cfg = TsCfg<KD, PAIR>;
     using OutT = typename TdTraits<TD>::type;
-    constexpr uint32_t S = PAIR ? kW4Stages : kW4StagesSingle;
-    constexpr uint32_t kActRows = PAIR ? 96u : 192u;        // activation rows this CTA stages per K step
-    constexpr uint32_t kActBytes = kActRows * 128u;
+    constexpr bool kF16 = Cfg::kF16;
+    constexpr uint32_t S = Cfg::S, NG = Cfg::NG, T = kTsT;
+    constexpr uint32_t kActRows = Cfg::kActRows, kActBytes = Cfg::kActBytes;
+    constexpr uint32_t kStepK = kF16 ? 64u : 128u;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *sAct = smem;                              // S x 12 (pair) or 24 KiB; both multiples of 1024
-    uint8_t *sNib = sAct + S * kActBytes;            // S x 8448 B
-    float *sRowAll = reinterpret_cast<float *>(sNib + S * kW4NibBytes);   // [8 warps][scale_a 96 | zp_a 96]
-    int32_t *sRsum = reinterpret_cast<int32_t *>(sRowAll + 8 * 192);      // [2 accumulators][2 converter sets][128]
+    uint8_t *sAct = smem;                                   // S x 12 or 24 KiB (multiples of 1024)
+    uint8_t *sNib = sAct + S * kActBytes;                   // NG groups of packed int4
+    int32_t *sRsum = reinterpret_cast<int32_t *>(sNib + NG * Cfg::kNibGroupBytes);   // [2 accumulators][2 converter sets][128]
     uint64_t *bars = reinterpret_cast<uint64_t *>(sRsum + 512);
-    constexpr uint32_t T = kW4TStages;
-    // K steps are committed in groups of two (it >> 1): tcgen05.commit after MMAs that take their M-side
-    // operand from tensor memory costs a pipeline drain, so one commit per group releases two
-    // shared-memory stages and two tensor-memory operand stages together.
-    constexpr uint32_t NG = S / 2;   // shared-memory stage groups; the tensor-memory stages form T / 2 = 2 groups
-    constexpr uint32_t kFull = 0, kGroupDone = S, kConvFull = 2 * S, kTmemFull = 2 * S + 2 * T,
-                       kTmemEmpty = kTmemFull + 2, kRsumFull = kTmemFull + 4, kRsumEmpty = kTmemFull + 6;
+    constexpr uint32_t kFull = 0, kGroupDone = S, kConvFull = S + NG, kTmemFull = S + NG + T, kTmemEmpty = kTmemFull + 2,
+                       kRsumFull = kTmemFull + 4, kRsumEmpty = kTmemFull + 6;
     uint32_t *sTmemBase = reinterpret_cast<uint32_t *>(bars + kTmemFull + 8);
     volatile int *sAbort = reinterpret_cast<volatile int *>(sTmemBase + 1);
 
@@ -336,10 +344,11 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
     auto BAR = [&](uint32_t idx) { return bar0 + idx * 8u; };
 
     const uint32_t tiles_m128 = (args.m + 127) / 128;          // 128-row blocks that exist in A_packed
-    const uint32_t tmc = (args.m + kW4MT - 1) / kW4MT;         // 192-row tiles of the activations
+    const uint32_t tmc = (args.m + kTsMT - 1) / kTsMT;         // 192-row tiles of the activations
     const uint32_t nblocks = (args.n + 127) / 128, tnc = PAIR ? (nblocks + 1) / 2 : nblocks;
     const uint32_t num_tiles = tmc * tnc;
-    const uint32_t KB = (args.k + 127) / 128;
+    const uint32_t ksteps = (args.k + kStepK - 1) / kStepK;    // K steps per tile
+    const uint32_t ngroups = (ksteps + 1) / 2;                 // groups per tile (the last may hold one step)
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; ++s) ptx::mbar_init(BAR(kFull + s), 1);
@@ -368,74 +377,79 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
     if constexpr (PAIR) ptx::cluster_sync_all();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *sTmemBase;
-    const uint32_t tmem_a = tmem_base + 2 * kW4MT;   // operand stages after the two accumulators
+    const uint32_t tmem_a = tmem_base + 2 * kTsMT;   // operand stages after the two accumulators
     long long wcyc[3] = {0, 0, 0};
     const long long t_role0 = args.dbg ? clock64() : 0;
 
     if (warp == 0) {
         // ===================== producer (both CTAs) =====================
-        uint32_t it = 0;
+        uint32_t Gc = 0;   // groups issued so far
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs) {
             const uint32_t tm = t % tmc, tn = t / tmc;
             const uint32_t nb = PAIR ? tn * 2 + rank : tn;
             const bool nib_valid = nb < nblocks;
-            const uint8_t *nib_src = args.B + (size_t)nb * args.b_kblocks_total * kI4CxBlockBytes;
+            const uint8_t *nib_src = args.B + (size_t)nb * args.b_kblocks_total * (kF16 ? kI4C2BlockBytes : kI4CxBlockBytes);
             // this CTA's activation rows [a0, a0 + kActRows) = at most two pieces of 128-row blocks
-            const uint32_t a0 = tm * kW4MT + rank * 96u;
+            const uint32_t a0 = tm * kTsMT + rank * 96u;
             const uint32_t blk1 = a0 >> 7, off1 = a0 & 127u;
             const uint32_t rows1 = min(kActRows, 128u - off1), rows2 = kActRows - rows1;
             const bool v1 = blk1 < tiles_m128, v2 = rows2 > 0 && (blk1 + 1) < tiles_m128;
             const uint8_t *act1 = args.A + (size_t)blk1 * args.a_kblocks_total * kI8BlockBytes + off1 * 128u;
             const uint8_t *act2 = args.A + (size_t)(blk1 + 1) * args.a_kblocks_total * kI8BlockBytes;
-            const uint32_t tx = (nib_valid ? kW4NibBytes : 0u) + (v1 ? rows1 * 128u : 0u) + (v2 ? rows2 * 128u : 0u);
-            for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
-                const uint32_t s = it % S, G = it >> 1;
-                if ((it & 1u) == 0u) {   // first K step of a group: the group that used these two stages last is done
-                    if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kGroupDone + G % NG), ((G / NG) & 1u) ^ 1u, sAbort, args.fault,
-                                                              kFaultProducerWait))) {
-                        ok = false;
-                        break;
+            const uint32_t act_tx = (v1 ? rows1 * 128u : 0u) + (v2 ? rows2 * 128u : 0u);
+            for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc) {
+                const uint32_t gs = Gc % NG;
+                if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kGroupDone + gs), ((Gc / NG) & 1u) ^ 1u, sAbort, args.fault,
+                                                          kFaultProducerWait))) {
+                    ok = false;
+                    break;
+                }
+                // every group runs both of its steps so that all barriers advance in lockstep; when the tile
+                // has an odd number of K steps the last one is empty (no bytes, no MMAs)
+                for (uint32_t h = 0; h < 2; ++h) {
+                    const uint32_t s = gs * 2 + h, ks = g * 2 + h;
+                    if (ks >= ksteps) {
+                        if (lane == 0) ptx::mbar_arrive(BAR(kFull + s));
+                        __syncwarp();
+                        continue;
                     }
+                    // W4A8: every step brings its own 128-k block of nibbles; W4A16: the group's single block rides on step 0
+                    const bool nib_now = nib_valid && (!kF16 || h == 0);
+                    const uint32_t nib_bytes = kF16 ? 8192u : 8448u;
+                    if (lane == 0) ptx::mbar_arrive_expect_tx(BAR(kFull + s), act_tx + (nib_now ? nib_bytes : 0u));
+                    __syncwarp();
+                    // three lanes issue one bulk copy each in the same instruction
+                    if (lane == 0) {
+                        if (nib_now)
+                            ptx::bulk_g2s(ptx::smem_u32(sNib + gs * Cfg::kNibGroupBytes + (kF16 ? 0u : h * 8448u)),
+                                          nib_src + (size_t)(kF16 ? g : ks) * nib_bytes, nib_bytes, BAR(kFull + s));
+                    } else if (lane == 1) {
+                        if (v1)
+                            ptx::bulk_g2s(ptx::smem_u32(sAct + s * kActBytes), act1 + (size_t)ks * kI8BlockBytes, rows1 * 128u,
+                                          BAR(kFull + s));
+                    } else if (lane == 2) {
+                        if (v2)
+                            ptx::bulk_g2s(ptx::smem_u32(sAct + s * kActBytes + rows1 * 128u), act2 + (size_t)ks * kI8BlockBytes,
+                                          rows2 * 128u, BAR(kFull + s));
+                    }
+                    __syncwarp();
                 }
-                if (lane == 0) ptx::mbar_arrive_expect_tx(BAR(kFull + s), tx);
-                __syncwarp();
-                // three lanes issue one bulk copy each in the same instruction
-                if (lane == 0) {
-                    if (nib_valid)
-                        ptx::bulk_g2s(ptx::smem_u32(sNib + s * kW4NibBytes), nib_src + (size_t)kb * kI4CxBlockBytes, kW4NibBytes,
-                                      BAR(kFull + s));
-                } else if (lane == 1) {
-                    if (v1)
-                        ptx::bulk_g2s(ptx::smem_u32(sAct + s * kActBytes), act1 + (size_t)kb * kI8BlockBytes, rows1 * 128u,
-                                      BAR(kFull + s));
-                } else if (lane == 2) {
-                    if (v2)
-                        ptx::bulk_g2s(ptx::smem_u32(sAct + s * kActBytes + rows1 * 128u), act2 + (size_t)kb * kI8BlockBytes,
-                                      rows2 * 128u, BAR(kFull + s));
-                }
-                __syncwarp();
             }
         }
         if (!ok) {
-            const uint32_t pending = it < S ? it : S;
-            for (uint32_t i = 0; i < pending; ++i) {
-                const uint32_t j = it - 1 - i;
-                const uint32_t s = j % S, ph = (j / S) & 1u;
-                const long long t0 = clock64();
-                while (!ptx::mbar_try_wait(BAR(kFull + s), ph)) {
-                    if (clock64() - t0 > ptx::kWaitLimitCycles) {
-                        if (args.fault) atomicCAS(args.fault, 0u, (unsigned)kFaultDrainWait);
-                        break;
-                    }
-                }
+            // bail-out: give the copies already issued (a few KiB each) a bounded time to land before the
+            // CTA returns its shared memory
+            const long long t0 = clock64();
+            while (clock64() - t0 < 4000000ll) {
             }
         }
     } else if (warp == 1) {
         // ===================== MMA issuer (leader CTA only; the peer's warp 1 idles) =====================
         if (rank == 0) {
-            const uint32_t idesc = ptx::make_idesc(2u, 1u, 1u, PAIR ? 256 : 128, kW4MT);
-            uint32_t it = 0, ti = 0;
+            const uint32_t idesc = kF16 ? ptx::make_idesc(1u, 0u, 0u, PAIR ? 256 : 128, kTsMT)
+                                        : ptx::make_idesc(2u, 1u, 1u, PAIR ? 256 : 128, kTsMT);
+            uint32_t Gc = 0, ti = 0;
             bool ok = true;
             for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
                 const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
@@ -444,32 +458,45 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
                     break;
                 }
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * kW4MT;
-                for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
-                    const uint32_t s = it % S, ts = it % T, pht = (it / T) & 1u;
-                    // all eight converter warps have written their rows of operand stage ts (which also
-                    // means both CTAs' activation halves of shared-memory stage s have landed)
-                    if (!TQT_PTIMED(1, ptx::mbar_wait_cluster(BAR(kConvFull + ts), pht, sAbort, args.fault, kFaultMmaWaitFull, true))) {
-                        ok = false;
-                        break;
-                    }
-                    ptx::tc_fence_after();
-                    if (lane == 0) {
-                        const uint64_t b_desc = ptx::make_desc_k_sw128(ptx::smem_u32(sAct + s * kActBytes));
-#pragma unroll
-                        for (uint32_t j = 0; j < 4; ++j) {
-                            if constexpr (PAIR)
-                                ptx::mma_i8_ts_pair(d_tmem, tmem_a + ts * 32u + j * 8u, b_desc + 2 * j, idesc, (kb | j) ? 1u : 0u);
-                            else
-                                ptx::mma_i8_ts(d_tmem, tmem_a + ts * 32u + j * 8u, b_desc + 2 * j, idesc, (kb | j) ? 1u : 0u);
+                const uint32_t d_tmem = tmem_base + acc * kTsMT;
+                for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc) {
+                    const uint32_t gs = Gc % NG;
+                    for (uint32_t h = 0; h < 2; ++h) {
+                        const uint32_t s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
+                        const bool step_valid = g * 2 + h < ksteps;
+                        // all converter warps have written their rows of operand stage ts (which also means the
+                        // activation rows of shared-memory stage s have landed, in both CTAs of a pair)
+                        if (!TQT_PTIMED(1, ptx::mbar_wait_cluster(BAR(kConvFull + ts), (Gc >> 1) & 1u, sAbort, args.fault,
+                                                                  kFaultMmaWaitFull, true))) {
+                            ok = false;
+                            break;
                         }
-                        const uint32_t G = it >> 1;
+                        ptx::tc_fence_after();
+                        if (lane == 0 && step_valid) {
+                            const uint64_t b_desc = ptx::make_desc_k_sw128(ptx::smem_u32(sAct + s * kActBytes));
+#pragma unroll
+                            for (uint32_t j = 0; j < 4; ++j) {
+                                const uint32_t accum = (g | h | j) ? 1u : 0u;
+                                const uint32_t a_t = tmem_a + ts * 32u + j * 8u;
+                                if constexpr (kF16) {
+                                    if constexpr (PAIR) ptx::mma_f16_ts_pair(d_tmem, a_t, b_desc + 2 * j, idesc, accum);
+                                    else ptx::mma_f16_ts(d_tmem, a_t, b_desc + 2 * j, idesc, accum);
+                                } else {
+                                    if constexpr (PAIR) ptx::mma_i8_ts_pair(d_tmem, a_t, b_desc + 2 * j, idesc, accum);
+                                    else ptx::mma_i8_ts(d_tmem, a_t, b_desc + 2 * j, idesc, accum);
+                                }
+                            }
+                        }
+                        __syncwarp();
+                    }
+                    if (!ok) break;
+                    if (lane == 0) {
                         if constexpr (PAIR) {
-                            if (it & 1u) ptx::tc_commit_pair(BAR(kGroupDone + G % NG), 3);
-                            if (kb == KB - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
+                            ptx::tc_commit_pair(BAR(kGroupDone + gs), 3);
+                            if (g == ngroups - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
                         } else {
-                            if (it & 1u) ptx::tc_commit(BAR(kGroupDone + G % NG));
-                            if (kb == KB - 1) ptx::tc_commit(BAR(kTmemFull + acc));
+                            ptx::tc_commit(BAR(kGroupDone + gs));
+                            if (g == ngroups - 1) ptx::tc_commit(BAR(kTmemFull + acc));
                         }
                     }
                     __syncwarp();
@@ -490,24 +517,35 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
             const uint32_t n = (PAIR ? tn * 2 + rank : tn) * 128u + row;
             const bool n_ok = n < args.n;
-            const uint32_t m0 = tm * kW4MT + half * 96u;
+            const uint32_t m0 = tm * kTsMT + half * 96u;
             const uint32_t mcols = args.m > m0 ? min(96u, args.m - m0) : 0u;
-            const float sb = n_ok ? args.scale_b[n] : 0.0f;
+            float sb = 0.0f;
+            if constexpr (!kF16) sb = n_ok ? args.scale_b[n] : 0.0f;
             const float bv = (n_ok && args.bias) ? TdTraits<TD>::load(args.bias, n) : 0.0f;
-            if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)) ||
-                !TQT_PTIMED(1, ptx::mbar_wait(BAR(kRsumFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait))) {
+            if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait))) {
                 ok = false;
                 break;
             }
+            int32_t rs = 0;
+            if constexpr (!kF16) {
+                if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kRsumFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait))) {
+                    ok = false;
+                    break;
+                }
+                rs = sRsum[acc * 256 + row] + sRsum[acc * 256 + 128 + row];
+            }
             ptx::tc_fence_after();
-            const int32_t rs = sRsum[acc * 256 + row] + sRsum[acc * 256 + 128 + row];
-            const uint32_t t_addr = tmem_base + acc * kW4MT + half * 96u + ((quad * 32u) << 16);
+            const uint32_t t_addr = tmem_base + acc * kTsMT + half * 96u + ((quad * 32u) << 16);
             const uint32_t nchunks = (mcols + 31u) / 32u;
             for (uint32_t ch = 0; ch < nchunks; ++ch) {
                 const uint32_t c0 = ch * 32u;
                 const uint32_t nvalid = min(32u, mcols - c0);
-                const float sa_l = lane < nvalid ? __ldg(args.scale_a + m0 + c0 + lane) : 0.0f;
-                const int32_t zp_l = lane < nvalid ? __ldg(args.zp_a + m0 + c0 + lane) : 0;
+                float sa_l = 0.0f;
+                int32_t zp_l = 0;
+                if constexpr (!kF16) {
+                    sa_l = lane < nvalid ? __ldg(args.scale_a + m0 + c0 + lane) : 0.0f;
+                    zp_l = lane < nvalid ? __ldg(args.zp_a + m0 + c0 + lane) : 0;
+                }
                 uint32_t r[32];
                 __syncwarp();
                 const long long tl0 = args.dbg ? clock64() : 0;
@@ -517,15 +555,20 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
                 OutT *dcol = static_cast<OutT *>(args.D) + (size_t)(m0 + c0) * args.ldd + n;
 #pragma unroll
                 for (uint32_t j = 0; j < 32; ++j) {
-                    const float sa = __shfl_sync(0xffffffffu, sa_l, j);
-                    const int32_t zp = __shfl_sync(0xffffffffu, zp_l, j);
-                    // operands were 16*q: the accumulator is an exact multiple of 16
-                    const int32_t a = (((int32_t)r[j]) >> 4) - zp * rs;
+                    float v;
+                    if constexpr (!kF16) {
+                        const float sa = __shfl_sync(0xffffffffu, sa_l, j);
+                        const int32_t zp = __shfl_sync(0xffffffffu, zp_l, j);
+                        // operands were 16*q: the accumulator is an exact multiple of 16
+                        const int32_t a = (((int32_t)r[j]) >> 4) - zp * rs;
+                        v = __fmul_rn(__fmul_rn(__int2float_rn(a), sa), sb);
+                    } else {
+                        v = __uint_as_float(r[j]);
+                    }
                     if (n_ok && j < nvalid) {
-                        float cv = 0.0f;
-                        if (args.C) cv = TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n);
-                        const float v = w4a8_epilogue(a, sa, sb, args.C != nullptr, cv, args.bias != nullptr, bv, args.cmin_f,
-                                                      args.cmax_f);
+                        if (args.C) v = __fadd_rn(v, TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n));
+                        if (args.bias) v = __fadd_rn(v, bv);
+                        v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
                         dcol[(size_t)j * args.ldd] = cvt_out<OutT>(v);   // the warp writes 32 consecutive channels
                     }
                 }
@@ -537,19 +580,18 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
                     ptx::mbar_arrive(BAR(kTmemEmpty + acc));
                 else
                     ptx::mbar_arrive_cluster(ptx::mapa(BAR(kTmemEmpty + acc), 0));
-                ptx::mbar_arrive(BAR(kRsumEmpty + acc));
+                if constexpr (!kF16) ptx::mbar_arrive(BAR(kRsumEmpty + acc));
             }
         }
     } else {
-        // ===================== converters (warps 10..17): int4 -> int8 (16*q) into tensor memory ========
-        // Two warps per tensor-memory lane quadrant: set 0 (warps 10..13) takes the even K steps, set 1
-        // (warps 14..17) the odd ones.  Inside a warp the tensor-memory store of step i stays in flight
-        // while step i+2 is fetched and expanded; only then does the warp wait for the store and
-        // announce step i.
+        // ===================== converters (warps 10..17): int4 -> MMA operand type, into tensor memory ========
+        // Two warps per tensor-memory lane quadrant: set 0 (warps 10..13) takes step 0 of every group, set 1
+        // (warps 14..17) step 1.  Inside a warp the tensor-memory store of one step stays in flight while
+        // the next one is fetched and expanded; only then does the warp wait for the store and announce it.
         const uint32_t quad = warp & 3u, cset = (warp - 10u) >> 2;
         const uint32_t row = quad * 32u + lane;
         const uint32_t swz_in = (row >> 1) & 3u;
-        const uint32_t conv_full_leader = ptx::mapa(BAR(kConvFull), 0);   // + 8 * s
+        const uint32_t conv_full_leader = PAIR ? ptx::mapa(BAR(kConvFull), 0) : 0u;   // + 8 * ts
         auto announce = [&](uint32_t ts) {
             ptx::tmem_wait_st();
             ptx::tc_fence_before();
@@ -561,38 +603,106 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
                     ptx::mbar_arrive_cluster(conv_full_leader + ts * 8u);
             }
         };
-        uint32_t it = 0, ti = 0;
+        uint32_t Gc = 0, ti = 0;
         bool ok = true;
         bool pending = false;      // a tensor-memory store has been issued but not announced
-        uint32_t pending_s = 0;
+        uint32_t pending_ts = 0;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
+            const uint32_t tn = t / tmc;
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
+            const size_t nrow = (size_t)(PAIR ? tn * 2 + rank : tn) * 128u + row;
             int32_t rsum = 0;
-            for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
-                if ((it & 1u) != cset) continue;
-                const uint32_t s = it % S, ph = (it / S) & 1u, ts = it % T;
-                if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultConverterWait))) {
+            for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc) {
+                const uint32_t h = cset, gs = Gc % NG, s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
+                const uint32_t phs = (Gc / NG) & 1u;
+                const bool step_valid = g * 2 + h < ksteps;
+                if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kFull + s), phs, sAbort, args.fault, kFaultConverterWait))) {
                     ok = false;
                     break;
                 }
-                const uint8_t *nrow = sNib + s * kW4NibBytes + row * 64u;
-                uint32_t regs[32];
-#pragma unroll
-                for (uint32_t seg = 0; seg < 4; ++seg) {
-                    const uint4 w = *reinterpret_cast<const uint4 *>(nrow + ((seg ^ swz_in) << 4));
-                    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j) {
-                        regs[seg * 8 + j] = (ws[j] << 4) & 0xF0F0F0F0u;       // k = 32 seg + 4 j .. + 3
-                        regs[seg * 8 + 4 + j] = ws[j] & 0xF0F0F0F0u;          // k = 32 seg + 16 + 4 j .. + 3
+                if (kF16 && h == 1) {   // the group's nibbles arrived with step 0
+                    if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kFull + gs * 2), phs, sAbort, args.fault, kFaultConverterWait))) {
+                        ok = false;
+                        break;
                     }
                 }
-                rsum += (int32_t) reinterpret_cast<const int16_t *>(sNib + s * kW4NibBytes + kI4NibBytes)[row];
-                if (pending) announce(pending_s);
+                if (!step_valid) {   // empty step of an odd tile: keep the barrier in step, nothing to convert
+                    if (pending) {
+                        announce(pending_ts);
+                        pending = false;
+                    }
+                    // like a real step, it may only be announced once the group that used this operand stage
+                    // before is done: otherwise two announcements could fall into one phase of the barrier
+                    if (Gc >= 2u) {
+                        const uint32_t Gp = Gc - 2u;
+                        if (!TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
+                                                                  kFaultConverterWait))) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rank == 0)
+                            ptx::mbar_arrive(BAR(kConvFull + ts));
+                        else
+                            ptx::mbar_arrive_cluster(conv_full_leader + ts * 8u);
+                    }
+                    continue;
+                }
+                uint32_t regs[32];
+                if constexpr (!kF16) {
+                    const uint8_t *blk = sNib + gs * Cfg::kNibGroupBytes + h * 8448u;
+                    const uint8_t *nrowp = blk + row * 64u;
+#pragma unroll
+                    for (uint32_t seg = 0; seg < 4; ++seg) {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(nrowp + ((seg ^ swz_in) << 4));
+                        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            regs[seg * 8 + j] = (ws[j] << 4) & 0xF0F0F0F0u;       // k = 32 seg + 4 j .. + 3
+                            regs[seg * 8 + 4 + j] = ws[j] & 0xF0F0F0F0u;          // k = 32 seg + 16 + 4 j .. + 3
+                        }
+                    }
+                    rsum += (int32_t) reinterpret_cast<const int16_t *>(blk + kI4NibBytes)[row];
+                } else {
+                    // 64 k of this step = segments 2h, 2h+1 of the 128-k block; each word holds 8 k as nibbles
+                    // (k0,k2,k4,k6,k1,k3,k5,k7) so that (w >> 4t) & 0x000F000F = (k2t, k2t+1).  nibble u = q + 8;
+                    // 0x6400 | u is the f16 1024 + u, so q = that - 1032 exactly, and q * scale is rounded once.
+                    const uint8_t *nrowp = sNib + gs * Cfg::kNibGroupBytes + row * 64u;
+                    const bool n_ok = nrow < args.n;
+                    const uint32_t kbase = (g * 2 + h) * 64u;
+                    const __half *srow = args.scale_blk + nrow * args.ldsb;
+                    const __half2 k1032 = __float2half2_rn(1032.0f);
+                    const bool word_scale = (args.bl & 7u) == 0u;   // one scale per 8-k word
+#pragma unroll
+                    for (uint32_t sg = 0; sg < 2; ++sg) {
+                        const uint4 w4 = *reinterpret_cast<const uint4 *>(nrowp + (((2 * h + sg) ^ swz_in) << 4));
+                        const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                        for (uint32_t wi = 0; wi < 4; ++wi) {
+                            const uint32_t k0 = kbase + sg * 32u + wi * 8u;   // first k of this word
+                            __half2 sc2 = __float2half2_rn(0.0f);
+                            if (word_scale) {
+                                if (n_ok && k0 < args.k) sc2 = __half2half2(__ldg(srow + k0 / args.bl));
+                            }
+#pragma unroll
+                            for (uint32_t tt = 0; tt < 4; ++tt) {
+                                if (!word_scale) {
+                                    const uint32_t kk = k0 + 2 * tt;   // bl is even: a pair never straddles blocks
+                                    sc2 = (n_ok && kk < args.k) ? __half2half2(__ldg(srow + kk / args.bl)) : __float2half2_rn(0.0f);
+                                }
+                                const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
+                                const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032), sc2);
+                                regs[sg * 16 + wi * 4 + tt] = *reinterpret_cast<const uint32_t *>(&v);
+                            }
+                        }
+                    }
+                }
+                if (pending) announce(pending_ts);
                 // the MMAs of the group two groups back read this tensor-memory stage: they must be done
-                const uint32_t G = it >> 1;
-                if (G >= 2u) {
-                    const uint32_t Gp = G - 2u;
+                if (Gc >= 2u) {
+                    const uint32_t Gp = Gc - 2u;
                     if (!TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
                                                               kFaultConverterWait))) {
                         ok = false;
@@ -602,22 +712,24 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
                 __syncwarp();
                 ptx::tmem_st_32x32b_x32(tmem_a + ts * 32u + ((quad * 32u) << 16), regs);
                 pending = true;
-                pending_s = ts;
+                pending_ts = ts;
             }
             if (!ok) break;
             if (pending) {   // the tile's last step must be visible before the leader can finish the tile
-                announce(pending_s);
+                announce(pending_ts);
                 pending = false;
             }
-            if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kRsumEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultConverterWait))) {
-                ok = false;
-                break;
+            if constexpr (!kF16) {
+                if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kRsumEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultConverterWait))) {
+                    ok = false;
+                    break;
+                }
+                sRsum[acc * 256 + cset * 128 + row] = rsum;
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(BAR(kRsumFull + acc));
             }
-            sRsum[acc * 256 + cset * 128 + row] = rsum;
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(BAR(kRsumFull + acc));
         }
-        if (pending) announce(pending_s);
+        if (pending) announce(pending_ts);
     }
 
     if (args.dbg && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 10)) {
@@ -639,51 +751,23 @@ __device__ __forceinline__ void w4a8_ts_body(const UmmaArgs &args)
     }
 }
 
-template <Dtype TD>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kW4Threads, 1) gemm_pair_w4a8_kernel(const UmmaArgs args)
+template <TsKind KD, Dtype TD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1) gemm_ts_pair_kernel(const UmmaArgs args)
 {
-    w4a8_ts_body<TD, true>(args);
+    ts_body<KD, TD, true>(args);
 }
 
 // Same kernel on one CTA (cta_group::1): the CTA stages all 192 activation rows itself.
-template <Dtype TD>
-__global__ void __launch_bounds__(kW4Threads, 1) gemm_ts_w4a8_kernel(const UmmaArgs args)
+template <TsKind KD, Dtype TD>
+__global__ void __launch_bounds__(kTsThreads, 1) gemm_ts_kernel(const UmmaArgs args)
 {
-    w4a8_ts_body<TD, false>(args);
+    ts_body<KD, TD, false>(args);
 }
-
 
 // ---- host side ------------------------------------------------------------------------------------------
 template <class Kern>
-static Result launch_pair(Kern kern, const UmmaArgs &a, uint32_t num_tiles, uint32_t threads, uint32_t smem, cudaStream_t st,
-                          bool *attr_set)
-{
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
-        attr_set[dev] = true;
-    }
-    const uint32_t max_pairs = (uint32_t)sm_count_cached() / 2;
-    const uint32_t pairs = num_tiles < max_pairs ? num_tiles : max_pairs;
-    kern<<<pairs * 2, threads, smem, st>>>(a);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
-    return Result{kOk, 0};
-}
-
-Result pair_gemm_i8(const UmmaArgs &a, bool requant, cudaStream_t st)
-{
-    const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
-    static bool set_s32[64] = {false}, set_req[64] = {false};
-    if (requant) return launch_pair(gemm_pair_i8_kernel<EpiKind::Req8>, a, tiles, kI8Threads, kI8Smem, st, set_req);
-    return launch_pair(gemm_pair_i8_kernel<EpiKind::S32>, a, tiles, kI8Threads, kI8Smem, st, set_s32);
-}
-
-template <class Kern>
-static Result launch_single(Kern kern, const UmmaArgs &a, uint32_t num_tiles, uint32_t threads, uint32_t smem, cudaStream_t st,
-                            bool *attr_set)
+static Result launch_grid(Kern kern, const UmmaArgs &a, uint32_t num_tiles, bool pair, uint32_t threads, uint32_t smem,
+                          cudaStream_t st, bool *attr_set)
 {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -693,32 +777,50 @@ static Result launch_single(Kern kern, const UmmaArgs &a, uint32_t num_tiles, ui
         attr_set[dev] = true;
     }
     const uint32_t sms = (uint32_t)sm_count_cached();
-    kern<<<num_tiles < sms ? num_tiles : sms, threads, smem, st>>>(a);
+    uint32_t grid;
+    if (pair) {
+        const uint32_t max_pairs = sms / 2;
+        grid = 2 * (num_tiles < max_pairs ? num_tiles : max_pairs);
+    } else {
+        grid = num_tiles < sms ? num_tiles : sms;
+    }
+    kern<<<grid, threads, smem, st>>>(a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
     return Result{kOk, 0};
 }
 
-Result ts_gemm_w4a8(const UmmaArgs &a, Dtype td, cudaStream_t st)
+Result pair_gemm_i8(const UmmaArgs &a, bool requant, cudaStream_t st)
 {
-    const uint32_t tiles = ((a.m + kW4MT - 1) / kW4MT) * ((a.n + 127) / 128);
-    static bool set0[64] = {false}, set1[64] = {false}, set2[64] = {false};
+    const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
+    static bool set_s32[64] = {false}, set_req[64] = {false};
+    if (requant) return launch_grid(gemm_pair_i8_kernel<EpiKind::Req8>, a, tiles, true, kI8Threads, kI8Smem, st, set_req);
+    return launch_grid(gemm_pair_i8_kernel<EpiKind::S32>, a, tiles, true, kI8Threads, kI8Smem, st, set_s32);
+}
+
+template <TsKind KD, Dtype TD>
+static Result launch_ts(const UmmaArgs &a, bool pair, cudaStream_t st)
+{
+    const uint32_t nblocks = (a.n + 127) / 128;
+    const uint32_t tiles = ((a.m + kTsMT - 1) / kTsMT) * (pair ? (nblocks + 1) / 2 : nblocks);
+    static bool set_p[64] = {false}, set_s[64] = {false};
+    if (pair) return launch_grid(gemm_ts_pair_kernel<KD, TD>, a, tiles, true, kTsThreads, TsCfg<KD, true>::kSmem, st, set_p);
+    return launch_grid(gemm_ts_kernel<KD, TD>, a, tiles, false, kTsThreads, TsCfg<KD, false>::kSmem, st, set_s);
+}
+
+Result ts_gemm_w4a8(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st)
+{
     switch (td) {
-        case Dtype::F32: return launch_single(gemm_ts_w4a8_kernel<Dtype::F32>, a, tiles, kW4Threads, kW4SmemSingle, st, set0);
-        case Dtype::F16: return launch_single(gemm_ts_w4a8_kernel<Dtype::F16>, a, tiles, kW4Threads, kW4SmemSingle, st, set1);
-        default: return launch_single(gemm_ts_w4a8_kernel<Dtype::BF16>, a, tiles, kW4Threads, kW4SmemSingle, st, set2);
+        case Dtype::F32: return launch_ts<TsKind::W4A8, Dtype::F32>(a, pair, st);
+        case Dtype::F16: return launch_ts<TsKind::W4A8, Dtype::F16>(a, pair, st);
+        default: return launch_ts<TsKind::W4A8, Dtype::BF16>(a, pair, st);
     }
 }
 
-Result pair_gemm_w4a8(const UmmaArgs &a, Dtype td, cudaStream_t st)
+Result ts_gemm_w4a16(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st)
 {
-    const uint32_t tiles = ((a.m + kW4MT - 1) / kW4MT) * ((((a.n + 127) / 128) + 1) / 2);
-    static bool set0[64] = {false}, set1[64] = {false}, set2[64] = {false};
-    switch (td) {
-        case Dtype::F32: return launch_pair(gemm_pair_w4a8_kernel<Dtype::F32>, a, tiles, kW4Threads, kW4Smem, st, set0);
-        case Dtype::F16: return launch_pair(gemm_pair_w4a8_kernel<Dtype::F16>, a, tiles, kW4Threads, kW4Smem, st, set1);
-        default: return launch_pair(gemm_pair_w4a8_kernel<Dtype::BF16>, a, tiles, kW4Threads, kW4Smem, st, set2);
-    }
+    if (td == Dtype::F16) return launch_ts<TsKind::W4A16, Dtype::F16>(a, pair, st);
+    return launch_ts<TsKind::W4A16, Dtype::F32>(a, pair, st);
 }
 
 }  // namespace tqt

@@ -565,8 +565,8 @@ static bool fill_common(UmmaArgs &a, const GemmCommon &g, size_t out_elem, size_
 }
 
 Result pair_gemm_i8(const UmmaArgs &a, bool requant, cudaStream_t st);
-Result pair_gemm_w4a8(const UmmaArgs &a, Dtype td, cudaStream_t st);
-Result ts_gemm_w4a8(const UmmaArgs &a, Dtype td, cudaStream_t st);
+Result ts_gemm_w4a8(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st);
+Result ts_gemm_w4a16(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st);
 
 // TQT_B200_UMMA=single|pair forces one of the two tensor-core kernels (tests); default: CTA pairs
 // once the problem has more than one 128-row tile, the single-CTA kernel below that.
@@ -624,8 +624,8 @@ Result umma_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float 
     a.cmin_f = cmin;
     a.cmax_f = cmax;
     cudaStream_t st = (cudaStream_t)g.stream;
-    if (umma_variant() == 3) return ts_gemm_w4a8(a, td, st);
-    if (use_pair(a.m, 96)) return pair_gemm_w4a8(a, td, st);
+    if (umma_variant() == 3) return ts_gemm_w4a8(a, td, false, st);
+    if (use_pair(a.m, 96)) return ts_gemm_w4a8(a, td, true, st);
     switch (td) {
         case Dtype::F32: return launch_umma<BMode::I4Cx, EpiKind::W4A8, Dtype::F32>(a, st);
         case Dtype::F16: return launch_umma<BMode::I4Cx, EpiKind::W4A8, Dtype::F16>(a, st);
@@ -645,6 +645,8 @@ Result umma_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size
     a.cmin_f = cmin;
     a.cmax_f = cmax;
     cudaStream_t st = (cudaStream_t)g.stream;
+    if (umma_variant() == 3) return ts_gemm_w4a16(a, td, false, st);
+    if (use_pair(a.m, 96)) return ts_gemm_w4a16(a, td, true, st);
     if (td == Dtype::F16) return launch_umma<BMode::I4C2, EpiKind::W4A16, Dtype::F16>(a, st);
     return launch_umma<BMode::I4C2, EpiKind::W4A16, Dtype::F32>(a, st);
 }
