@@ -592,6 +592,11 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
         const uint32_t row = quad * 32u + lane;
         const uint32_t swz_in = (row >> 1) & 3u;
         const uint32_t conv_full_leader = PAIR ? ptx::mapa(BAR(kConvFull), 0) : 0u;   // + 8 * ts
+        const bool word_scale = kF16 && (args.bl & 7u) == 0u;   // W4A16: one scale per 8-k word (bl a multiple of 8)
+        const int bl_shift = (kF16 && args.bl && (args.bl & (args.bl - 1u)) == 0u) ? (int)__ffs((int)args.bl) - 1 : -1;
+        // the last window of a row may read up to 7 entries past the row's k / bl scales: only when that stays
+        // inside the row stride (ldsb a multiple of 8 covers it) and the base is 16-byte aligned
+        const bool sc_vec = kF16 && bl_shift >= 3 && (args.ldsb & 7u) == 0u && (reinterpret_cast<uintptr_t>(args.scale_blk) & 15u) == 0u;
         auto announce = [&](uint32_t ts) {
             ptx::tmem_wait_st();
             ptx::tc_fence_before();
@@ -612,10 +617,50 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
             const size_t nrow = (size_t)(PAIR ? tn * 2 + rank : tn) * 128u + row;
             int32_t rsum = 0;
+            // W4A16 block scales: scale_b[nrow, k / bl].  When bl is a power of two >= 8 and the rows of scale_b
+            // are 16-byte aligned, one 128-bit load fetches the eight scales that cover the next 8 * bl values of
+            // k (four K steps at bl = 32) and stays cached in registers; otherwise eight scalar loads per step.
+            uint4 sc_win = make_uint4(0, 0, 0, 0);
+            uint32_t sc_base = 0xffffffffu;
+            auto load_scales = [&](uint32_t step, bool valid, __half(&sc)[8]) {
+                const uint32_t kb0 = step * 64u;
+                const bool n_ok = nrow < args.n;
+                const __half *srow = args.scale_blk + nrow * args.ldsb;
+                if (sc_vec) {
+                    const uint32_t sh = (uint32_t)bl_shift & 31u;   // sc_vec implies bl_shift >= 3
+                    const uint32_t i0 = kb0 >> sh;
+                    const uint32_t base = i0 & ~7u;
+                    if (base != sc_base) {
+                        sc_win = (valid && n_ok) ? __ldg(reinterpret_cast<const uint4 *>(srow + base)) : make_uint4(0, 0, 0, 0);
+                        sc_base = base;
+                    }
+                    const unsigned long long lo = ((unsigned long long)sc_win.y << 32) | sc_win.x;
+                    const unsigned long long hi = ((unsigned long long)sc_win.w << 32) | sc_win.z;
+#pragma unroll
+                    for (uint32_t w = 0; w < 8; ++w) {
+                        const uint32_t k0 = kb0 + w * 8u;
+                        const uint32_t idx = (k0 >> sh) - base;   // 0..7 (entries past k / bl are never selected for k0 < k)
+                        const unsigned long long v = (idx & 4u) ? hi : lo;
+                        const unsigned short bits = (unsigned short)(v >> (16u * (idx & 3u)));
+                        sc[w] = (valid && k0 < args.k) ? __ushort_as_half(bits) : __ushort_as_half((unsigned short)0);
+                    }
+                } else {
+#pragma unroll
+                    for (uint32_t w = 0; w < 8; ++w) {
+                        const uint32_t k0 = kb0 + w * 8u;
+                        const uint32_t bi = bl_shift >= 0 ? (k0 >> ((uint32_t)bl_shift & 31u)) : (k0 / args.bl);
+                        sc[w] = (valid && word_scale && n_ok && k0 < args.k) ? __ldg(srow + bi) : __ushort_as_half((unsigned short)0);
+                    }
+                }
+            };
             for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc) {
                 const uint32_t h = cset, gs = Gc % NG, s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
                 const uint32_t phs = (Gc / NG) & 1u;
                 const bool step_valid = g * 2 + h < ksteps;
+                // W4A16: the block scales of a step (one per 8-k word) do not depend on the barriers; they were
+                // requested during the previous step of this warp (or are requested here, for a tile's first step)
+                __half sc8[8];
+                if constexpr (kF16) load_scales(g * 2 + h, step_valid, sc8);
                 if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kFull + s), phs, sAbort, args.fault, kFaultConverterWait))) {
                     ok = false;
                     break;
@@ -674,27 +719,40 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                     const uint32_t kbase = (g * 2 + h) * 64u;
                     const __half *srow = args.scale_blk + nrow * args.ldsb;
                     const __half2 k1032 = __float2half2_rn(1032.0f);
-                    const bool word_scale = (args.bl & 7u) == 0u;   // one scale per 8-k word
+                    if (word_scale) {
+                        // common case (block length a multiple of 8): branch-free, one scale per 8-k word
 #pragma unroll
-                    for (uint32_t sg = 0; sg < 2; ++sg) {
-                        const uint4 w4 = *reinterpret_cast<const uint4 *>(nrowp + (((2 * h + sg) ^ swz_in) << 4));
-                        const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
+                        for (uint32_t sg = 0; sg < 2; ++sg) {
+                            const uint4 w4 = *reinterpret_cast<const uint4 *>(nrowp + (((2 * h + sg) ^ swz_in) << 4));
+                            const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
-                        for (uint32_t wi = 0; wi < 4; ++wi) {
-                            const uint32_t k0 = kbase + sg * 32u + wi * 8u;   // first k of this word
-                            __half2 sc2 = __float2half2_rn(0.0f);
-                            if (word_scale) {
-                                if (n_ok && k0 < args.k) sc2 = __half2half2(__ldg(srow + k0 / args.bl));
-                            }
+                            for (uint32_t wi = 0; wi < 4; ++wi) {
+                                const __half2 sc2 = __half2half2(sc8[sg * 4 + wi]);
 #pragma unroll
-                            for (uint32_t tt = 0; tt < 4; ++tt) {
-                                if (!word_scale) {
-                                    const uint32_t kk = k0 + 2 * tt;   // bl is even: a pair never straddles blocks
-                                    sc2 = (n_ok && kk < args.k) ? __half2half2(__ldg(srow + kk / args.bl)) : __float2half2_rn(0.0f);
+                                for (uint32_t tt = 0; tt < 4; ++tt) {
+                                    const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
+                                    const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032), sc2);
+                                    regs[sg * 16 + wi * 4 + tt] = *reinterpret_cast<const uint32_t *>(&v);
                                 }
-                                const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
-                                const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032), sc2);
-                                regs[sg * 16 + wi * 4 + tt] = *reinterpret_cast<const uint32_t *>(&v);
+                            }
+                        }
+                    } else {
+                        // block lengths 2, 4, 6, ...: one scale per pair of k (a pair never straddles blocks)
+#pragma unroll
+                        for (uint32_t sg = 0; sg < 2; ++sg) {
+                            const uint4 w4 = *reinterpret_cast<const uint4 *>(nrowp + (((2 * h + sg) ^ swz_in) << 4));
+                            const uint32_t ws[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                            for (uint32_t wi = 0; wi < 4; ++wi) {
+#pragma unroll
+                                for (uint32_t tt = 0; tt < 4; ++tt) {
+                                    const uint32_t kk = kbase + sg * 32u + wi * 8u + 2 * tt;
+                                    const __half2 sc2 = (n_ok && kk < args.k) ? __half2half2(__ldg(srow + kk / args.bl))
+                                                                              : __float2half2_rn(0.0f);
+                                    const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
+                                    const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032), sc2);
+                                    regs[sg * 16 + wi * 4 + tt] = *reinterpret_cast<const uint32_t *>(&v);
+                                }
                             }
                         }
                     }
