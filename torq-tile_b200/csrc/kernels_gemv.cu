@@ -1,14 +1,18 @@
-// HBM-streaming W4A8 GEMV for decode (m <= 8; 9..16 rows run on the tensor-core kernel): no tensor cores, no clusters, no scratch memory.
+// HBM-streaming W4A8 GEMV for decode (m <= 8; more rows run on the tensor-core kernel): no tensor
+// cores, no clusters, no shared-memory staging of weights, no scratch memory.
 //
-// One CTA per 32 output columns (32 consecutive rows of one 128-row block tile of B_packed) over
-// the whole K.  Warp w owns rows 4w..4w+3; inside a warp lane = (row, kgroup): the eight kgroups
-// split the K blocks.  Every thread issues the 128-bit loads of its share of the weights straight
-// into registers at kernel entry (16 loads = 256 B per thread per round of 32 K blocks, 64 KiB per
-// CTA), so the whole weight matrix is in flight across the GPU before any arithmetic starts and no
-// single thread serialises the requests.  Nibbles are expanded with two logic ops per 8 weights
-// (operands 16*q, as in the tensor-core kernel), accumulated with dp4a against activation words
-// staged in shared memory, and the eight kgroups are combined with warp shuffles: integer sums, so
-// the result is exact and independent of the split.  The epilogue is the GEMM's (reference:
+// A CTA owns 8 consecutive output columns (8 rows of one 128-row block tile of B_packed); its eight
+// warps take interleaved K blocks.  Inside a warp lane = (row, 16-byte segment), so one warp-wide
+// 128-bit load covers 512 contiguous bytes of a packed block (every 32-byte sector is used whole,
+// once).  A thread holds only four loads at a time and few registers, so six to eight CTAs (48-64
+// warps) are resident per SM: on this part a streaming read reaches full bandwidth with many warps
+// that each have a few loads outstanding, not with few warps that have many (measured: 148 x 2
+// CTAs with 8 loads per thread reach 5.5 TB/s on 117 MB, 148 x 4 CTAs with 4 loads 6.4 TB/s).
+// Nibbles are expanded with two logic ops per 8 weights (operands 16*q, as in the tensor-core
+// kernel) and accumulated with dp4a against activation words read through L1 (a few KiB, always
+// resident; weights bypass L1).  The four segments of a row are combined with warp shuffles and the
+// eight warps through shared memory: integer sums, so the result is exact and independent of the
+// split.  The epilogue is the GEMM's (reference:
 // src/gemm/gemm_i8_i4/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp/..._4x1vl_rvv.cpp:118-177).
 //
 // Programmatic dependent launch: the kernel lets its successor start at once and requests its
@@ -22,22 +26,12 @@
 
 namespace tqt {
 
-long long *timing_buffer();
-
-__device__ __forceinline__ long long gtime_ns()
-{
-    long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
 constexpr uint32_t kGemvThreads = 256;
-constexpr uint32_t kGemvRows = 32;      // output columns per CTA
-constexpr uint32_t kGemvRoundKB = 32;   // K blocks per round: 8 kgroups x 4 blocks per thread
+constexpr uint32_t kGemvWarpRows = 8;   // output columns per warp
 
 struct GemvArgs {
     uint32_t m, n, k;
-    const uint8_t *A;  // packed int8 blocks (row-tile 0 only: m <= 16)
+    const uint8_t *A;  // packed int8 blocks (row-tile 0 only: m <= 8)
     const uint8_t *B;  // packed qsi4cx blocks
     uint32_t b_kblocks_total;
     const void *C;
@@ -50,7 +44,6 @@ struct GemvArgs {
     const float *scale_b;
     float cmin, cmax;
     int pdl;
-    long long *dbg;  // optional per-CTA phase timestamps (diagnostic), 16 slots per CTA
 };
 
 // 128-bit streaming load: read-only path, do not keep the line in L1.
@@ -63,118 +56,112 @@ __device__ __forceinline__ uint4 ldg_stream(const void *p)
     return v;
 }
 
-template <int MR, Dtype TD>
-__global__ void __launch_bounds__(kGemvThreads, (MR <= 4 ? 2 : 1)) gemv_w4a8_kernel(const GemvArgs args)
-{
-    // activations of one round, de-swizzled: [32 K blocks][MR rows][128 B] (+16 B per block against bank conflicts)
-    constexpr uint32_t kActStride = MR * 128u + 16u;
-    __shared__ __align__(16) uint8_t sAct[kGemvRoundKB * kActStride];
-    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t tile = blockIdx.x >> 2, quarter = blockIdx.x & 3u;
-    const uint32_t KB = (args.k + 127) / 128;
-    const uint32_t row_l = lane >> 3, kg = lane & 7u;
-    const uint32_t r_blk = quarter * kGemvRows + warp * 4u + row_l;   // row inside the 128-row block
-    const uint32_t swz = (r_blk >> 1) & 3u;
+constexpr uint32_t kGemvSlices = 8;     // warps of a CTA = interleaved K slices
+constexpr uint32_t kGemvChunk = 4;      // loads in flight per thread
 
-    long long ts[5] = {0, 0, 0, 0, 0};
-    const bool dbg = args.dbg != nullptr && tid == 0;
-    if (dbg) ts[0] = gtime_ns();
+template <int MR>
+constexpr int gemv_min_ctas() { return MR <= 2 ? 5 : (MR <= 4 ? 4 : 3); }
+
+template <int MR, Dtype TD>
+__global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR>()) gemv_w4a8_kernel(const GemvArgs args)
+{
+    constexpr uint32_t S = kGemvSlices, CH = kGemvChunk;
+    __shared__ int32_t sRed[(S - 1) * kGemvWarpRows * (MR + 1)];
+    const uint32_t tid = threadIdx.x, ks = tid >> 5, lane = tid & 31u;
+    const uint32_t row0 = blockIdx.x * kGemvWarpRows;              // first output column of this CTA
+    const uint32_t tile = row0 >> 7;
+    const uint32_t rr = lane >> 2;                                 // row inside the CTA
+    const uint32_t r_blk = (row0 & 127u) + rr;                     // row inside the 128-row block
+    const uint32_t pos = lane & 3u;                                // physical 16-byte segment
+    const uint32_t seg = pos ^ ((r_blk >> 1) & 3u);                // logical segment: k = 32*seg .. 32*seg+31
+    const uint32_t KB = (args.k + 127) / 128;
+    const uint32_t T = KB > ks ? (KB - ks + S - 1) / S : 0;        // K blocks of this warp: ks, ks+S, ...
+
     if (args.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-    const uint8_t *wbase = args.B + (size_t)tile * args.b_kblocks_total * kI4CxBlockBytes + r_blk * 64u;
-    uint4 wcur[16];
-    auto load_round = [&](uint32_t base, uint4(&w)[16]) {
+    const uint8_t *wp = args.B + ((size_t)tile * args.b_kblocks_total + ks) * kI4CxBlockBytes + r_blk * 64u + pos * 16u;
+    constexpr size_t kWStep = (size_t)S * kI4CxBlockBytes;
+    uint4 w[CH];
+    auto load_chunk = [&](uint32_t t0) {
 #pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) {
-            const uint32_t kb = base + kg + 8u * i;
-            if (kb < KB) {
-                const uint8_t *p = wbase + (size_t)kb * kI4CxBlockBytes;
-#pragma unroll
-                for (uint32_t seg = 0; seg < 4; ++seg) w[i * 4 + seg] = ldg_stream(p + ((seg ^ swz) << 4));
-            } else {
-#pragma unroll
-                for (uint32_t seg = 0; seg < 4; ++seg) w[i * 4 + seg] = make_uint4(0, 0, 0, 0);
-            }
-        }
+        for (uint32_t i = 0; i < CH; ++i)
+            w[i] = (t0 + i < T) ? ldg_stream(wp + (size_t)(t0 + i) * kWStep) : make_uint4(0, 0, 0, 0);
     };
-    load_round(0, wcur);
-    if (dbg) ts[1] = gtime_ns();
+    load_chunk(0);
     // weights are static; everything else may have been produced by the preceding kernel
     if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (dbg) ts[2] = gtime_ns();
 
-    int32_t acc[MR], acc2[MR];
+    int32_t acc[MR];
 #pragma unroll
-    for (int i = 0; i < MR; ++i) acc[i] = acc2[i] = 0;
-    int32_t rs16 = 0;   // 16 * sum of q over this thread's K blocks
+    for (int i = 0; i < MR; ++i) acc[i] = 0;
+    int32_t rs16 = 0;   // 16 * sum of q over this thread's share
 
-    for (uint32_t base = 0; base < KB; base += kGemvRoundKB) {
-        const uint32_t cnt = min(kGemvRoundKB, KB - base);
-        if (base) __syncthreads();   // previous round's activations are no longer needed
-        for (uint32_t i = tid; i < cnt * MR * 8u; i += kGemvThreads) {
-            const uint32_t c = i & 7u, row = (i >> 3) % MR, kbl = (i >> 3) / MR;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (row < args.m)
-                v = __ldg(reinterpret_cast<const uint4 *>(args.A + (size_t)(base + kbl) * kI8BlockBytes +
-                                                          sw128_byte(row, c * 16u)));
-            *reinterpret_cast<uint4 *>(sAct + kbl * kActStride + row * 128u + c * 16u) = v;
-        }
-        if (base) load_round(base, wcur);
-        __syncthreads();
-        if (dbg && base == 0) ts[3] = gtime_ns();
+    // activation words of row mi for this thread's segment: 16-byte chunks 2*seg and 2*seg+1 of the
+    // swizzled row; chunk c of row mi sits at mi*128 + ((c ^ mi) << 4)
+    const uint8_t *ap = args.A + (size_t)ks * kI8BlockBytes;
+    constexpr size_t kAStep = (size_t)S * kI8BlockBytes;
+
+    for (uint32_t t0 = 0; t0 < T; t0 += CH) {
 #pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) {
-            const uint32_t s = kg + 8u * i;
-            if (s < cnt) {
-                const uint8_t *act = sAct + s * kActStride;
+        for (uint32_t i = 0; i < CH; ++i) {
+            if (t0 + i < T) {
+                const uint8_t *act = ap + (size_t)(t0 + i) * kAStep;
+                const uint32_t ws[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+                uint32_t lo[4], hi[4];
 #pragma unroll
-                for (uint32_t seg = 0; seg < 4; ++seg) {
-                    const uint4 w = wcur[i * 4 + seg];
-                    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
-                    uint32_t lo[4], hi[4];
+                for (int j = 0; j < 4; ++j) {
+                    lo[j] = (ws[j] << 4) & 0xF0F0F0F0u;   // 16*q for k = 32*seg + 4j .. +3
+                    hi[j] = ws[j] & 0xF0F0F0F0u;          // 16*q for k = 32*seg + 16 + 4j .. +3
+                    rs16 = __dp4a((int)lo[j], 0x01010101, rs16);
+                    rs16 = __dp4a((int)hi[j], 0x01010101, rs16);
+                }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        lo[j] = (ws[j] << 4) & 0xF0F0F0F0u;   // 16*q for k = 32*seg + 4j .. +3
-                        hi[j] = ws[j] & 0xF0F0F0F0u;          // 16*q for k = 32*seg + 16 + 4j .. +3
-                        rs16 = __dp4a((int)lo[j], 0x01010101, rs16);
-                        rs16 = __dp4a((int)hi[j], 0x01010101, rs16);
-                    }
-#pragma unroll
-                    for (int mi = 0; mi < MR; ++mi) {
-                        const uint4 a0 = *reinterpret_cast<const uint4 *>(act + mi * 128u + seg * 32u);
-                        const uint4 a1 = *reinterpret_cast<const uint4 *>(act + mi * 128u + seg * 32u + 16u);
+                for (int mi = 0; mi < MR; ++mi) {
+                    if ((uint32_t)mi < args.m) {
+                        const uint4 a0 = __ldg(reinterpret_cast<const uint4 *>(act + sw128_byte((uint32_t)mi, seg * 32u)));
+                        const uint4 a1 = __ldg(reinterpret_cast<const uint4 *>(act + sw128_byte((uint32_t)mi, seg * 32u + 16u)));
                         const uint32_t al[4] = {a0.x, a0.y, a0.z, a0.w};
                         const uint32_t ah[4] = {a1.x, a1.y, a1.z, a1.w};
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             acc[mi] = __dp4a((int)al[j], (int)lo[j], acc[mi]);
-                            acc2[mi] = __dp4a((int)ah[j], (int)hi[j], acc2[mi]);
+                            acc[mi] = __dp4a((int)ah[j], (int)hi[j], acc[mi]);
                         }
                     }
                 }
             }
         }
+        if (t0 + CH < T) load_chunk(t0 + CH);
     }
 
-    // combine the eight K groups of each row (lanes that differ in their low three bits)
+    // combine the four segments of each row (lanes that differ in their low two bits) ...
 #pragma unroll
     for (int mi = 0; mi < MR; ++mi) {
-        int32_t v = acc[mi] + acc2[mi];
+        int32_t v = acc[mi];
         v += __shfl_xor_sync(0xffffffffu, v, 1);
         v += __shfl_xor_sync(0xffffffffu, v, 2);
-        v += __shfl_xor_sync(0xffffffffu, v, 4);
         acc[mi] = v;
     }
     rs16 += __shfl_xor_sync(0xffffffffu, rs16, 1);
     rs16 += __shfl_xor_sync(0xffffffffu, rs16, 2);
-    rs16 += __shfl_xor_sync(0xffffffffu, rs16, 4);
-    if (dbg) {
-        ts[4] = gtime_ns();
-        for (int i = 0; i < 5; ++i) args.dbg[(size_t)blockIdx.x * 16 + i] = ts[i];
+    // ... and the eight warps through shared memory
+    if (ks > 0 && pos == 0) {
+        int32_t *dst = sRed + ((ks - 1) * kGemvWarpRows + rr) * (MR + 1);
+#pragma unroll
+        for (int mi = 0; mi < MR; ++mi) dst[mi] = acc[mi];
+        dst[MR] = rs16;
     }
+    __syncthreads();
 
-    const uint32_t n = tile * 128u + r_blk;
-    if (kg == 0 && n < args.n) {
+    const uint32_t n = row0 + rr;
+    if (ks == 0 && pos == 0 && n < args.n) {
+#pragma unroll
+        for (uint32_t s2 = 1; s2 < S; ++s2) {
+            const int32_t *src = sRed + ((s2 - 1) * kGemvWarpRows + rr) * (MR + 1);
+#pragma unroll
+            for (int mi = 0; mi < MR; ++mi) acc[mi] += src[mi];
+            rs16 += src[MR];
+        }
         const int32_t rs = rs16 >> 4;
         const float sb = args.scale_b[n];
         const float bv = args.bias ? TdTraits<TD>::load(args.bias, n) : 0.0f;
@@ -203,11 +190,11 @@ static bool pdl_enabled()
 }
 
 template <int MR, Dtype TD>
-static Result launch_gemv_t(GemvArgs a, uint32_t ctas, cudaStream_t st)
+static Result launch_gemv_t(GemvArgs a, cudaStream_t st)
 {
     a.pdl = pdl_enabled() ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ctas, 1, 1);
+    cfg.gridDim = dim3((a.n + kGemvWarpRows - 1) / kGemvWarpRows, 1, 1);   // CTA c owns columns [8c, 8c + 8)
     cfg.blockDim = dim3(kGemvThreads, 1, 1);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
@@ -222,12 +209,12 @@ static Result launch_gemv_t(GemvArgs a, uint32_t ctas, cudaStream_t st)
 }
 
 template <Dtype TD>
-static Result launch_gemv_m(const GemvArgs &a, uint32_t ctas, cudaStream_t st)
+static Result launch_gemv_m(const GemvArgs &a, cudaStream_t st)
 {
-    if (a.m <= 1) return launch_gemv_t<1, TD>(a, ctas, st);
-    if (a.m <= 2) return launch_gemv_t<2, TD>(a, ctas, st);
-    if (a.m <= 4) return launch_gemv_t<4, TD>(a, ctas, st);
-    return launch_gemv_t<8, TD>(a, ctas, st);
+    if (a.m <= 1) return launch_gemv_t<1, TD>(a, st);
+    if (a.m <= 2) return launch_gemv_t<2, TD>(a, st);
+    if (a.m <= 4) return launch_gemv_t<4, TD>(a, st);
+    return launch_gemv_t<8, TD>(a, st);
 }
 
 Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
@@ -252,13 +239,11 @@ Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin,
     a.scale_b = p.scale_b;
     a.cmin = cmin;
     a.cmax = cmax;
-    a.dbg = timing_buffer();
-    const uint32_t ctas = (uint32_t)ceil_div(g.n, kGemvRows);   // CTA c owns columns [32c, 32c + 32)
     cudaStream_t st = (cudaStream_t)g.stream;
     switch (td) {
-        case Dtype::F32: return launch_gemv_m<Dtype::F32>(a, ctas, st);
-        case Dtype::F16: return launch_gemv_m<Dtype::F16>(a, ctas, st);
-        default: return launch_gemv_m<Dtype::BF16>(a, ctas, st);
+        case Dtype::F32: return launch_gemv_m<Dtype::F32>(a, st);
+        case Dtype::F16: return launch_gemv_m<Dtype::F16>(a, st);
+        default: return launch_gemv_m<Dtype::BF16>(a, st);
     }
 }
 
