@@ -42,7 +42,6 @@ CONFIGS = {
     "c4": (4096, 4096, 4096, "gemm_1xnbias_reqi32toi8_clamp_qai8_qai8p_qsi8cxp M=K=N=4096 (static W8A8, int8 out)"),
     "c5": (8192, 8192, 28672, "gemm_1xnbias_clamp_f16_f16p_qsi4c2p M=8192 K=8192 N=28672 bl=32 (Llama-3-70B MLP)"),
 }
-GEMV_BYTES = 4096 * 4096 // 2 + 3 * 4 * 4096 + 4096 + 8   # weights + scale_b, bias, D + int8 row + (scale, zp)
 
 
 def measured_peaks():
@@ -315,6 +314,11 @@ def run_ours(args):
     decode = None
     if cfg == "c3" and rank == 0 and not args.no_decode:
         decode = bench_decode(torch, lin, pkg, dev, peaks)
+        decode["other_shapes"] = []
+        for (K2, N2, c2) in ((4096, 14336, 16), (8192, 28672, 6)):   # the prefill configs' weight shapes at M=1
+            d2 = bench_decode(torch, lin, pkg, dev, peaks, K=K2, N=N2, copies=c2)
+            decode["other_shapes"].append({"workload": d2["workload"], "gbs": d2["value"], "us_per_gemv": d2["us_per_gemv"],
+                                           "frac": d2["roofline"]["frac"], "read_ceiling_gbs": d2["read_ceiling"]["gbs"]})
 
     if rank != 0:
         if world > 1:
@@ -362,10 +366,32 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def bench_decode(torch, lin, pkg, dev, peaks, copies=48, reps=20):
-    """GEMV M=1, K=N=4096 f32: one CUDA graph replays `copies` GEMVs over distinct weight sets
-    (48 x 8.65 MB > L2), so every launch streams its weights from HBM."""
-    K = N = 4096
+def _graph_time_us(torch, stream, launch_all, launches, reps):
+    """Capture `launch_all` (which issues `launches` kernels) in a CUDA graph and return us per kernel."""
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        launch_all()
+        stream.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            launch_all()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * launches)
+
+
+def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20):
+    """GEMV M=1 f32: one CUDA graph replays `copies` GEMVs over distinct weight sets (together larger
+    than L2), so every launch streams its weights from HBM.  `read_ceiling` is a kernel with the same
+    launch shape that only reads the same number of bytes from the same buffers, timed the same way."""
+    import ctypes
+    nbytes = N * K // 2 + 3 * 4 * N + K + 8   # weights + scale_b, bias, D + int8 row + (scale, zp)
     gen = torch.Generator(device=dev)
     gen.manual_seed(7)
     layers = []
@@ -379,28 +405,30 @@ def bench_decode(torch, lin, pkg, dev, peaks, copies=48, reps=20):
         L.gemm(1)
     torch.cuda.synchronize()
     stream = torch.cuda.Stream()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
+
+    def gemvs():
         for L in layers:
             L.gemm(1)
-        stream.synchronize()
-        with torch.cuda.graph(graph, stream=stream):
-            for L in layers:
-                L.gemm(1)
-    for _ in range(3):
-        graph.replay()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1e3 / (reps * copies)
-    gbs = GEMV_BYTES / (us * 1e-6) / 1e9
+
+    us = _graph_time_us(torch, stream, gemvs, copies, reps)
+    lib = pkg.lib()
+    lib.tqt_cuda_debug_stream_read.argtypes = [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+    lib.tqt_cuda_debug_stream_read.restype = None
+    rd = nbytes // 16 * 16
+
+    def reads():
+        pkg.set_stream(torch.cuda.current_stream().cuda_stream)
+        for L in layers:
+            lib.tqt_cuda_debug_stream_read(L.b_packed.data_ptr(), rd, None)
+
+    us_read = _graph_time_us(torch, stream, reads, copies, reps)
+    pkg.set_stream(torch.cuda.current_stream().cuda_stream)
+    gbs = nbytes / (us * 1e-6) / 1e9
     return {"metric": "w4a8_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "us_per_gemv": us,
-            "workload": "gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp decode M=1 K=4096 N=4096",
-            "bytes_per_gemv": GEMV_BYTES, "gpu_launches": reps * copies,
+            "workload": f"gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp decode M=1 K={K} N={N}",
+            "bytes_per_gemv": nbytes, "gpu_launches": reps * copies,
+            "read_ceiling": {"gbs": rd / (us_read * 1e-6) / 1e9, "us": us_read,
+                             "note": "a kernel with the GEMV's launch shape that only reads the same bytes, same graph"},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm"], "traffic": None,
                          "note": f"CUDA-graph replay of {copies} back-to-back GEMVs over distinct weights; peak = hbm_gbs of {peaks['source']}"}}
@@ -409,7 +437,7 @@ def bench_decode(torch, lin, pkg, dev, peaks, copies=48, reps=20):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=40)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))

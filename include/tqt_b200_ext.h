@@ -67,6 +67,12 @@ int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k);
  * epilogue warp, one converter warp: {wait0, wait1, wait2, total} each).  NULL switches it off. */
 void tqt_cuda_debug_set_timing_buffer(void *dev_ptr);
 
+/* Diagnostic: launch, on the calling thread's stream, a kernel with the GEMV's launch shape (thread
+ * count, loads in flight, programmatic dependent launch) that only reads `bytes` bytes from the
+ * device buffer src (16-byte aligned) and computes nothing: the read ceiling the GEMV's achieved
+ * bandwidth is compared with at a given size.  sink: 128 bytes of device memory, or NULL. */
+void tqt_cuda_debug_stream_read(const void *src, size_t bytes, void *sink);
+
 #if !defined(TQT_B200_NO_HALF_TYPES)
 /* Return the bit pattern of a 16-bit float received by value: lets a foreign-function binding
  * verify how it passes the clamp arguments of the f16 / bf16 kernel types. */

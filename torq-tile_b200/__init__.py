@@ -348,7 +348,8 @@ def bt_unpack_qsi4c2p(n, k, B_packed, ldb_packed, B, ldb):
 EXTENSION_SYMBOLS = (
     ["tqt_cuda_set_stream", "tqt_cuda_get_stream", "tqt_cuda_get_last_status", "tqt_cuda_get_last_cuda_error",
      "tqt_cuda_read_device_fault", "tqt_cuda_version", "tqt_shard_plan_n", "tqt_cuda_kernel_choice_w4a8",
-     "tqt_cuda_debug_f16_bits", "tqt_cuda_debug_bf16_bits", "tqt_cuda_debug_set_timing_buffer"]
+     "tqt_cuda_debug_f16_bits", "tqt_cuda_debug_bf16_bits", "tqt_cuda_debug_set_timing_buffer",
+     "tqt_cuda_debug_stream_read"]
     + [f"tqt_run_quant_pack_qai8dxp_{t}_{VARIANT}" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_quant_qai8dx_{t}_sm100a" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_{n}_{VARIANT}" for n in ("a_unpack_i8", "a_unpack_f16", "bt_unpack_qsi4cxp", "bt_unpack_qsi4c2p")]

@@ -98,6 +98,9 @@ int read_device_fault(void *stream);
 // (nullptr switches it off).  Owned by the caller.
 void set_timing_buffer(void *dev_ptr);
 
+// Diagnostic: launch a kernel with the GEMV's launch shape that only reads `bytes` from src (16-byte aligned).
+Result stream_read(const void *src, size_t bytes, void *sink, void *stream);
+
 // Path override from the environment (TQT_B200_PATH = auto|umma|gemv|simt), for tests.
 Path env_path();
 
