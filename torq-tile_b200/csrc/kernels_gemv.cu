@@ -1,23 +1,29 @@
 // HBM-streaming W4A8 GEMV for decode (m <= 8; more rows run on the tensor-core kernel): no tensor
 // cores, no clusters, no shared-memory staging of weights, no scratch memory.
 //
-// A CTA owns 8 consecutive output columns (8 rows of one 128-row block tile of B_packed); its eight
-// warps take interleaved K blocks.  Inside a warp lane = (row, 16-byte segment), so one warp-wide
-// 128-bit load covers 512 contiguous bytes of a packed block (every 32-byte sector is used whole,
-// once).  A thread holds eight loads at a time and few registers, so eight CTAs (32 warps) are
-// resident per SM and two to three successive GEMVs fit on the GPU together: on this part a streaming read reaches full bandwidth with many warps
-// that each have a few loads outstanding, not with few warps that have many (measured: 148 x 2
-// CTAs with 8 loads per thread reach 5.5 TB/s on 117 MB, 148 x 4 CTAs with 4 loads 6.4 TB/s).
+// A CTA owns 8 consecutive output columns (8 rows of one 128-row block tile of B_packed) and loops
+// over such groups when there are more groups than resident CTAs; its eight warps take interleaved
+// K blocks.  Inside a warp lane = (row, 16-byte segment), so one warp-wide 128-bit load covers 512
+// contiguous bytes of a packed block: every 32-byte sector is used whole, once.  A thread holds four
+// weight loads at a time (64 registers in all), so four CTAs (32 warps) are resident per SM: on this
+// part a streaming read reaches full bandwidth with many warps that each have a few loads
+// outstanding, not with few warps that have many.  The next group's (or round's) loads are issued
+// as soon as the registers are free, before the current group is combined and stored.
 // Nibbles are expanded with two logic ops per 8 weights (operands 16*q, as in the tensor-core
-// kernel) and accumulated with dp4a against activation words read through L1 (a few KiB, always
-// resident; weights bypass L1).  The four segments of a row are combined with warp shuffles and the
-// eight warps through shared memory: integer sums, so the result is exact and independent of the
-// split.  The epilogue is the GEMM's (reference:
+// kernel) and accumulated with dp4a; the zero-point correction uses the int16 partial row sums
+// stored at the tail of every packed block.  The four segments of a row are combined with warp
+// shuffles and the eight warps through shared memory: integer sums, so the result is exact and
+// independent of the split.  The epilogue is the GEMM's (reference:
 // src/gemm/gemm_i8_i4/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp/..._4x1vl_rvv.cpp:118-177).
 //
 // Programmatic dependent launch: the kernel lets its successor start at once and requests its
-// weights before waiting for its predecessor, so back-to-back GEMVs (the layers of a decode step)
-// overlap their memory phases; activations, C and D are touched only after the wait.
+// weights and per-column constants before waiting for its predecessor, so back-to-back GEMVs (the
+// layers of a decode step) overlap their memory phases.  Everything after that wait is on the
+// critical path of the chain (a kernel's wait ends only when its predecessor has completed), so it
+// is kept short: the activation words of a whole chunk are requested together, straight into
+// registers (staging them in shared memory, or fetching the weights with bulk copies to make room
+// for more resident kernels, both measured slower).  Activations, C and D are touched only after
+// the wait.
 // TQT_B200_PDL=0 switches this off.
 #include <cstdlib>
 
