@@ -160,3 +160,45 @@ def test_quantiser_strided_rows(oracle):
     p.quant_qai8dx(a_dev, q, s, z)
     sync_and_check()
     assert np.array_equal(q.cpu().numpy(), q_o) and np.array_equal(z.cpu().numpy(), z_o)
+
+
+@pytest.mark.parametrize("ta", ["f16", "bf16"])
+@pytest.mark.parametrize("m,k", [(256, 4096), (40, 1024), (33, 16), (128, 4080)])
+def test_quantiser_rows_in_registers_exact_division(oracle, m, k, ta):
+    """Many 16-bit rows with k <= 4096 take the warp-per-row kernel, which divides by the row scale
+    through a corrected reciprocal.  Values are planted next to the rounding boundaries (quotients
+    near j + 0.5) and at the extremes of the row; every byte must still equal the reference's
+    round(x / scale) + zero point."""
+    p = pkg()
+    p.use_current_torch_stream()
+    rng = np.random.default_rng(k * 7 + m)
+    tt = torch.float16 if ta == "f16" else torch.bfloat16
+    A = rng.normal(0, 1, (m, k)).astype(np.float32)
+    A[:, 0] = rng.uniform(-6, -2, m)      # row minimum
+    A[:, 1] = rng.uniform(2, 6, m)        # row maximum
+    scale = (A[:, 1] - A[:, 0]) / 255.0
+    half = rng.integers(-100, 100, (m, k)).astype(np.float32) + 0.5
+    plant = rng.random((m, k)) < 0.5
+    plant[:, :2] = False
+    A = np.where(plant, np.clip(half * scale[:, None], A[:, :1], A[:, 1:2]), A)
+    if m > 2:
+        A[2] = 0.0
+    a_dev = torch.from_numpy(A).to(DEV).to(tt)
+    q_o, s_o, z_o = oracle.quantize_a_per_row_asym(bits16(a_dev), TD_F16 if ta == "f16" else TD_BF16)
+    q = torch.full((m, k), 77, dtype=torch.int8, device=DEV)
+    s = torch.zeros(m, dtype=torch.float32, device=DEV)
+    z = torch.zeros(m, dtype=torch.int32, device=DEV)
+    p.quant_qai8dx(a_dev, q, s, z)
+    sync_and_check()
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), s_o.view(np.uint32))
+    assert np.array_equal(z.cpu().numpy(), z_o)
+    assert np.array_equal(q.cpu().numpy(), q_o)
+    uk = p.GemmW4A8("f32")
+    packed = torch.full((uk.get_a_packed_size(m, k),), 0x33, dtype=torch.uint8, device=DEV)
+    s2, z2 = torch.zeros_like(s), torch.zeros_like(z)
+    p.quant_pack_qai8dxp(a_dev, packed, s2, z2)
+    back = torch.zeros((m, k), dtype=torch.int8, device=DEV)
+    p.a_unpack_i8(m, k, packed, k, back, k)
+    sync_and_check()
+    assert np.array_equal(back.cpu().numpy(), q_o)
+    assert np.array_equal(s2.cpu().numpy().view(np.uint32), s_o.view(np.uint32))

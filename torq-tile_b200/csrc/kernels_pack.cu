@@ -399,6 +399,120 @@ __global__ void __launch_bounds__(256) quant_qai8dx_kernel(size_t m, size_t k, c
     }
 }
 
+// Warp-per-row variant for 16-bit inputs whose rows fit in registers (k <= 4096, k a multiple of 16,
+// 16-byte aligned rows): no block-wide synchronisation, 16 loads of 16 bytes in flight per lane, every
+// row read exactly once.  The per-element division x / s is done as Markstein's correction of
+// x * RN(1/s) (q0 = x*y; e = x - q0*s exactly, by fma; q = q0 + e*y): with y the correctly rounded
+// reciprocal this is the correctly rounded quotient, i.e. bit-identical to the IEEE division the
+// reference performs (test/common/test_common.h:232-240), at three operations per element.
+template <Dtype TA, bool PACKED>
+__global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t k, const void *__restrict__ A, size_t lda,
+                                                                uint8_t *__restrict__ out, size_t ldq, size_t kblocks_total,
+                                                                float *__restrict__ scale_a, int32_t *__restrict__ zp_a)
+{
+    static_assert(TA != Dtype::F32, "16-bit inputs only");
+    const uint32_t lane = threadIdx.x & 31u;
+    const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= m) return;
+    const uint32_t nchunks = (uint32_t)(k / 16);   // 16-element chunks of the row; chunk c belongs to lane c % 32
+    const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(A) + row * lda);
+    uint4 raw[8][2];
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        const uint32_t c = lane + 32u * i;
+        if (c < nchunks) {
+            raw[i][0] = __ldg(src + 2 * c);
+            raw[i][1] = __ldg(src + 2 * c + 1);
+        } else {
+            raw[i][0] = raw[i][1] = make_uint4(0, 0, 0, 0);
+        }
+    }
+    auto widen = [](uint32_t w, float &lo, float &hi) {
+        if (TA == Dtype::F16) {
+            const __half2 h = *reinterpret_cast<const __half2 *>(&w);
+            lo = __low2float(h);
+            hi = __high2float(h);
+        } else {
+            lo = __uint_as_float(w << 16);
+            hi = __uint_as_float(w & 0xffff0000u);
+        }
+    };
+    float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        if (lane + 32u * i < nchunks) {
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t w[4] = {raw[i][h].x, raw[i][h].y, raw[i][h].z, raw[i][h].w};
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    float lo, hi;
+                    widen(w[j], lo, hi);
+                    vmin = lo < vmin ? lo : vmin;
+                    vmax = lo > vmax ? lo : vmax;
+                    vmin = hi < vmin ? hi : vmin;
+                    vmax = hi > vmax ? hi : vmax;
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        vmin = fminf(vmin, __shfl_xor_sync(0xffffffffu, vmin, o));
+        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    }
+    vmax = vmax > 0.0f ? vmax : 0.0f;
+    vmin = vmin < 0.0f ? vmin : 0.0f;
+    const float s = __fdiv_rn(__fsub_rn(vmax, vmin), 255.0f);
+    int zp = 0;
+    if (s != 0.0f) {
+        zp = (int)rintf(__fsub_rn(-128.0f, __fdiv_rn(vmin, s)));
+        zp = zp < -128 ? -128 : (zp > 127 ? 127 : zp);
+    }
+    if (lane == 0) {
+        scale_a[row] = s != 0.0f ? s : 1.0f;
+        zp_a[row] = zp;
+    }
+    const float y = s != 0.0f ? __frcp_rn(s) : 0.0f;
+    const size_t tile = row >> 7;
+    const uint32_t r = (uint32_t)(row & 127);
+    const uint32_t out_chunks = PACKED ? (uint32_t)((k + 127) / 128) * 8u : nchunks;   // packed rows are zero-padded to the block width
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        const uint32_t c = lane + 32u * i;
+        if (c >= out_chunks) continue;
+        uint32_t packed[4] = {0, 0, 0, 0};
+        if (c < nchunks && s != 0.0f) {
+#pragma unroll
+            for (uint32_t h = 0; h < 2; ++h) {
+                const uint32_t w[4] = {raw[i][h].x, raw[i][h].y, raw[i][h].z, raw[i][h].w};
+#pragma unroll
+                for (uint32_t j = 0; j < 4; ++j) {
+                    float x2[2];
+                    widen(w[j], x2[0], x2[1]);
+#pragma unroll
+                    for (uint32_t e2 = 0; e2 < 2; ++e2) {
+                        const float q0 = __fmul_rn(x2[e2], y);
+                        const float err = __fmaf_rn(-q0, s, x2[e2]);
+                        const float q = __fmaf_rn(err, y, q0);
+                        int v = __float2int_rn(q) + zp;
+                        v = v > 127 ? 127 : (v < -128 ? -128 : v);
+                        const uint32_t idx = h * 8u + j * 2u + e2;   // element inside the chunk
+                        packed[idx >> 2] |= ((uint32_t)v & 0xffu) << ((idx & 3u) * 8u);
+                    }
+                }
+            }
+        }
+        const uint4 q4 = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        if (PACKED) {
+            uint8_t *base = out + (tile * kblocks_total + (c >> 3)) * kI8BlockBytes;
+            *reinterpret_cast<uint4 *>(base + sw128_byte(r, (c & 7u) * 16u)) = q4;
+        } else {
+            *reinterpret_cast<uint4 *>(out + row * ldq + (size_t)c * 16u) = q4;
+        }
+    }
+}
+
 Result launch_quant_qai8dx(void *stream, size_t m, size_t k, const void *A, size_t lda, Dtype ta, void *out,
                            size_t ldq, bool packed, float *scale_a, int32_t *zp_a)
 {
@@ -408,6 +522,26 @@ Result launch_quant_qai8dx(void *stream, size_t m, size_t k, const void *A, size
     const unsigned grid = (unsigned)m;
     const size_t kbt = ceil_div(k, 128);
     uint8_t *o = (uint8_t *)out;
+    // many 16-bit rows that fit in registers: one warp per row
+    const bool warp_rows = ta != Dtype::F32 && m >= 32 && k <= 4096 && k % 16 == 0 && lda % 8 == 0 &&
+                           (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+                           (packed || (ldq % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0));
+    if (warp_rows) {
+        const unsigned wgrid = (unsigned)((m + 7) / 8);
+#define TQT_LAUNCH_QW(TA_)                                                                                             \
+    do {                                                                                                               \
+        if (packed)                                                                                                    \
+            quant_qai8dx_warp_kernel<TA_, true><<<wgrid, 256, 0, st>>>(m, k, A, lda, o, ldq, kbt, scale_a, zp_a);      \
+        else                                                                                                           \
+            quant_qai8dx_warp_kernel<TA_, false><<<wgrid, 256, 0, st>>>(m, k, A, lda, o, ldq, kbt, scale_a, zp_a);     \
+    } while (0)
+        if (ta == Dtype::F16)
+            TQT_LAUNCH_QW(Dtype::F16);
+        else
+            TQT_LAUNCH_QW(Dtype::BF16);
+#undef TQT_LAUNCH_QW
+        return check_launch();
+    }
 #define TQT_LAUNCH_Q(TA_)                                                                                              \
     do {                                                                                                               \
         if (packed)                                                                                                    \

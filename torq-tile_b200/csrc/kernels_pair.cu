@@ -24,6 +24,8 @@
 // waits are bounded; teardown is a hardware cluster barrier that every path reaches.
 //
 // Reference semantics of the epilogues: see kernels_umma.cu.
+#include <cstdlib>
+
 #include "epilogues.cuh"
 #include "ptx_sm100.cuh"
 #include "umma_args.cuh"
@@ -834,7 +836,12 @@ static Result launch_grid(Kern kern, const UmmaArgs &a, uint32_t num_tiles, bool
         if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
         attr_set[dev] = true;
     }
-    const uint32_t sms = (uint32_t)sm_count_cached();
+    uint32_t sms = (uint32_t)sm_count_cached();
+    static const int sm_limit = [] {   // diagnostic: run on fewer SMs (TQT_B200_SM_LIMIT), e.g. to separate per-SM from shared limits
+        const char *e = std::getenv("TQT_B200_SM_LIMIT");
+        return e ? std::atoi(e) : 0;
+    }();
+    if (sm_limit > 1 && (uint32_t)sm_limit < sms) sms = (uint32_t)sm_limit;
     uint32_t grid;
     if (pair) {
         const uint32_t max_pairs = sms / 2;

@@ -17,7 +17,92 @@ _TORCH_TD = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 FLT_MAX = 3.4028234663852886e38
 
 
-class W4A8Linear:
+class _HostPipelined:
+    """Host-memory entry point shared by the operators: ``forward_host(a_host, out_host)``.
+
+    The rows of A are processed in chunks on three streams (host->device copy, prepare + run_gemm,
+    device->host copy), so the copies of one chunk overlap the kernels and the opposite-direction
+    copies of its neighbours; PCIe is full duplex.  Stream-ordered like any asynchronous torch
+    operation: the call returns once everything is enqueued, and the calling stream waits for the
+    last copy, so ``torch.cuda.current_stream().synchronize()`` (or an event) completes the call.
+    Both host tensors must be pinned.  ``prepare`` is the operator's quantise+pack or pack step.
+    """
+
+    def _pipe(self, m, chunks, in_dtype):
+        key = ("pipe", m, chunks)
+        st = self._ws.get(key)
+        if st is None:
+            dev = self.b_packed.device
+            rows = -(-m // chunks)
+            rows = -(-rows // 128) * 128   # whole row tiles per chunk
+            bounds = [(r0, min(m, r0 + rows)) for r0 in range(0, m, rows)]
+            st = dict(bounds=bounds,
+                      a_dev=torch.empty((m, self.k), dtype=in_dtype, device=dev),
+                      out_dev=torch.empty((m, self.n), dtype=self.out_dtype, device=dev),
+                      s_in=torch.cuda.Stream(dev), s_run=torch.cuda.Stream(dev), s_out=torch.cuda.Stream(dev),
+                      used=False)
+            for mode in ("eager", "capture"):   # events recorded during a graph capture belong to that graph
+                st[mode] = {name: [torch.cuda.Event() for _ in bounds] for name in ("loaded", "consumed", "computed", "copied")}
+            self._ws[key] = st
+        return st
+
+    def _enqueue(self, a_host, out_host, st, cross_call):
+        cur = torch.cuda.current_stream()
+        st["s_in"].wait_stream(cur)
+        st["s_run"].wait_stream(cur)
+        st["s_out"].wait_stream(cur)
+        chained = cross_call and st["used"]
+        ev = st["eager" if cross_call else "capture"]
+        for c, (r0, r1) in enumerate(st["bounds"]):
+            with torch.cuda.stream(st["s_in"]):
+                if chained:
+                    st["s_in"].wait_event(ev["consumed"][c])   # the previous call has read this chunk
+                st["a_dev"][r0:r1].copy_(a_host[r0:r1], non_blocking=True)
+                ev["loaded"][c].record()
+            with torch.cuda.stream(st["s_run"]):
+                st["s_run"].wait_event(ev["loaded"][c])
+                if chained:
+                    st["s_run"].wait_event(ev["copied"][c])    # the previous call's result has left the device
+                self.prepare(st["a_dev"][r0:r1])
+                ev["consumed"][c].record()
+                self.gemm(r1 - r0, out=st["out_dev"][r0:r1])
+                ev["computed"][c].record()
+            with torch.cuda.stream(st["s_out"]):
+                st["s_out"].wait_event(ev["computed"][c])
+                out_host[r0:r1].copy_(st["out_dev"][r0:r1], non_blocking=True)
+                ev["copied"][c].record()
+        if cross_call:
+            st["used"] = True
+        cur.wait_stream(st["s_out"])
+
+    def forward_host(self, a_host, out_host, chunks=4, graph=True):
+        """a_host [m, k] (pinned) -> out_host [m, n] (pinned).  With ``graph`` (default) the enqueued
+        copies and kernels of a given (a_host, out_host) pair are captured once in a CUDA graph and
+        replayed on later calls, which takes the per-chunk launch overhead off the host; the two
+        tensors must then stay alive and in place for as long as the operator is used with them."""
+        m = a_host.shape[0]
+        st = self._pipe(m, chunks, a_host.dtype)
+        if not graph:
+            self._enqueue(a_host, out_host, st, cross_call=True)
+            return out_host
+        key = ("graph", a_host.data_ptr(), out_host.data_ptr(), m, chunks)
+        g = self._ws.get(key)
+        if g is None:
+            self._enqueue(a_host, out_host, st, cross_call=True)   # allocates the workspaces; delivers this call
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._enqueue(a_host, out_host, st, cross_call=False)
+            stale = [k2 for k2 in self._ws if isinstance(k2, tuple) and k2[0] == "graph"]
+            for k2 in stale[:-7]:   # keep a handful of captured pairs
+                del self._ws[k2]
+            self._ws[key] = g
+            return out_host
+        g.replay()
+        return out_host
+
+
+class W4A8Linear(_HostPipelined):
     """D = clamp(dequant(quant(A)) * dequant(W)^T + bias): qai8dxp x qsi4cxp, float output.
 
     ``nib`` is the [n, k/2] uint8 weight in the reference's encoding (low nibble = even k, value
@@ -27,7 +112,7 @@ class W4A8Linear:
 
     def __init__(self, nib, scale_b, k, out_dtype="bf16", bias=None, clamp=None):
         self.uk = GemmW4A8(out_dtype)
-        self.td = _TORCH_TD[out_dtype]
+        self.td = self.out_dtype = _TORCH_TD[out_dtype]
         self.n, self.k = nib.shape[0], k
         dev = nib.device
         use_current_torch_stream()
@@ -59,25 +144,30 @@ class W4A8Linear:
         quant_pack_qai8dxp(A, ws["a_packed"], ws["scale_a"], ws["zp_a"])
         return ws
 
-    def gemm(self, m, Cm=None):
-        """run_gemm on the workspace of size m (after quantize()); returns the output tensor."""
+    def gemm(self, m, Cm=None, out=None):
+        """run_gemm on the workspace of size m (after quantize()); returns the output tensor
+        (the workspace's, or ``out`` [m, n] with any row stride)."""
         ws = self.workspace(m)
+        out = ws["out"] if out is None else out
         use_current_torch_stream()
-        self.uk.run_gemm(m, self.n, self.k, ws["a_packed"], self.k, 0, self.b_packed, self.k, 0, Cm, self.n, ws["out"],
-                         self.n, self.bias, self.clamp[0], self.clamp[1], ws["params"])
-        return ws["out"]
+        self.uk.run_gemm(m, self.n, self.k, ws["a_packed"], self.k, 0, self.b_packed, self.k, 0, Cm, self.n, out,
+                         out.stride(0), self.bias, self.clamp[0], self.clamp[1], ws["params"])
+        return out
+
+    prepare = quantize
 
     def __call__(self, A, Cm=None):
         self.quantize(A)
         return self.gemm(A.shape[0], Cm)
 
 
-class W8A8RequantLinear:
+class W8A8RequantLinear(_HostPipelined):
     """Static W8A8 with int8 output: qai8 x qsi8cxp (weights [n, k] int8), int32 bias with the
     activation zero point already fused (bias - zp_a * sum_k w), as the reference's callers do."""
 
     def __init__(self, w_i8, scale_b, scale_a, zero_point_a, scale_d, zero_point_d, bias_fused=None, clamp=(-128, 127)):
         self.uk = GemmReqI8()
+        self.out_dtype = torch.int8
         self.n, self.k = w_i8.shape
         dev = w_i8.device
         use_current_torch_stream()
@@ -104,24 +194,27 @@ class W8A8RequantLinear:
         self.uk.run_a_pack(A_i8.shape[0], self.k, A_i8.stride(0), self.k, 0, A_i8, ws["a_packed"])
         return ws
 
-    def gemm(self, m, Cm=None):
+    def gemm(self, m, Cm=None, out=None):
         ws = self.workspace(m)
+        out = ws["out"] if out is None else out
         use_current_torch_stream()
-        self.uk.run_gemm(m, self.n, self.k, ws["a_packed"], self.k, 0, self.b_packed, self.k, 0, Cm, self.n, ws["out"],
-                         self.n, self.bias, self.clamp[0], self.clamp[1], self.params)
-        return ws["out"]
+        self.uk.run_gemm(m, self.n, self.k, ws["a_packed"], self.k, 0, self.b_packed, self.k, 0, Cm, self.n, out,
+                         out.stride(0), self.bias, self.clamp[0], self.clamp[1], self.params)
+        return out
+
+    prepare = pack
 
     def __call__(self, A_i8, Cm=None):
         self.pack(A_i8)
         return self.gemm(A_i8.shape[0], Cm)
 
 
-class W4A16Linear:
+class W4A16Linear(_HostPipelined):
     """f16 activations x block-quantised int4 weights (qsi4c2, f16 scale per bl elements of k)."""
 
     def __init__(self, nib, scale_b, k, bl, out_dtype="f16", bias=None, clamp=None):
         self.uk = GemmW4A16(out_dtype)
-        self.td = _TORCH_TD[out_dtype]
+        self.td = self.out_dtype = _TORCH_TD[out_dtype]
         self.n, self.k, self.bl = nib.shape[0], k, bl
         dev = nib.device
         use_current_torch_stream()
@@ -149,12 +242,15 @@ class W4A16Linear:
         self.uk.run_a_pack(A_f16.shape[0], self.k, A_f16.stride(0), self.k, 0, A_f16, ws["a_packed"])
         return ws
 
-    def gemm(self, m, Cm=None):
+    def gemm(self, m, Cm=None, out=None):
         ws = self.workspace(m)
+        out = ws["out"] if out is None else out
         use_current_torch_stream()
         self.uk.run_gemm(m, self.n, self.k, self.bl, ws["a_packed"], self.k, 0, self.b_packed, self.k, 0, self.scale_b,
-                         self.k // self.bl, Cm, self.n, ws["out"], self.n, self.bias, self.clamp[0], self.clamp[1])
-        return ws["out"]
+                         self.k // self.bl, Cm, self.n, out, out.stride(0), self.bias, self.clamp[0], self.clamp[1])
+        return out
+
+    prepare = pack
 
     def __call__(self, A_f16, Cm=None):
         self.pack(A_f16)
