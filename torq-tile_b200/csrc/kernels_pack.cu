@@ -437,7 +437,16 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
             hi = __uint_as_float(w & 0xffff0000u);
         }
     };
-    float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
+    // row minimum / maximum with packed 16-bit min/max (a NaN operand is ignored, as the reference's
+    // comparisons ignore it); lanes without data keep the neutral start values
+    using V2 = typename std::conditional<TA == Dtype::F16, __half2, __nv_bfloat162>::type;
+    auto as_v2 = [](uint32_t w) {
+        V2 v;
+        memcpy(&v, &w, 4);
+        return v;
+    };
+    V2 mn2 = as_v2(raw[0][0].x), mx2 = mn2;
+    bool any = lane < nchunks;
 #pragma unroll
     for (uint32_t i = 0; i < 8; ++i) {
         if (lane + 32u * i < nchunks) {
@@ -446,15 +455,22 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
                 const uint32_t w[4] = {raw[i][h].x, raw[i][h].y, raw[i][h].z, raw[i][h].w};
 #pragma unroll
                 for (uint32_t j = 0; j < 4; ++j) {
-                    float lo, hi;
-                    widen(w[j], lo, hi);
-                    vmin = lo < vmin ? lo : vmin;
-                    vmax = lo > vmax ? lo : vmax;
-                    vmin = hi < vmin ? hi : vmin;
-                    vmax = hi > vmax ? hi : vmax;
+                    mn2 = __hmin2(mn2, as_v2(w[j]));
+                    mx2 = __hmax2(mx2, as_v2(w[j]));
                 }
             }
         }
+    }
+    float vmin = 3.402823466e+38f, vmax = -3.402823466e+38f;
+    if (any) {
+        uint32_t wmn, wmx;
+        memcpy(&wmn, &mn2, 4);
+        memcpy(&wmx, &mx2, 4);
+        float a0, a1, b0, b1;
+        widen(wmn, a0, a1);
+        widen(wmx, b0, b1);
+        vmin = fminf(a0, a1);
+        vmax = fmaxf(b0, b1);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -486,6 +502,7 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
 #pragma unroll
             for (uint32_t h = 0; h < 2; ++h) {
                 const uint32_t w[4] = {raw[i][h].x, raw[i][h].y, raw[i][h].z, raw[i][h].w};
+                int v[8];
 #pragma unroll
                 for (uint32_t j = 0; j < 4; ++j) {
                     float x2[2];
@@ -495,11 +512,16 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
                         const float q0 = __fmul_rn(x2[e2], y);
                         const float err = __fmaf_rn(-q0, s, x2[e2]);
                         const float q = __fmaf_rn(err, y, q0);
-                        int v = __float2int_rn(q) + zp;
-                        v = v > 127 ? 127 : (v < -128 ? -128 : v);
-                        const uint32_t idx = h * 8u + j * 2u + e2;   // element inside the chunk
-                        packed[idx >> 2] |= ((uint32_t)v & 0xffu) << ((idx & 3u) * 8u);
+                        v[j * 2 + e2] = __float2int_rn(q) + zp;
                     }
+                }
+                // saturate to int8 and pack four values per word: element 0 in the lowest byte
+#pragma unroll
+                for (uint32_t g = 0; g < 2; ++g) {
+                    uint32_t hi16, word;
+                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi16) : "r"(v[g * 4 + 3]), "r"(v[g * 4 + 2]), "r"(0));
+                    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(word) : "r"(v[g * 4 + 1]), "r"(v[g * 4 + 0]), "r"(hi16));
+                    packed[h * 2 + g] = word;
                 }
             }
         }

@@ -45,7 +45,7 @@ namespace tqt {
 // int8 x int8
 // ======================================================================================================
 constexpr uint32_t kI8Stages = 6;
-constexpr uint32_t kI8Threads = 320;   // warp 0 producer, warp 1 MMA / relay, warps 2..9 epilogue
+constexpr uint32_t kI8Threads = 352;   // warp 0 producer (even K steps), warp 1 MMA / relay, warps 2..9 epilogue, warp 10 producer (odd K steps)
 constexpr uint32_t kI8Smem = 1024 + kI8Stages * 32768 + 8 * 3 * 128 * 4 + 256;
 
 template <EpiKind EK>
@@ -99,12 +99,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
     long long wcyc[3] = {0, 0, 0};
     const long long t_role0 = args.dbg ? clock64() : 0;
 
-    if (warp == 0) {
-        // ===================== producer (both CTAs) =====================
+    if (warp == 0 || warp == 10) {
+        // ===================== producers (both CTAs) =====================
+        // The issue of a bulk copy costs its warp a few hundred cycles whatever its size (measured: one
+        // warp sustains one set of copies per ~400-500 cycles, n warps n times that, up to ~72 B/clk per
+        // SM), so two warps issue alternate K steps: warp 0 the even ones, warp 10 the odd ones.
+        const uint32_t pw = warp == 0 ? 0u : 1u;
         uint32_t it = 0;
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs) {
-            const uint32_t pm = t % pmc, tn = t / pmc;
+            uint32_t pm, tn;
+            tile_coords(t, pmc, tnc, args.band_m, pm, tn);
             const uint32_t nblk = min(2u, nblocks - tn * 2);
             const uint32_t mtile = pm * 2 + rank;
             const bool a_valid = mtile < tiles_m;
@@ -113,6 +118,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
             const uint8_t *b_src = nblk == 2 ? args.B + (size_t)(tn * 2 + rank) * args.b_kblocks_total * kI8BlockBytes
                                              : args.B + (size_t)(tn * 2) * args.b_kblocks_total * kI8BlockBytes + rank * 8192u;
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
+                if ((it & 1u) != pw) continue;
                 const uint32_t s = it % S, ph = (it / S) & 1u;
                 if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kEmpty + s), ph ^ 1u, sAbort, args.fault, kFaultProducerWait))) {
                     ok = false;
@@ -150,7 +156,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
         uint32_t it = 0, ti = 0;
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
-            const uint32_t tn = t / pmc;
+            uint32_t pm_unused, tn;
+            tile_coords(t, pmc, tnc, args.band_m, pm_unused, tn);
             const uint32_t nblk = min(2u, nblocks - tn * 2);
             const uint32_t idesc = nblk == 2 ? idesc256 : idesc128;
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
@@ -202,7 +209,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
         uint32_t ti = 0;
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
-            const uint32_t pm = t % pmc, tn = t / pmc;
+            uint32_t pm, tn;
+            tile_coords(t, pmc, tnc, args.band_m, pm, tn);
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
             const uint32_t n0 = tn * 256u + half * 128u;
             const uint32_t ncols = args.n > n0 ? min(128u, args.n - n0) : 0u;
@@ -299,13 +307,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
 enum class TsKind : int { W4A8 = 0, W4A16 = 1 };
 
 constexpr uint32_t kTsMT = 192;            // activation rows per tile (MMA N); 96 per CTA in a pair
-constexpr uint32_t kTsThreads = 576;       // warp 0 producer, 1 MMA, 2..9 epilogue, 10..17 converters
+constexpr uint32_t kTsThreads = 608;       // warp 0 producer (step 0 of each group), 1 MMA, 2..9 epilogue, 10..17 converters, 18 producer (step 1)
 constexpr uint32_t kTsT = 4;               // tensor-memory operand stages (4 x 32 columns)
 
 template <TsKind KD, bool PAIR>
 struct TsCfg {
     static constexpr bool kF16 = KD == TsKind::W4A16;
-    static constexpr uint32_t NG = PAIR ? 4u : 3u;                 // shared-memory stage groups (two K steps each)
+    static constexpr uint32_t NG = PAIR ? 5u : 3u;                 // shared-memory stage groups (two K steps each)
     static constexpr uint32_t S = NG * 2u;
     static constexpr uint32_t kActRows = PAIR ? 96u : 192u;        // activation rows this CTA stages per K step
     static constexpr uint32_t kActBytes = kActRows * 128u;
@@ -383,12 +391,17 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     long long wcyc[3] = {0, 0, 0};
     const long long t_role0 = args.dbg ? clock64() : 0;
 
-    if (warp == 0) {
-        // ===================== producer (both CTAs) =====================
+    if (warp == 0 || warp == 18) {
+        // ===================== producers (both CTAs) =====================
+        // The issue of a bulk copy costs its warp a few hundred cycles whatever its size (measured: one
+        // warp sustains one set of copies per ~400-500 cycles, n warps n times that, up to ~72 B/clk per
+        // SM), so the two K steps of a group are issued by two warps: warp 0 step 0, warp 18 step 1.
+        const uint32_t ph = warp == 0 ? 0u : 1u;
         uint32_t Gc = 0;   // groups issued so far
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs) {
-            const uint32_t tm = t % tmc, tn = t / tmc;
+            uint32_t tm, tn;
+            tile_coords(t, tmc, tnc, args.band_m, tm, tn);
             const uint32_t nb = PAIR ? tn * 2 + rank : tn;
             const bool nib_valid = nb < nblocks;
             const uint8_t *nib_src = args.B + (size_t)nb * args.b_kblocks_total * (kF16 ? kI4C2BlockBytes : kI4CxBlockBytes);
@@ -409,7 +422,8 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 }
                 // every group runs both of its steps so that all barriers advance in lockstep; when the tile
                 // has an odd number of K steps the last one is empty (no bytes, no MMAs)
-                for (uint32_t h = 0; h < 2; ++h) {
+                {
+                    const uint32_t h = ph;
                     const uint32_t s = gs * 2 + h, ks = g * 2 + h;
                     if (ks >= ksteps) {
                         if (lane == 0) ptx::mbar_arrive(BAR(kFull + s));
@@ -515,7 +529,8 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
         uint32_t ti = 0;
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
-            const uint32_t tm = t % tmc, tn = t / tmc;
+            uint32_t tm, tn;
+            tile_coords(t, tmc, tnc, args.band_m, tm, tn);
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
             const uint32_t n = (PAIR ? tn * 2 + rank : tn) * 128u + row;
             const bool n_ok = n < args.n;
@@ -588,8 +603,10 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     } else {
         // ===================== converters (warps 10..17): int4 -> MMA operand type, into tensor memory ========
         // Two warps per tensor-memory lane quadrant: set 0 (warps 10..13) takes step 0 of every group, set 1
-        // (warps 14..17) step 1.  Inside a warp the tensor-memory store of one step stays in flight while
-        // the next one is fetched and expanded; only then does the warp wait for the store and announce it.
+        // (warps 14..17) step 1.  A step is fetched and expanded into registers before the warp waits for its
+        // tensor-memory stage to be free; the store is then announced at once (deferring the announcement
+        // past the next step's expansion, to hide the store latency, put that expansion on the MMA's
+        // critical path: the converters have slack, the MMA issuer has none).
         const uint32_t quad = warp & 3u, cset = (warp - 10u) >> 2;
         const uint32_t row = quad * 32u + lane;
         const uint32_t swz_in = (row >> 1) & 3u;
@@ -612,10 +629,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
         };
         uint32_t Gc = 0, ti = 0;
         bool ok = true;
-        bool pending = false;      // a tensor-memory store has been issued but not announced
-        uint32_t pending_ts = 0;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
-            const uint32_t tn = t / tmc;
+            uint32_t tm_unused, tn;
+            tile_coords(t, tmc, tnc, args.band_m, tm_unused, tn);
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
             const size_t nrow = (size_t)(PAIR ? tn * 2 + rank : tn) * 128u + row;
             int32_t rsum = 0;
@@ -674,10 +690,6 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                     }
                 }
                 if (!step_valid) {   // empty step of an odd tile: keep the barrier in step, nothing to convert
-                    if (pending) {
-                        announce(pending_ts);
-                        pending = false;
-                    }
                     // like a real step, it may only be announced once the group that used this operand stage
                     // before is done: otherwise two announcements could fall into one phase of the barrier
                     if (Gc >= 2u) {
@@ -759,7 +771,6 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                         }
                     }
                 }
-                if (pending) announce(pending_ts);
                 // the MMAs of the group two groups back read this tensor-memory stage: they must be done
                 if (Gc >= 2u) {
                     const uint32_t Gp = Gc - 2u;
@@ -771,14 +782,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 }
                 __syncwarp();
                 ptx::tmem_st_32x32b_x32(tmem_a + ts * 32u + ((quad * 32u) << 16), regs);
-                pending = true;
-                pending_ts = ts;
+                announce(ts);
             }
             if (!ok) break;
-            if (pending) {   // the tile's last step must be visible before the leader can finish the tile
-                announce(pending_ts);
-                pending = false;
-            }
             if constexpr (!kF16) {
                 if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kRsumEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultConverterWait))) {
                     ok = false;
@@ -789,7 +795,6 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 if (lane == 0) ptx::mbar_arrive(BAR(kRsumFull + acc));
             }
         }
-        if (pending) announce(pending_ts);
     }
 
     if (args.dbg && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 10)) {

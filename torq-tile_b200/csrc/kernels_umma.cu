@@ -587,12 +587,26 @@ static bool use_pair(uint32_t m, uint32_t min_m)
     return m > min_m;
 }
 
+// Operands that together overflow L2 (126 MB, shared with the output stream): walk the tile grid in
+// bands of 8 activation-row tiles, so a band's activations stay resident while the weights stream once
+// per band.  TQT_B200_BAND overrides (0 = one band), for measurements.
+static uint32_t choose_band(size_t a_bytes, size_t b_bytes)
+{
+    static const int forced = [] {
+        const char *e = std::getenv("TQT_B200_BAND");
+        return e ? std::atoi(e) : -1;
+    }();
+    if (forced >= 0) return (uint32_t)forced;
+    return a_bytes + b_bytes > (size_t)72 << 20 ? 8u : 0u;
+}
+
 Result umma_gemm_i32(const GemmCommon &g, int32_t cmin, int32_t cmax)
 {
     UmmaArgs a{};
     if (!fill_common(a, g, 4, 128, 128)) return Result{kUnsupported, 0};
     a.cmin_i = cmin;
     a.cmax_i = cmax;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k);
     if (use_pair(a.m, 128)) return pair_gemm_i8(a, false, (cudaStream_t)g.stream);
     return launch_umma<BMode::I8, EpiKind::S32, Dtype::F32>(a, (cudaStream_t)g.stream);
 }
@@ -608,6 +622,7 @@ Result umma_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmi
     a.rq_per_tensor = p.quant_channel_b == 1;
     a.rq_scale_d = p.scale_d;
     a.rq_zp_d = p.zero_point_d;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k);
     if (use_pair(a.m, 128)) return pair_gemm_i8(a, true, (cudaStream_t)g.stream);
     return launch_umma<BMode::I8, EpiKind::Req8, Dtype::F32>(a, (cudaStream_t)g.stream);
 }
@@ -623,6 +638,7 @@ Result umma_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float 
     a.scale_b = p.scale_b;
     a.cmin_f = cmin;
     a.cmax_f = cmax;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k / 2);
     cudaStream_t st = (cudaStream_t)g.stream;
     if (umma_variant() == 3) return ts_gemm_w4a8(a, td, false, st);
     if (use_pair(a.m, 96)) return ts_gemm_w4a8(a, td, true, st);
@@ -644,6 +660,7 @@ Result umma_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size
     a.bl = (uint32_t)bl;
     a.cmin_f = cmin;
     a.cmax_f = cmax;
+    a.band_m = choose_band(g.m * g.k * 2, g.n * g.k / 2);
     cudaStream_t st = (cudaStream_t)g.stream;
     if (umma_variant() == 3) return ts_gemm_w4a16(a, td, false, st);
     if (use_pair(a.m, 96)) return ts_gemm_w4a16(a, td, true, st);

@@ -35,9 +35,28 @@ struct UmmaArgs {
     const __half *scale_blk;
     size_t ldsb;
     uint32_t bl;
+    uint32_t band_m;  // tile order: activation-row tiles are walked in bands of this many (0 = one band)
     unsigned int *fault;
     long long *dbg;  // optional per-CTA role timing (diagnostic), 16 slots per CTA
 };
+
+// Tile t of a cm x cn tile grid, walked band by band: inside a band of `band` row tiles the row index
+// runs fastest, so the tiles in flight at any time share `band` row tiles and a few column tiles and the
+// row-tile operand of a band stays in L2 while the column-tile operand streams through once per band.
+__device__ __forceinline__ void tile_coords(uint32_t t, uint32_t cm, uint32_t cn, uint32_t band, uint32_t &im, uint32_t &in)
+{
+    if (band == 0 || band >= cm) {
+        im = t % cm;
+        in = t / cm;
+        return;
+    }
+    const uint32_t per_band = band * cn;
+    const uint32_t b = t / per_band, r = t - b * per_band;
+    const uint32_t m0 = b * band;
+    const uint32_t h = min(band, cm - m0);
+    im = m0 + r % h;
+    in = r / h;
+}
 
 // output element type of each epilogue
 template <EpiKind EK, Dtype TD>
