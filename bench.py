@@ -340,6 +340,8 @@ def run_ours(args):
         cpu = {"value": tops, "unit": "TOPS", "cores": nthreads, "kind": "port",
                "sample": f"{rows} of {M} rows x all N x K in {secs:.1f} s, oracle/tqt_oracle.c with {nthreads} OpenMP threads"}
 
+    # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch, from the ncu captures summarised under profiles/
+    ncu_traffic = {"c3": 55.86e6, "c4": 33.78e6, "c5": None}[cfg] if world == 1 else None
     int8_peak = 2.0 * peaks["bf16_sustained"] if cfg != "c5" else peaks["bf16_sustained"]
     achieved = ops_local / (ms_gemm * 1e-3) / 1e12
     line = {
@@ -355,7 +357,7 @@ def run_ours(args):
         "sustained": None if ms_sustained is None else {"steps": sustain_steps, "ms_per_step": ms_sustained,
                                                         "value": ops / (ms_sustained * 1e-3) / 1e12, "unit": unit},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
-                     "frac": achieved / int8_peak, "traffic": None,
+                     "frac": achieved / int8_peak, "traffic": ncu_traffic,
                      "note": ("run_gemm kernel alone, per GPU; peak = 2 x bf16_tflops_sustained of " + peaks["source"] +
                               " (int8 tensor rate is twice the bf16 rate)") if cfg != "c5" else
                              "run_gemm kernel alone, per GPU; peak = bf16_tflops_sustained of " + peaks["source"]},
@@ -440,7 +442,7 @@ def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20
             "read_ceiling": {"gbs": rd / (us_read * 1e-6) / 1e9, "us": us_read,
                              "note": "a kernel with the GEMV's launch shape that only reads the same bytes, same graph"},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm"], "traffic": None,
+                         "frac": gbs / peaks["hbm"], "traffic": 8.698e6 if (K, N) == (4096, 4096) else None,
                          "note": f"CUDA-graph replay of {copies} back-to-back GEMVs over distinct weights; peak = hbm_gbs of {peaks['source']}"}}
 
 
