@@ -65,6 +65,9 @@ class Oracle:
         lib.tqo_gemm_reqi32toi8.argtypes = [_sz, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int, _vp, _sz, _vp,
                                             _vp, _sz, C.c_int8, C.c_int8, C.c_float, _vp, C.c_int32,
                                             C.c_float, C.c_int32]
+        lib.tqo_gemm_mx1bias_reqi32toi8.argtypes = [_sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _vp, _sz,
+                                                    C.c_int8, C.c_int8, _vp, C.c_int32, C.c_float, C.c_float,
+                                                    C.c_int32]
         lib.tqo_quantize_fp16_to_int4.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp, _sz]
         lib.tqo_gemm_w4a16.argtypes = [_sz, _sz, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp,
                                        _sz, _vp, C.c_float, C.c_float, C.c_int]
@@ -133,6 +136,17 @@ class Oracle:
                                      _ptr(Cm), n, _ptr(bias), _ptr(D), n, int(clamp[0]), int(clamp[1]),
                                      float(scale_a), _ptr(scale_b), int(quant_channel_b), float(scale_d),
                                      int(zp_d))
+        return D
+
+    def gemm_mx1bias_reqi32toi8(self, A, B_kn, scale_a, scale_b, scale_d, zp_d, bias=None, Cm=None,
+                                clamp=(-128, 127), quant_channel_a=0):
+        """A [m,k] int8, B [k,n] int8, scale_a [m] f32, bias [m] int32."""
+        m, k = A.shape
+        n = B_kn.shape[1]
+        D = np.empty((m, n), np.int8)
+        self.lib.tqo_gemm_mx1bias_reqi32toi8(m, n, k, _ptr(A), k, _ptr(B_kn), n, _ptr(Cm), n, _ptr(bias), _ptr(D), n,
+                                             int(clamp[0]), int(clamp[1]), _ptr(scale_a), int(quant_channel_a),
+                                             float(scale_b), float(scale_d), int(zp_d))
         return D
 
     def quantize_fp16_to_int4(self, W_f16_bits, bl):

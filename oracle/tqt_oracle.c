@@ -440,6 +440,45 @@ void tqo_gemm_reqi32toi8(size_t m, size_t n, size_t k, const int8_t *A, size_t l
 }
 
 /* ------------------------------------------------------------------------- */
+/* gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dx[p]_qai8[p]: static W8A8 with a   */
+/* per-row scale of A and an Mx1 bias.  acc = C + A*B + bias[m]; per row      */
+/* real = (double)sa[m]*(double)sb/sd (row 0 for every row when                */
+/* quant_channel_a == 1), then the same integer tail                           */
+/* (src/gemm/gemm_i8_i8/gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8/       */
+/*  tqt_gemm_..._4x1vl_rvv.cpp:84-118, 141-163; requant                        */
+/*  tqt_kernel_gemm_i8_i8_4x1vl_rvv.h:264-330).  A [m,k], B [k,n] row-major.   */
+/* zero_point_b is not applied: callers pre-fuse it into the bias.            */
+/* Parity unpinned beyond the reference's own +-1 LSB dequantised tolerance,   */
+/* like tqo_gemm_reqi32toi8 (same tail).                                       */
+/* ------------------------------------------------------------------------- */
+void tqo_gemm_mx1bias_reqi32toi8(size_t m, size_t n, size_t k, const int8_t *A, size_t lda,
+                                 const int8_t *B, size_t ldb, const int32_t *C, size_t ldc,
+                                 const int32_t *bias, int8_t *D, size_t ldd, int8_t clamp_min,
+                                 int8_t clamp_max, const float *scale_a, int32_t quant_channel_a,
+                                 float scale_b, float scale_d, int32_t zp_d)
+{
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t i = 0; i < (ptrdiff_t)m; ++i) {
+        size_t si = (quant_channel_a == 1) ? 0 : (size_t)i;
+        double real = (double)scale_a[si] * (double)scale_b / (double)scale_d;
+        int32_t mult, s;
+        tqo_quantize_multiplier(real, &mult, &s);
+        int32_t sh = -s - 1;
+        for (size_t j = 0; j < n; ++j) {
+            int32_t acc = 0;
+            for (size_t p = 0; p < k; ++p) acc += (int32_t)A[i * lda + p] * (int32_t)B[p * ldb + j];
+            uint32_t u = (uint32_t)acc;
+            if (C) u += (uint32_t)C[i * ldc + j];
+            if (bias) u += (uint32_t)bias[i];
+            int32_t t = tqo_requantize_one((int32_t)u, mult, sh, zp_d);
+            if (t < clamp_min) t = clamp_min;
+            if (t > clamp_max) t = clamp_max;
+            D[i * ldd + j] = (int8_t)t;
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------- */
 /* qsi4c2: block-wise int4 quantisation of f16 weights with f16 scales.       */
 /* Follows test/common/quantize_utils.h:34-70 (quantize_fp16_to_int4):        */
 /* scale = signed-absmax / -8, q = min((int8)(v/scale + 8.5), 15).            */

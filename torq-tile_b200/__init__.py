@@ -294,6 +294,104 @@ class GemmW4A16(_UKernel):
         check("run_gemm " + self.type_name)
 
 
+# ---- sibling kernel types (generic CUDA-core path) ------------------------------------------------
+class QaI8QsI8DxQaI8Params(C.Structure):
+    """struct tqt_qai8_qsi8dx_qai8_params (host struct; scale_a is a device array)."""
+    _fields_ = [("scale_a", _vp), ("quant_channel_a", C.c_int32), ("scale_b", C.c_float),
+                ("zero_point_b", C.c_int32), ("scale_d", C.c_float), ("zero_point_d", C.c_int32)]
+
+
+class QaI8DxpQsI8CxpParams(C.Structure):
+    """struct tqt_qai8dxp_qsi8cxp_params (host struct holding three device arrays)."""
+    _fields_ = [("scale_a", _vp), ("zero_point_a", _vp), ("scale_b", _vp)]
+
+
+_UNPACKED_HELPERS = (("get_m_step", 0), ("get_n_step", 0), ("get_a_offset", 3), ("get_b_offset", 3),
+                     ("get_c_offset", 3), ("get_bias_offset", 1), ("get_d_offset", 3), ("get_d_size", 2))
+_PACKED_HELPERS_B = _PACKED_HELPERS + (("get_bias_offset", 1),)
+
+
+class SiblingGemm(_UKernel):
+    """One of the sibling kernel types of include/tqt_b200_gemm_siblings.h.
+
+    ``type_name`` selects it; the signature of run_gemm follows from the name:
+    ``clamp`` "i8" / "f32" / "f16" / "bf16" (type of the two clamp arguments), ``params`` the ctypes
+    struct class (None for the W4A16 types, which take bl / scale_b / ldsb instead)."""
+
+    def __init__(self, type_name: str):
+        self.type_name = type_name
+        t = type_name
+        self.w4a16 = "_f16_qsi4c2t" in t
+        a_packed = "qai8dxp" in t or "qsi8dxp" in t
+        b_packed = t.endswith("p")
+        if self.w4a16:
+            self.helpers_size = (("get_m_step", 0), ("get_n_step", 0), ("get_a_offset", 4), ("get_b_offset", 4),
+                                 ("get_scale_b_offset", 3), ("get_c_offset", 3), ("get_bias_offset", 1),
+                                 ("get_d_offset", 3), ("get_d_size", 2))
+            packs = []
+        elif a_packed and b_packed:
+            self.helpers_size = _PACKED_HELPERS_B
+            packs = ["run_a_pack", "run_b_pack", "run_bt_pack"]
+        elif b_packed:   # A unpacked, B packed
+            self.helpers_size = (("get_m_step", 0), ("get_n_step", 0), ("get_a_offset", 3), ("get_b_packed_offset", 4),
+                                 ("get_c_offset", 3), ("get_bias_offset", 1), ("get_d_offset", 3), ("get_d_size", 2),
+                                 ("get_b_packed_size", 2))
+            packs = ["run_b_pack", "run_bt_pack"]
+        else:
+            self.helpers_size = _UNPACKED_HELPERS
+            packs = []
+        self.actions = [h[0] for h in self.helpers_size] + packs + ["run_gemm"]
+        if "reqi32toi8" in t:
+            self.clamp = "i8"
+            self.params_cls = QaI8QsI8DxQaI8Params if "mx1bias" in t else QaI8QaI8QsI8CxParams
+        else:
+            self.clamp = t.split("_clamp_")[1].split("_")[0]
+            self.params_cls = None if self.w4a16 else (QaI8DxQsI4CxParams if "qsi4cx" in t else QaI8DxpQsI8CxpParams)
+        super().__init__()
+
+    def run_a_pack(self, m, k, lda, lda_packed, k_idx, A, A_packed):
+        self._pack("run_a_pack", m, k, lda, lda_packed, k_idx, A, A_packed)
+
+    def run_b_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_b_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def run_bt_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_bt_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def _clamp_arg(self, v):
+        if self.clamp == "i8":
+            return C.c_int8(int(v))
+        if self.clamp == "f32":
+            return C.c_float(v)
+        return half_arg(f16_bits(v) if self.clamp == "f16" else bf16_bits(v))
+
+    def run_gemm(self, m, n, k, A, lda, k_idx_a, B, ldb, k_idx_b, Cm, ldc, D, ldd, bias, clamp_min, clamp_max,
+                 params=None, bl=None, scale_b=None, ldsb=0):
+        f = self._sym("run_gemm")
+        ct = C.c_int8 if self.clamp == "i8" else C.c_float
+        f.restype = None
+        if self.w4a16:
+            f.argtypes = [_sz, _sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, _sz, _vp, ct, ct]
+            f(m, n, k, bl, _addr(A), lda, k_idx_a, _addr(B), ldb, k_idx_b, _addr(scale_b), ldsb, _addr(Cm), ldc,
+              _addr(D), ldd, _addr(bias), self._clamp_arg(clamp_min), self._clamp_arg(clamp_max))
+        else:
+            f.argtypes = [_sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, ct, ct,
+                          C.POINTER(self.params_cls)]
+            f(m, n, k, _addr(A), lda, k_idx_a, _addr(B), ldb, k_idx_b, _addr(Cm), ldc, _addr(D), ldd, _addr(bias),
+              self._clamp_arg(clamp_min), self._clamp_arg(clamp_max), None if params is None else C.byref(params))
+        check("run_gemm " + self.type_name)
+
+
+SIBLING_TYPES = (
+    [f"gemm_1xnbias_clamp_{t}_qai8dx_qsi4cxt" for t in ("f32", "f16", "bf16")]
+    + ["gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxt", "gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp",
+       "gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8", "gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p"]
+    + [f"gemm_1xnbias_clamp_{t}_qai8dx_qsi8cxt" for t in ("f32", "f16")]
+    + [f"gemm_1xnbias_clamp_{t}_qai8dxp_qsi8cxp" for t in ("f32", "f16")]
+    + [f"gemm_1xnbias_clamp_{t}_f16_qsi4c2t" for t in ("f16", "f32")]
+)
+
+
 # ---- extensions ------------------------------------------------------------------------------------
 _TA_NAMES = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}
 
@@ -358,4 +456,4 @@ EXTENSION_SYMBOLS = (
 
 def all_ukernels():
     return [GemmClampI32I8I8(), GemmClampI32I8pI8p(), GemmReqI8(), GemmW4A8("f32"), GemmW4A8("f16"),
-            GemmW4A8("bf16"), GemmW4A16("f16"), GemmW4A16("f32")]
+            GemmW4A8("bf16"), GemmW4A16("f16"), GemmW4A16("f32")] + [SiblingGemm(t) for t in SIBLING_TYPES]

@@ -6,6 +6,7 @@
 #include "../../include/tqt_b200_gemm_f16_i4.h"
 #include "../../include/tqt_b200_gemm_i8_i4.h"
 #include "../../include/tqt_b200_gemm_i8_i8.h"
+#include "../../include/tqt_b200_gemm_siblings.h"
 #include "tqt_internal.h"
 
 using namespace tqt;
@@ -453,6 +454,8 @@ uint16_t tqt_cuda_debug_bf16_bits(bfloat16_t v)
 void tqt_cuda_debug_set_timing_buffer(void *dev_ptr) { set_timing_buffer(dev_ptr); }
 
 void tqt_cuda_debug_stream_read(const void *src, size_t bytes, void *sink) { set_result(stream_read(src, bytes, sink, t_stream)); }
+
+#include "abi_siblings.inc"
 
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k)
 {

@@ -38,6 +38,16 @@ struct PackedI4Cx {  // qsi4cx blocks, returns the signed value q
     }
 };
 
+struct RowMajorNib {  // [rows, k / 2] bytes, row stride in bytes; byte = (q_hi + 8) << 4 | (q_lo + 8), low nibble = even k
+    const uint8_t *p;
+    size_t ld_bytes;
+    __device__ int8_t get(size_t r, size_t k) const
+    {
+        const uint32_t v = (p[r * ld_bytes + (k >> 1)] >> ((k & 1) * 4)) & 0xFu;
+        return (int8_t)((int)v - 8);
+    }
+};
+
 template <class LA, class LB, class Epi, bool RSUM>
 __global__ void __launch_bounds__(256) gemm_simt_i8_kernel(size_t m, size_t n, size_t k, LA la, LB lb, Epi epi)
 {
@@ -160,9 +170,77 @@ Result simt_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float 
     }
 }
 
+// ---- sibling kernel types: any operand layout -------------------------------------------------------------
+// Calls f(accessor) with the int8 accessor that matches the layout.
+template <class F>
+static Result with_i8_layout(Layout l, const void *p, size_t ld, F f)
+{
+    switch (l) {
+        case Layout::Packed: return f(PackedI8{(const int8_t *)p, ceil_div(ld, 128)});
+        case Layout::RowMajor: return f(RowMajorI8{(const int8_t *)p, ld});
+        default: return f(ColMajorI8{(const int8_t *)p, ld});
+    }
+}
+
+template <class Epi, bool RSUM>
+static Result run_simt_layouts(const GemmCommon &g, Layout la, Layout lb, Epi epi)
+{
+    return with_i8_layout(la, g.A, g.lda, [&](auto a) {
+        return with_i8_layout(lb, g.B, g.ldb, [&](auto b) { return run_simt<decltype(a), decltype(b), Epi, RSUM>(g, a, b, epi); });
+    });
+}
+
+Result launch_gemm_requant_i8_layouts(const GemmCommon &g, const RequantParams &p, int cmin, int cmax, Layout la,
+                                      Layout lb)
+{
+    EpiRequant epi{(const int32_t *)g.C, g.ldc, (const int32_t *)g.bias, (int8_t *)g.D, g.ldd, p.scale_a, p.scale_b,
+                   p.quant_channel_b, p.scale_d, p.zero_point_d, cmin, cmax};
+    return run_simt_layouts<EpiRequant, false>(g, la, lb, epi);
+}
+
+Result launch_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &p, int cmin, int cmax, Layout la,
+                                   Layout lb)
+{
+    EpiRequantRow epi{(const int32_t *)g.C, g.ldc, (const int32_t *)g.bias, (int8_t *)g.D, g.ldd, p.scale_a,
+                      p.quant_channel_a, p.scale_b, p.scale_d, p.zero_point_d, cmin, cmax};
+    return run_simt_layouts<EpiRequantRow, false>(g, la, lb, epi);
+}
+
+Result launch_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax, Layout la,
+                        Layout lb)
+{
+    if (td == Dtype::F32) {
+        EpiDxCx<Dtype::F32> epi{g.bias, g.D, g.ldd, p.scale_a, p.zp_a, p.scale_b, cmin, cmax};
+        return run_simt_layouts<EpiDxCx<Dtype::F32>, true>(g, la, lb, epi);
+    }
+    if (td != Dtype::F16) return Result{kUnsupported, 0};
+    EpiDxCx<Dtype::F16> epi{g.bias, g.D, g.ldd, p.scale_a, p.zp_a, p.scale_b, cmin, cmax};
+    return run_simt_layouts<EpiDxCx<Dtype::F16>, true>(g, la, lb, epi);
+}
+
+template <Dtype TD>
+static Result simt_w4a8_unpacked_t(const GemmCommon &g, const W4A8Params &p, float cmin, float cmax)
+{
+    EpiW4A8<TD> epi{g.C, g.ldc, g.bias, g.D, g.ldd, p.scale_a, p.zp_a, p.scale_b, cmin, cmax};
+    RowMajorI8 la{(const int8_t *)g.A, g.lda};
+    RowMajorNib lb{(const uint8_t *)g.B, g.ldb / 2};
+    return run_simt<RowMajorI8, RowMajorNib, EpiW4A8<TD>, true>(g, la, lb, epi);
+}
+
+Result launch_gemm_w4a8_unpacked(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
+{
+    switch (td) {
+        case Dtype::F32: return simt_w4a8_unpacked_t<Dtype::F32>(g, p, cmin, cmax);
+        case Dtype::F16: return simt_w4a8_unpacked_t<Dtype::F16>(g, p, cmin, cmax);
+        default: return simt_w4a8_unpacked_t<Dtype::BF16>(g, p, cmin, cmax);
+    }
+}
+
 // ---- W4A16 (float) ------------------------------------------------------------------------------------
 // One output per thread, k-order f32 accumulation of a * f16((nib-8)*scale).  Test-size only.
-template <Dtype TD>
+// PACKED: A / B in the block layouts (a_ld / b_ld = blocks per row tile); else A f16 [m, a_ld elements],
+// B nibbles [n, b_ld bytes] with byte = (q_hi + 8) << 4 | (q_lo + 8), low nibble = even k.
+template <Dtype TD, bool PACKED>
 __global__ void gemm_simt_w4a16_kernel(size_t m, size_t n, size_t k, size_t bl, const uint8_t *__restrict__ A,
                                        size_t a_kblocks, const uint8_t *__restrict__ B, size_t b_kblocks,
                                        const __half *__restrict__ scale_b, size_t ldsb, const void *C, size_t ldc,
@@ -173,11 +251,18 @@ __global__ void gemm_simt_w4a16_kernel(size_t m, size_t n, size_t k, size_t bl, 
     if (nn >= n || mm >= m) return;
     float acc = 0.0f;
     for (size_t kk = 0; kk < k; ++kk) {
-        const uint8_t *ab = A + ((mm >> 7) * a_kblocks + (kk >> 6)) * kF16BlockBytes + sw128_byte((uint32_t)(mm & 127), (uint32_t)(kk & 63) * 2);
-        const float a = __half2float(*reinterpret_cast<const __half *>(ab));
-        uint32_t hi;
-        const uint32_t bb = i4c2_byte((uint32_t)(nn & 127), (uint32_t)(kk & 127), &hi);
-        const int q = (int)((B[((nn >> 7) * b_kblocks + (kk >> 7)) * kI4C2BlockBytes + bb] >> (hi * 4)) & 0xFu) - 8;
+        float a;
+        int q;
+        if (PACKED) {
+            const uint8_t *ab = A + ((mm >> 7) * a_kblocks + (kk >> 6)) * kF16BlockBytes + sw128_byte((uint32_t)(mm & 127), (uint32_t)(kk & 63) * 2);
+            a = __half2float(*reinterpret_cast<const __half *>(ab));
+            uint32_t hi;
+            const uint32_t bb = i4c2_byte((uint32_t)(nn & 127), (uint32_t)(kk & 127), &hi);
+            q = (int)((B[((nn >> 7) * b_kblocks + (kk >> 7)) * kI4C2BlockBytes + bb] >> (hi * 4)) & 0xFu) - 8;
+        } else {
+            a = __half2float(reinterpret_cast<const __half *>(A)[mm * a_kblocks + kk]);
+            q = (int)((B[nn * b_kblocks + (kk >> 1)] >> ((kk & 1) * 4)) & 0xFu) - 8;
+        }
         const __half w = __hmul(__int2half_rn(q), scale_b[nn * ldsb + kk / bl]);
         acc = __fmaf_rn(a, __half2float(w), acc);
     }
@@ -196,13 +281,33 @@ Result simt_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size
     dim3 grid((unsigned)ceil_div(g.n, 128), (unsigned)g.m);
     cudaStream_t st = (cudaStream_t)g.stream;
     if (td == Dtype::F16)
-        gemm_simt_w4a16_kernel<Dtype::F16><<<grid, 128, 0, st>>>(g.m, g.n, g.k, bl, (const uint8_t *)g.A, ceil_div(g.lda, 64),
+        gemm_simt_w4a16_kernel<Dtype::F16, true><<<grid, 128, 0, st>>>(g.m, g.n, g.k, bl, (const uint8_t *)g.A, ceil_div(g.lda, 64),
                                                                (const uint8_t *)g.B, ceil_div(g.ldb, 128), (const __half *)scale_b,
                                                                ldsb, g.C, g.ldc, g.D, g.ldd, g.bias, cmin, cmax);
     else
-        gemm_simt_w4a16_kernel<Dtype::F32><<<grid, 128, 0, st>>>(g.m, g.n, g.k, bl, (const uint8_t *)g.A, ceil_div(g.lda, 64),
+        gemm_simt_w4a16_kernel<Dtype::F32, true><<<grid, 128, 0, st>>>(g.m, g.n, g.k, bl, (const uint8_t *)g.A, ceil_div(g.lda, 64),
                                                                (const uint8_t *)g.B, ceil_div(g.ldb, 128), (const __half *)scale_b,
                                                                ldsb, g.C, g.ldc, g.D, g.ldd, g.bias, cmin, cmax);
+    return check_launch();
+}
+
+Result launch_gemm_w4a16_unpacked(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td,
+                                  float cmin, float cmax)
+{
+    if (g.m == 0 || g.n == 0) return Result{kOk, 0};
+    if (g.m > 65535) return Result{kUnsupported, 0};
+    dim3 grid((unsigned)ceil_div(g.n, 128), (unsigned)g.m);
+    cudaStream_t st = (cudaStream_t)g.stream;
+    if (td == Dtype::F16)
+        gemm_simt_w4a16_kernel<Dtype::F16, false><<<grid, 128, 0, st>>>(g.m, g.n, g.k, bl, (const uint8_t *)g.A, g.lda,
+                                                                      (const uint8_t *)g.B, g.ldb / 2, (const __half *)scale_b,
+                                                                      ldsb, g.C, g.ldc, g.D, g.ldd, g.bias, cmin, cmax);
+    else if (td == Dtype::F32)
+        gemm_simt_w4a16_kernel<Dtype::F32, false><<<grid, 128, 0, st>>>(g.m, g.n, g.k, bl, (const uint8_t *)g.A, g.lda,
+                                                                      (const uint8_t *)g.B, g.ldb / 2, (const __half *)scale_b,
+                                                                      ldsb, g.C, g.ldc, g.D, g.ldd, g.bias, cmin, cmax);
+    else
+        return Result{kUnsupported, 0};
     return check_launch();
 }
 

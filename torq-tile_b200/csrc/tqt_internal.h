@@ -90,6 +90,38 @@ Result launch_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, floa
 Result launch_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td,
                          float clamp_min, float clamp_max, Path path);
 
+// ---- sibling kernel types (generic CUDA-core path) --------------------------------------------
+// How an operand is stored: Packed = the 128 x 128 block layout; RowMajor = [rows, k] with stride ld
+// (rows = m for A, n for B: the reference's "t" layouts); KMajor = [k, rows] with stride ld.
+enum class Layout : int { Packed = 0, RowMajor = 1, KMajor = 2 };
+
+// 1xN-bias requantising GEMM with any operand layouts.
+Result launch_gemm_requant_i8_layouts(const GemmCommon &g, const RequantParams &p, int clamp_min, int clamp_max,
+                                      Layout la, Layout lb);
+
+struct RowRequantParams {
+    const float *scale_a;  // device [m] (one value when quant_channel_a == 1)
+    int quant_channel_a;
+    float scale_b;
+    float scale_d;
+    int32_t zero_point_d;
+};
+// Mx1-bias requantising GEMM (per-row scale of A), bias int32 [m].
+Result launch_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &p, int clamp_min, int clamp_max,
+                                   Layout la, Layout lb);
+
+// qai8dx x qsi8cx, float output of type td (F32 or F16); C is ignored, bias typed like D.
+Result launch_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float clamp_min, float clamp_max,
+                        Layout la, Layout lb);
+
+// W4A8 on unpacked operands: A int8 [m, lda], B nibbles [n, ldb / 2 bytes] (low nibble = even k, value q + 8).
+Result launch_gemm_w4a8_unpacked(const GemmCommon &g, const W4A8Params &p, Dtype td, float clamp_min,
+                                 float clamp_max);
+
+// W4A16 on unpacked operands: A f16 [m, lda], B nibbles [n, ldb / 2 bytes], scale_b [n, ldsb] f16.
+Result launch_gemm_w4a16_unpacked(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td,
+                                  float clamp_min, float clamp_max);
+
 // Reads (and clears) the device-side watchdog word of the current device after synchronising
 // the stream.  0 = no fault.
 int read_device_fault(void *stream);
