@@ -15,7 +15,8 @@ Inputs are seeded synthetic data with the shapes and value distributions the con
 With --gpus N > 1 (launched by torch.distributed.run, one rank per GPU) the weight matrix is split
 along N across the ranks (column-parallel, total work fixed: "strong" scaling); activations are
 replicated; no collective is on the data path.  --gather additionally times an NCCL all-gather
-of the output column shards (reported separately as "gather_ms", not part of "value").
+of the output column shards and the fused form (peer stores from the GEMM epilogue), reported
+separately under "gather", not part of "value".
 
 --impl reference times the CPU implementation of the same path on the host cores (the oracle port
 built from oracle/tqt_oracle.c; the reference's W4A8 code lives in a gtest translation unit that
@@ -171,6 +172,8 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
+        if args.gather:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only: no multicast binding
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     torch.cuda.set_device(local_rank)
@@ -306,15 +309,49 @@ def run_ours(args):
     e2e_steps = max(3, min(args.steps, 10))
     ms_e2e = timed(step_e2e, e2e_steps, max(3, min(args.warmup, 3)))
 
-    # ---- optional: all-gather of the output column shards over NVLink (NCCL) -----------------------
-    gather_ms = None
-    if world > 1 and args.gather:
+    # ---- optional: the full output on every GPU -------------------------------------------------------
+    # (a) the step followed by an NCCL all-gather of the column shards; (b) the fused form: the GEMM's epilogue
+    # stores every tile into the peer-mapped output buffers of all ranks (tqt_cuda_set_output_replicas), no collective.
+    gather = None
+    if world > 1 and args.gather and cfg in ("c3", "c5"):
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only: no multicast binding
+        import torch.distributed._symmetric_memory as symm
         out_local = layers[0].workspace(M)["out"]
-        gathered = torch.empty((world * out_local.shape[0], out_local.shape[1]), dtype=out_local.dtype, device=dev)
+        staged = torch.empty((world * M, n_local), dtype=out_local.dtype, device=dev)
+        full = symm.empty((M, N), dtype=out_local.dtype, device=dev)
+        hdl = symm.rendezvous(full, dist.group.WORLD.group_name)
+        peers = [int(hdl.buffer_ptrs[r]) for r in range(world) if r != rank]
+        g_steps, g_warm = max(3, min(args.steps, 50)), 3
 
-        def gather_step(i):
-            dist.all_gather_into_tensor(gathered, layers[i % R].workspace(M)["out"])
-        gather_ms = timed(gather_step, max(3, min(args.steps, 10)), 3)
+        def step_nccl(i):
+            out = step_device(i)
+            dist.all_gather_into_tensor(staged, out)
+
+        def step_fused(i):
+            L = layers[i % R]
+            (L.quantize if cfg == "c3" else L.pack)(a_dev)
+            pkg.set_output_replicas(full.data_ptr(), peers)
+            try:
+                L.gemm(M, out=full[:, n_begin:n_begin + n_local])
+            finally:
+                pkg.set_output_replicas(0, [])
+
+        ms_nccl = timed(step_nccl, g_steps, g_warm)
+        ms_fused = timed(step_fused, g_steps, g_warm)
+        # the two forms must agree: run step 0 both ways and compare every rank's copy of the full output
+        full.zero_()
+        barrier()
+        step_fused(0)
+        barrier()
+        step_nccl(0)
+        barrier()
+        same = all(torch.equal(full[:, r * n_local:(r + 1) * n_local], staged[r * M:(r + 1) * M]) for r in range(world))
+        flag = torch.tensor([1 if same else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        gather = {"nccl_step_ms": ms_nccl, "fused_step_ms": ms_fused, "outputs_equal_on_all_ranks": bool(flag.item()),
+                  "bytes_per_rank": M * n_local * out_local.element_size(),
+                  "note": "nccl: step + all_gather_into_tensor of the column shards; fused: the GEMM epilogue stores "
+                          "each tile into every rank's output buffer (peer stores over NVLink), no collective"}
 
     fault = pkg.read_device_fault()
 
@@ -366,9 +403,8 @@ def run_ours(args):
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks, "device_fault": fault,
     }
-    if gather_ms is not None:
-        line["gather_ms"] = gather_ms
-        line["config"]["gather"] = f"all_gather_into_tensor of [{M}, {n_local}] shards into a [world * M, N/world] staging buffer"
+    if gather is not None:
+        line["gather"] = gather
     if cpu:
         line["cpu_baseline"] = cpu
     if decode:
@@ -454,7 +490,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c3", choices=sorted(CONFIGS))
     ap.add_argument("--rotate", type=int, default=4, help="distinct weight/output sets cycled through (defeats L2 reuse)")
-    ap.add_argument("--gather", action="store_true", help="also time an NCCL all-gather of the output shards (N > 1)")
+    ap.add_argument("--gather", action="store_true", help="N > 1: also time the step with the full output gathered on every GPU (NCCL, and fused peer stores)")
     ap.add_argument("--sustain-s", type=float, default=1.5, help="seconds of continued step loop for clock sampling (0 = off)")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")

@@ -58,6 +58,17 @@ void tqt_run_a_unpack_f16_128x128_sm100a(size_t m, size_t k, const void *A_packe
  */
 void tqt_shard_plan_n(size_t n, size_t world, size_t rank, size_t *n_begin, size_t *n_count);
 
+/* Output replicas for the calling thread's following run_gemm calls (fused GEMM -> all-gather): every
+ * element a kernel stores at address x inside the buffer that starts at local_base is also stored at
+ * replica_bases[i] + (x - local_base), i < count <= 7.  The replicas are copies of the same output buffer
+ * mapped from other GPUs (CUDA IPC or symmetric memory): the epilogue writes each tile to all of them with
+ * plain peer stores while the mainloop of the next tile runs, so no separate collective is needed.  The
+ * stores are visible to the peers once the kernel has completed; ordering against the peers' readers is the
+ * caller's (a barrier after the call).  count = 0 switches it off.  Honoured by the packed W4A8 and W4A16
+ * kernel types on their tensor-core path; any other run_gemm reports TQT_CUDA_UNSUPPORTED while replicas
+ * are set.  No counterpart in the reference, whose kernels write one buffer. */
+void tqt_cuda_set_output_replicas(const void *local_base, void *const *replica_bases, size_t count);
+
 /* Which device kernel a run_gemm call of the given shape would launch: 0 = tcgen05 tensor-core
  * GEMM, 1 = HBM-streaming GEMV (m <= 8), 2 = generic CUDA-core kernel (unpacked operands). */
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k);

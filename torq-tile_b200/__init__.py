@@ -106,6 +106,18 @@ def use_current_torch_stream() -> None:
     set_stream(torch.cuda.current_stream())
 
 
+def set_output_replicas(local_base: int, replica_bases) -> None:
+    """Also store the output of the following run_gemm calls at the same offsets inside the buffers that
+    start at ``replica_bases`` (device addresses, e.g. peer-mapped copies); an empty list switches it off."""
+    n = len(replica_bases)
+    arr = (C.c_void_p * max(n, 1))(*[C.c_void_p(int(b)) for b in replica_bases])
+    f = lib().tqt_cuda_set_output_replicas
+    f.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t]
+    f.restype = None
+    f(C.c_void_p(int(local_base)) if n else None, arr if n else None, n)
+    check("set_output_replicas")
+
+
 def read_device_fault() -> int:
     return int(lib().tqt_cuda_read_device_fault())
 
@@ -447,7 +459,7 @@ EXTENSION_SYMBOLS = (
     ["tqt_cuda_set_stream", "tqt_cuda_get_stream", "tqt_cuda_get_last_status", "tqt_cuda_get_last_cuda_error",
      "tqt_cuda_read_device_fault", "tqt_cuda_version", "tqt_shard_plan_n", "tqt_cuda_kernel_choice_w4a8",
      "tqt_cuda_debug_f16_bits", "tqt_cuda_debug_bf16_bits", "tqt_cuda_debug_set_timing_buffer",
-     "tqt_cuda_debug_stream_read"]
+     "tqt_cuda_debug_stream_read", "tqt_cuda_set_output_replicas"]
     + [f"tqt_run_quant_pack_qai8dxp_{t}_{VARIANT}" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_quant_qai8dx_{t}_sm100a" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_{n}_{VARIANT}" for n in ("a_unpack_i8", "a_unpack_f16", "bt_unpack_qsi4cxp", "bt_unpack_qsi4c2p")]

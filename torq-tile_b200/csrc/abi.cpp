@@ -16,6 +16,9 @@ namespace {
 thread_local void *t_stream = nullptr;
 thread_local int t_status = TQT_CUDA_OK;
 thread_local int t_cuda_error = 0;
+thread_local size_t t_n_replicas = 0;
+thread_local const char *t_replica_local = nullptr;
+thread_local long long t_replica_delta[7] = {0, 0, 0, 0, 0, 0, 0};
 
 inline void set_result(Result r)
 {
@@ -48,6 +51,8 @@ inline GemmCommon common(size_t m, size_t n, size_t k, const void *A, size_t lda
     g.D = D; g.ldd = ldd;
     g.bias = bias;
     g.stream = t_stream;
+    g.n_replicas = t_n_replicas;
+    for (size_t i = 0; i < t_n_replicas; ++i) g.replica_delta[i] = t_replica_delta[i];
     return g;
 }
 
@@ -454,6 +459,16 @@ uint16_t tqt_cuda_debug_bf16_bits(bfloat16_t v)
 void tqt_cuda_debug_set_timing_buffer(void *dev_ptr) { set_timing_buffer(dev_ptr); }
 
 void tqt_cuda_debug_stream_read(const void *src, size_t bytes, void *sink) { set_result(stream_read(src, bytes, sink, t_stream)); }
+
+void tqt_cuda_set_output_replicas(const void *local_base, void *const *replica_bases, size_t count)
+{
+    if (count > 7 || (count && (!local_base || !replica_bases))) return set_invalid();
+    t_n_replicas = count;
+    t_replica_local = static_cast<const char *>(local_base);
+    for (size_t i = 0; i < count; ++i)
+        t_replica_delta[i] = (long long)(static_cast<const char *>(replica_bases[i]) - t_replica_local);
+    set_ok();
+}
 
 #include "abi_siblings.inc"
 

@@ -41,7 +41,7 @@ Result launch_gemm_i32(const GemmCommon &g, bool packed, int32_t cmin, int32_t c
     if (empty_problem(g)) return Result{kOk, 0};
     if (path == Path::Gemv) return Result{kUnsupported, 0};
     if (!packed || g.k == 0 || path == Path::Simt) {
-        if (path == Path::Umma) return Result{kUnsupported, 0};
+        if (path == Path::Umma || g.n_replicas) return Result{kUnsupported, 0};
         return simt_gemm_i32(g, packed, cmin, cmax);
     }
     return umma_gemm_i32(g, cmin, cmax);
@@ -52,7 +52,7 @@ Result launch_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int c
     if (empty_problem(g)) return Result{kOk, 0};
     if (path == Path::Gemv) return Result{kUnsupported, 0};
     if (g.k == 0 || path == Path::Simt) {
-        if (path == Path::Umma) return Result{kUnsupported, 0};
+        if (path == Path::Umma || g.n_replicas) return Result{kUnsupported, 0};
         return simt_gemm_requant_i8(g, p, cmin, cmax);
     }
     return umma_gemm_requant_i8(g, p, cmin, cmax);
@@ -62,11 +62,11 @@ Result launch_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, floa
 {
     if (empty_problem(g)) return Result{kOk, 0};
     if (g.k == 0 || path == Path::Simt) {
-        if (path == Path::Umma || path == Path::Gemv) return Result{kUnsupported, 0};
+        if (path == Path::Umma || path == Path::Gemv || g.n_replicas) return Result{kUnsupported, 0};
         return simt_gemm_w4a8(g, p, td, cmin, cmax);
     }
-    if (path == Path::Gemv) return gemv_w4a8(g, p, td, cmin, cmax);
-    if (path == Path::Auto && g.m <= 8) {
+    if (path == Path::Gemv) return g.n_replicas ? Result{kUnsupported, 0} : gemv_w4a8(g, p, td, cmin, cmax);
+    if (path == Path::Auto && g.m <= 8 && !g.n_replicas) {
         Result r = gemv_w4a8(g, p, td, cmin, cmax);
         if (r.status != kUnsupported) return r;  // shapes the GEMV cannot hold fall through to the GEMM
     }
@@ -79,7 +79,7 @@ Result launch_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, si
     if (empty_problem(g)) return Result{kOk, 0};
     if (path == Path::Gemv) return Result{kUnsupported, 0};
     if (g.k == 0 || path == Path::Simt) {
-        if (path == Path::Umma) return Result{kUnsupported, 0};
+        if (path == Path::Umma || g.n_replicas) return Result{kUnsupported, 0};
         return simt_gemm_w4a16(g, bl, scale_b, ldsb, td, cmin, cmax);
     }
     return umma_gemm_w4a16(g, bl, scale_b, ldsb, td, cmin, cmax);

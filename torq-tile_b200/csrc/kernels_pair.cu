@@ -586,7 +586,11 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                         if (args.C) v = __fadd_rn(v, TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n));
                         if (args.bias) v = __fadd_rn(v, bv);
                         v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
-                        dcol[(size_t)j * args.ldd] = cvt_out<OutT>(v);   // the warp writes 32 consecutive channels
+                        const OutT o = cvt_out<OutT>(v);
+                        OutT *dst = dcol + (size_t)j * args.ldd;
+                        *dst = o;   // the warp writes 32 consecutive channels
+                        for (uint32_t rp = 0; rp < args.n_replicas; ++rp)   // peer-mapped copies of the output
+                            *reinterpret_cast<OutT *>(reinterpret_cast<char *>(dst) + args.replica_delta[rp]) = o;
                     }
                 }
             }

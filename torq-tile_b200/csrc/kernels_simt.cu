@@ -123,6 +123,7 @@ template <class LA, class LB, class Epi, bool RSUM>
 static Result run_simt(const GemmCommon &g, LA la, LB lb, Epi epi)
 {
     if (g.m == 0 || g.n == 0) return Result{kOk, 0};
+    if (g.n_replicas) return Result{kUnsupported, 0};   // output replicas are a feature of the tensor-core kernels
     const size_t gx = ceil_div(g.n, 64), gy = ceil_div(g.m, 64);
     if (gy > 65535 || gx > 0x7fffffffull) return Result{kUnsupported, 0};
     dim3 grid((unsigned)gx, (unsigned)gy);
@@ -277,7 +278,7 @@ Result simt_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size
                        float cmax)
 {
     if (g.m == 0 || g.n == 0) return Result{kOk, 0};
-    if (g.m > 65535) return Result{kUnsupported, 0};
+    if (g.m > 65535 || g.n_replicas) return Result{kUnsupported, 0};
     dim3 grid((unsigned)ceil_div(g.n, 128), (unsigned)g.m);
     cudaStream_t st = (cudaStream_t)g.stream;
     if (td == Dtype::F16)
@@ -295,7 +296,7 @@ Result launch_gemm_w4a16_unpacked(const GemmCommon &g, size_t bl, const void *sc
                                   float cmin, float cmax)
 {
     if (g.m == 0 || g.n == 0) return Result{kOk, 0};
-    if (g.m > 65535) return Result{kUnsupported, 0};
+    if (g.m > 65535 || g.n_replicas) return Result{kUnsupported, 0};
     dim3 grid((unsigned)ceil_div(g.n, 128), (unsigned)g.m);
     cudaStream_t st = (cudaStream_t)g.stream;
     if (td == Dtype::F16)

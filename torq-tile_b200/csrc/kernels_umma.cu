@@ -557,6 +557,8 @@ static bool fill_common(UmmaArgs &a, const GemmCommon &g, size_t out_elem, size_
     a.ldd = g.ldd;
     a.bias = g.bias;
     a.vec_store = ((reinterpret_cast<uintptr_t>(g.D) & 15) == 0 && ((g.ldd * out_elem) & 15) == 0) ? 1 : 0;
+    a.n_replicas = (uint32_t)(g.n_replicas > 7 ? 7 : g.n_replicas);
+    for (uint32_t i = 0; i < a.n_replicas; ++i) a.replica_delta[i] = g.replica_delta[i];
     a.fault = fault_word_device_ptr();
     a.dbg = g_timing_buffer;
     // bulk copies need 16-byte aligned sources; block sizes are multiples of 16
@@ -607,6 +609,7 @@ Result umma_gemm_i32(const GemmCommon &g, int32_t cmin, int32_t cmax)
     a.cmin_i = cmin;
     a.cmax_i = cmax;
     a.band_m = choose_band(g.m * g.k, g.n * g.k);
+    if (a.n_replicas) return Result{kUnsupported, 0};
     if (use_pair(a.m, 128)) return pair_gemm_i8(a, false, (cudaStream_t)g.stream);
     return launch_umma<BMode::I8, EpiKind::S32, Dtype::F32>(a, (cudaStream_t)g.stream);
 }
@@ -623,6 +626,7 @@ Result umma_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmi
     a.rq_scale_d = p.scale_d;
     a.rq_zp_d = p.zero_point_d;
     a.band_m = choose_band(g.m * g.k, g.n * g.k);
+    if (a.n_replicas) return Result{kUnsupported, 0};
     if (use_pair(a.m, 128)) return pair_gemm_i8(a, true, (cudaStream_t)g.stream);
     return launch_umma<BMode::I8, EpiKind::Req8, Dtype::F32>(a, (cudaStream_t)g.stream);
 }
@@ -642,6 +646,7 @@ Result umma_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float 
     cudaStream_t st = (cudaStream_t)g.stream;
     if (umma_variant() == 3) return ts_gemm_w4a8(a, td, false, st);
     if (use_pair(a.m, 96)) return ts_gemm_w4a8(a, td, true, st);
+    if (a.n_replicas) return ts_gemm_w4a8(a, td, false, st);   // only the tensor-memory kernels store replicas
     switch (td) {
         case Dtype::F32: return launch_umma<BMode::I4Cx, EpiKind::W4A8, Dtype::F32>(a, st);
         case Dtype::F16: return launch_umma<BMode::I4Cx, EpiKind::W4A8, Dtype::F16>(a, st);
@@ -664,6 +669,7 @@ Result umma_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size
     cudaStream_t st = (cudaStream_t)g.stream;
     if (umma_variant() == 3) return ts_gemm_w4a16(a, td, false, st);
     if (use_pair(a.m, 96)) return ts_gemm_w4a16(a, td, true, st);
+    if (a.n_replicas) return ts_gemm_w4a16(a, td, false, st);
     if (td == Dtype::F16) return launch_umma<BMode::I4C2, EpiKind::W4A16, Dtype::F16>(a, st);
     return launch_umma<BMode::I4C2, EpiKind::W4A16, Dtype::F32>(a, st);
 }

@@ -59,6 +59,11 @@ struct GemmCommon {
     size_t ldd;
     const void *bias;
     void *stream;
+    // Output replicas: every element stored at address x of D is also stored at x + replica_delta[i]
+    // (peer-mapped copies of the output buffer on other GPUs).  Honoured by the tensor-memory kernels
+    // of the W4A8 / W4A16 packed types; other paths report kUnsupported while replicas are set.
+    size_t n_replicas;
+    long long replica_delta[7];
 };
 
 enum class Path : int { Auto = 0, Umma = 1, Gemv = 2, Simt = 3 };

@@ -35,6 +35,8 @@ struct UmmaArgs {
     const __half *scale_blk;
     size_t ldsb;
     uint32_t bl;
+    uint32_t n_replicas;          // output replicas (see GemmCommon)
+    long long replica_delta[7];
     uint32_t band_m;  // tile order: activation-row tiles are walked in bands of this many (0 = one band)
     unsigned int *fault;
     long long *dbg;  // optional per-CTA role timing (diagnostic), 16 slots per CTA
