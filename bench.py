@@ -271,6 +271,19 @@ def run_ours(args):
         launches_per_step = 2
         dtype = "f16"
 
+    # The step's two launches replayed as one CUDA graph per weight set: the host then needs ~10 us per step
+    # instead of ~100 us of Python argument marshalling, which otherwise bounds the column shards on 2-8 GPUs.
+    eager_step, eager_gemm = step_device, gemm_only
+    if not args.no_graphs:
+        step_graphs = [L.captured(a_dev) for L in layers]
+        gemm_graphs = [L.captured(a_dev, gemm_only=True) for L in layers]
+
+        def step_device(i):   # noqa: F811
+            return step_graphs[i % R]()
+
+        def gemm_only(i):   # noqa: F811
+            return gemm_graphs[i % R]()
+
     ops = 2.0 * M * N * K               # whole job (all ranks)
     ops_local = 2.0 * M * n_local * K
     unit = "TOPS" if cfg != "c5" else "TFLOP/s"
@@ -336,6 +349,19 @@ def run_ours(args):
             finally:
                 pkg.set_output_replicas(0, [])
 
+        if not args.no_graphs:   # the fused step replayed as a graph too (the replica offsets are kernel arguments)
+            eager_fused, fused_graphs = step_fused, []
+            for li in range(R):
+                eager_fused(li)
+                torch.cuda.current_stream().synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    eager_fused(li)
+                fused_graphs.append(gr)
+
+            def step_fused(i):   # noqa: F811
+                fused_graphs[i % R].replay()
+
         ms_nccl = timed(step_nccl, g_steps, g_warm)
         ms_fused = timed(step_fused, g_steps, g_warm)
         # the two forms must agree: run step 0 both ways and compare every rank's copy of the full output
@@ -386,7 +412,8 @@ def run_ours(args):
         "value": ops / (ms_step * 1e-3) / 1e12, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype,
         "data": "synthetic",
-        "config": {"workload": desc, "step": "activation quantise+pack (or pack) kernel + run_gemm, weights packed once outside",
+        "config": {"workload": desc, "step": "activation quantise+pack (or pack) kernel + run_gemm, weights packed once outside" +
+                           ("" if args.no_graphs else "; the two launches replayed as one CUDA graph"),
                    "parallelism": f"N-sharded x{world}, no collective" if world > 1 else "single GPU",
                    "n_per_gpu": n_local,
                    "l2": f"rotating {R} weight/output sets per rank ({R * (layers[0].b_packed.numel() + out_bytes) / 1e6:.0f} MB) > 126 MB L2"},
@@ -492,6 +519,7 @@ def main():
     ap.add_argument("--rotate", type=int, default=4, help="distinct weight/output sets cycled through (defeats L2 reuse)")
     ap.add_argument("--gather", action="store_true", help="N > 1: also time the step with the full output gathered on every GPU (NCCL, and fused peer stores)")
     ap.add_argument("--sustain-s", type=float, default=1.5, help="seconds of continued step loop for clock sampling (0 = off)")
+    ap.add_argument("--no-graphs", action="store_true", help="issue the step's launches from Python instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     args = ap.parse_args()

@@ -268,3 +268,31 @@ def test_w4a16_kernels_forced(oracle, w4a8_variant, m, n, k, bl):
     want32 = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, bl, TD_F32, None, None, (-FMAX, FMAX))
     got32 = run_w4a16("f32", A.view(np.uint16), nib, sc, bl, None, None)
     _check_w4a16(got32, want32, "f32")
+
+
+@pytest.mark.parametrize("m,n", [(2048, 1792), (1500, 2600), (400, 7700)])
+def test_w4a8_wide_tile_single_wave(oracle, m, n):
+    """Shapes for which 192-row activation tiles need a second wave on 74 CTA pairs and 256-row tiles do
+    not (the per-GPU shape of the prefill config sharded 8 ways among them): the CTA-pair kernel then runs
+    one 256 x 256 tile per pair on a single accumulator.  Ragged last tiles included."""
+    k = 256
+    rng = np.random.default_rng(m + n)
+    A = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    nib, sb = oracle.quantize_b_per_channel_sym_int4(rng.normal(0, 0.02, (n, k)).astype(np.float32))
+    sa = rng.uniform(0.01, 0.05, m).astype(np.float32)
+    zp = rng.integers(-30, 30, m).astype(np.int32)
+    bias = f32_to_bf16_bits(rng.normal(0, 0.1, n).astype(np.float32))
+    want = oracle.gemm_w4a8(A, nib, sa, zp, sb, TD_BF16, None, bias, (-65504.0, 65504.0))
+    got = run_w4a8("bf16", A, sa, zp, nib, sb, None, bias)
+    assert np.array_equal(got, want)
+
+
+def test_w4a16_wide_tile_single_wave(oracle):
+    m, n, k, bl = 2048, 1792, 128, 32
+    rng = np.random.default_rng(77)
+    A = rng.normal(0, 1, (m, k)).astype(np.float16)
+    W = rng.normal(0, 0.02, (n, k)).astype(np.float16)
+    nib, sc = oracle.quantize_fp16_to_int4(W.view(np.uint16), bl)
+    want = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, bl, TD_F16, None, None)
+    got = run_w4a16("f16", A.view(np.uint16), nib, sc, bl, None, None)
+    assert rel_err(f16_bits_to_f32(got), f16_bits_to_f32(want)) < 2e-2

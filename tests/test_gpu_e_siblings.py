@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 TD_ID = {"f32": TD_F32, "f16": TD_F16, "bf16": TD_BF16}
 TD_TORCH = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
-SHAPES = [(5, 7, 16), (64, 96, 128), (130, 257, 194), (33, 140, 1026)]
+SHAPES = [(5, 7, 16), (64, 96, 128), (130, 257, 194), (33, 140, 1026), (300, 520, 640)]
 
 
 def _as_td(x, td):

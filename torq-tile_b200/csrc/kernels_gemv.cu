@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR>()) gemv_w4a8_k
     }
 }
 
-static bool pdl_enabled()
+bool pdl_enabled()
 {
     static int cached = -1;
     if (cached < 0) {

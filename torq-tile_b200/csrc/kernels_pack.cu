@@ -9,6 +9,8 @@
 
 namespace tqt {
 
+bool pdl_enabled();   // kernels_gemv.cu: programmatic dependent launch on (TQT_B200_PDL=0 switches it off)
+
 __device__ unsigned int g_device_fault = 0;
 
 unsigned int *fault_word_device_ptr()
@@ -411,6 +413,10 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
                                                                 float *__restrict__ scale_a, int32_t *__restrict__ zp_a)
 {
     static_assert(TA != Dtype::F32, "16-bit inputs only");
+    // programmatic dependent launch: the GEMM that follows may run its prologue now; this kernel itself waits
+    // for its predecessor (which may still read the packed buffer it is about to overwrite) before touching memory
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const uint32_t lane = threadIdx.x & 31u;
     const size_t row = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (row >= m) return;
@@ -550,18 +556,29 @@ Result launch_quant_qai8dx(void *stream, size_t m, size_t k, const void *A, size
                            (packed || (ldq % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0));
     if (warp_rows) {
         const unsigned wgrid = (unsigned)((m + 7) / 8);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(wgrid, 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;   // without the attribute the two griddepcontrol instructions are no-ops
+        cudaError_t e = cudaSuccess;
 #define TQT_LAUNCH_QW(TA_)                                                                                             \
     do {                                                                                                               \
         if (packed)                                                                                                    \
-            quant_qai8dx_warp_kernel<TA_, true><<<wgrid, 256, 0, st>>>(m, k, A, lda, o, ldq, kbt, scale_a, zp_a);      \
+            e = cudaLaunchKernelEx(&cfg, quant_qai8dx_warp_kernel<TA_, true>, m, k, A, lda, o, ldq, kbt, scale_a, zp_a);  \
         else                                                                                                           \
-            quant_qai8dx_warp_kernel<TA_, false><<<wgrid, 256, 0, st>>>(m, k, A, lda, o, ldq, kbt, scale_a, zp_a);     \
+            e = cudaLaunchKernelEx(&cfg, quant_qai8dx_warp_kernel<TA_, false>, m, k, A, lda, o, ldq, kbt, scale_a, zp_a); \
     } while (0)
         if (ta == Dtype::F16)
             TQT_LAUNCH_QW(Dtype::F16);
         else
             TQT_LAUNCH_QW(Dtype::BF16);
 #undef TQT_LAUNCH_QW
+        if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
         return check_launch();
     }
 #define TQT_LAUNCH_Q(TA_)                                                                                              \

@@ -227,6 +227,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                     sCol[256 + c] = (cok && args.bias) ? static_cast<const int32_t *>(args.bias)[n0 + c] : 0;
                 }
             }
+            // per-row requantisation (Mx1 bias types): this thread's row has one multiplier, shift and bias
+            int32_t row_mult = 0, row_rsh = 0, row_bias = 0;
+            if constexpr (EK == EpiKind::Req8Row) {
+                if (row_ok) {
+                    requant_column(args.rq_scale_rows[args.rq_per_tensor ? 0 : mrow], args.rq_scale_a, args.rq_scale_d, &row_mult,
+                                   &row_rsh);
+                    if (args.bias) row_bias = static_cast<const int32_t *>(args.bias)[mrow];
+                }
+            }
             __syncwarp();
             if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait))) {
                 ok = false;
@@ -254,6 +263,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                             if (args.C && j < nvalid)
                                 v = (int32_t)((uint32_t)v + (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c]);
                             out[j] = max(args.cmin_i, min(args.cmax_i, v));
+                        } else if constexpr (EK == EpiKind::Req8Row) {
+                            uint32_t u = r[j];
+                            if (args.C && j < nvalid) u += (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c];
+                            u += (uint32_t)row_bias;
+                            out[j] = (int8_t)requant_value((int32_t)u, row_mult, row_rsh, args.rq_zp_d, args.cmin_i, args.cmax_i);
                         } else {
                             uint32_t u = r[j];
                             if (args.C && j < nvalid) u += (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c];
@@ -306,17 +320,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
 // ======================================================================================================
 enum class TsKind : int { W4A8 = 0, W4A16 = 1 };
 
-constexpr uint32_t kTsMT = 192;            // activation rows per tile (MMA N); 96 per CTA in a pair
+constexpr uint32_t kTsMT = 192;            // activation rows per tile (MMA N) by default; 96 per CTA in a pair
+constexpr uint32_t kTsMTWide = 256;        // CTA pairs, launches of at most one tile per pair: one accumulator of 256 columns
 constexpr uint32_t kTsThreads = 608;       // warp 0 producer (step 0 of each group), 1 MMA, 2..9 epilogue, 10..17 converters, 18 producer (step 1)
 constexpr uint32_t kTsT = 4;               // tensor-memory operand stages (4 x 32 columns)
 
 template <TsKind KD, bool PAIR>
 struct TsCfg {
     static constexpr bool kF16 = KD == TsKind::W4A16;
-    static constexpr uint32_t NG = PAIR ? 5u : 3u;                 // shared-memory stage groups (two K steps each)
+    static constexpr uint32_t NG = PAIR ? 4u : 3u;                 // shared-memory stage groups (two K steps each)
     static constexpr uint32_t S = NG * 2u;
-    static constexpr uint32_t kActRows = PAIR ? 96u : 192u;        // activation rows this CTA stages per K step
-    static constexpr uint32_t kActBytes = kActRows * 128u;
+    static constexpr uint32_t kActRowsMax = PAIR ? 128u : 192u;    // activation rows this CTA stages per K step, at most
+    static constexpr uint32_t kActBytes = kActRowsMax * 128u;      // stage stride
     static constexpr uint32_t kNibGroupBytes = kF16 ? 8192u : 2u * 8448u;   // int4 bytes per group of two K steps
     static constexpr uint32_t kUsed = 1024u + S * kActBytes + NG * kNibGroupBytes + 2u * 2u * 128u * 4u + 512u;
     // more than half of an SM's shared memory: one CTA per SM, which owns all 512 tensor-memory columns
@@ -334,7 +349,11 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     using OutT = typename TdTraits<TD>::type;
     constexpr bool kF16 = Cfg::kF16;
     constexpr uint32_t S = Cfg::S, NG = Cfg::NG, T = kTsT;
-    constexpr uint32_t kActRows = Cfg::kActRows, kActBytes = Cfg::kActBytes;
+    constexpr uint32_t kActBytes = Cfg::kActBytes;
+    // activation rows per tile: 192 (two accumulators), or 256 for a CTA pair when the host found that every pair
+    // then gets at most one tile (one accumulator of 256 columns at column 0; the operand stages stay at 384)
+    const uint32_t mt = (PAIR && args.mt == kTsMTWide) ? kTsMTWide : kTsMT;
+    const uint32_t kActRows = PAIR ? mt / 2u : mt;          // rows this CTA stages per K step
     constexpr uint32_t kStepK = kF16 ? 64u : 128u;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -353,8 +372,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     const uint32_t bar0 = ptx::smem_u32(bars);
     auto BAR = [&](uint32_t idx) { return bar0 + idx * 8u; };
 
+    if (args.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the successor may start its own prologue
     const uint32_t tiles_m128 = (args.m + 127) / 128;          // 128-row blocks that exist in A_packed
-    const uint32_t tmc = (args.m + kTsMT - 1) / kTsMT;         // 192-row tiles of the activations
+    const uint32_t tmc = (args.m + mt - 1) / mt;               // row tiles of the activations
     const uint32_t nblocks = (args.n + 127) / 128, tnc = PAIR ? (nblocks + 1) / 2 : nblocks;
     const uint32_t num_tiles = tmc * tnc;
     const uint32_t ksteps = (args.k + kStepK - 1) / kStepK;    // K steps per tile
@@ -388,6 +408,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     ptx::tc_fence_after();
     const uint32_t tmem_base = *sTmemBase;
     const uint32_t tmem_a = tmem_base + 2 * kTsMT;   // operand stages after the two accumulators
+    // Programmatic dependent launch: barriers, tensor memory and the cluster handshake above overlap the tail of
+    // the preceding kernel (the activation quantiser); everything below reads what it produced.
+    if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     long long wcyc[3] = {0, 0, 0};
     const long long t_role0 = args.dbg ? clock64() : 0;
 
@@ -406,7 +429,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             const bool nib_valid = nb < nblocks;
             const uint8_t *nib_src = args.B + (size_t)nb * args.b_kblocks_total * (kF16 ? kI4C2BlockBytes : kI4CxBlockBytes);
             // this CTA's activation rows [a0, a0 + kActRows) = at most two pieces of 128-row blocks
-            const uint32_t a0 = tm * kTsMT + rank * 96u;
+            const uint32_t a0 = tm * mt + rank * kActRows;
             const uint32_t blk1 = a0 >> 7, off1 = a0 & 127u;
             const uint32_t rows1 = min(kActRows, 128u - off1), rows2 = kActRows - rows1;
             const bool v1 = blk1 < tiles_m128, v2 = rows2 > 0 && (blk1 + 1) < tiles_m128;
@@ -463,8 +486,8 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     } else if (warp == 1) {
         // ===================== MMA issuer (leader CTA only; the peer's warp 1 idles) =====================
         if (rank == 0) {
-            const uint32_t idesc = kF16 ? ptx::make_idesc(1u, 0u, 0u, PAIR ? 256 : 128, kTsMT)
-                                        : ptx::make_idesc(2u, 1u, 1u, PAIR ? 256 : 128, kTsMT);
+            const uint32_t idesc = kF16 ? ptx::make_idesc(1u, 0u, 0u, PAIR ? 256 : 128, mt)
+                                        : ptx::make_idesc(2u, 1u, 1u, PAIR ? 256 : 128, mt);
             uint32_t Gc = 0, ti = 0;
             bool ok = true;
             for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
@@ -474,7 +497,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                     break;
                 }
                 ptx::tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * kTsMT;
+                const uint32_t d_tmem = tmem_base + acc * mt;
                 for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc) {
                     const uint32_t gs = Gc % NG;
                     for (uint32_t h = 0; h < 2; ++h) {
@@ -534,8 +557,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
             const uint32_t n = (PAIR ? tn * 2 + rank : tn) * 128u + row;
             const bool n_ok = n < args.n;
-            const uint32_t m0 = tm * kTsMT + half * 96u;
-            const uint32_t mcols = args.m > m0 ? min(96u, args.m - m0) : 0u;
+            const uint32_t hcols = mt / 2u;   // accumulator columns (activation rows) of this warp's half
+            const uint32_t m0 = tm * mt + half * hcols;
+            const uint32_t mcols = args.m > m0 ? min(hcols, args.m - m0) : 0u;
             float sb = 0.0f;
             if constexpr (!kF16) sb = n_ok ? args.scale_b[n] : 0.0f;
             const float bv = (n_ok && args.bias) ? TdTraits<TD>::load(args.bias, n) : 0.0f;
@@ -552,7 +576,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 rs = sRsum[acc * 256 + row] + sRsum[acc * 256 + 128 + row];
             }
             ptx::tc_fence_after();
-            const uint32_t t_addr = tmem_base + acc * kTsMT + half * 96u + ((quad * 32u) << 16);
+            const uint32_t t_addr = tmem_base + acc * mt + half * hcols + ((quad * 32u) << 16);
             const uint32_t nchunks = (mcols + 31u) / 32u;
             for (uint32_t ch = 0; ch < nchunks; ++ch) {
                 const uint32_t c0 = ch * 32u;
@@ -858,10 +882,26 @@ static Result launch_grid(Kern kern, const UmmaArgs &a, uint32_t num_tiles, bool
     } else {
         grid = num_tiles < sms ? num_tiles : sms;
     }
-    kern<<<grid, threads, smem, st>>>(a);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 1 : 0;   // only kernels that execute griddepcontrol.wait set pdl
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
     return Result{kOk, 0};
+}
+
+Result pair_gemm_i8_rows(const UmmaArgs &a, cudaStream_t st)
+{
+    const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
+    static bool set_row[64] = {false};
+    return launch_grid(gemm_pair_i8_kernel<EpiKind::Req8Row>, a, tiles, true, kI8Threads, kI8Smem, st, set_row);
 }
 
 Result pair_gemm_i8(const UmmaArgs &a, bool requant, cudaStream_t st)
@@ -873,10 +913,21 @@ Result pair_gemm_i8(const UmmaArgs &a, bool requant, cudaStream_t st)
 }
 
 template <TsKind KD, Dtype TD>
-static Result launch_ts(const UmmaArgs &a, bool pair, cudaStream_t st)
+static Result launch_ts(const UmmaArgs &a_in, bool pair, cudaStream_t st)
 {
-    const uint32_t nblocks = (a.n + 127) / 128;
-    const uint32_t tiles = ((a.m + kTsMT - 1) / kTsMT) * (pair ? (nblocks + 1) / 2 : nblocks);
+    const uint32_t nblocks = (a_in.n + 127) / 128;
+    // a CTA pair may take 256 activation rows per tile when that makes the launch a single wave (every pair at
+    // most one tile) and 192-row tiles would need a second one: sharded shapes such as 2048 x 1792 on 74 pairs
+    UmmaArgs a = a_in;
+    uint32_t mt = kTsMT;
+    if (pair) {
+        const uint32_t tnc = (nblocks + 1) / 2, pairs = (uint32_t)sm_count_cached() / 2;
+        const uint32_t t192 = ((a.m + kTsMT - 1) / kTsMT) * tnc, t256 = ((a.m + kTsMTWide - 1) / kTsMTWide) * tnc;
+        if (t192 > pairs && t256 <= pairs) mt = kTsMTWide;
+    }
+    a.mt = mt;
+    a.pdl = pdl_enabled() ? 1 : 0;
+    const uint32_t tiles = ((a.m + mt - 1) / mt) * (pair ? (nblocks + 1) / 2 : nblocks);
     static bool set_p[64] = {false}, set_s[64] = {false};
     if (pair) return launch_grid(gemm_ts_pair_kernel<KD, TD>, a, tiles, true, kTsThreads, TsCfg<KD, true>::kSmem, st, set_p);
     return launch_grid(gemm_ts_kernel<KD, TD>, a, tiles, false, kTsThreads, TsCfg<KD, false>::kSmem, st, set_s);

@@ -199,9 +199,16 @@ Result launch_gemm_requant_i8_layouts(const GemmCommon &g, const RequantParams &
     return run_simt_layouts<EpiRequant, false>(g, la, lb, epi);
 }
 
+Result umma_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &p, int cmin, int cmax);
+
 Result launch_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &p, int cmin, int cmax, Layout la,
                                    Layout lb)
 {
+    // both operands packed: tensor cores (TQT_B200_PATH=simt keeps the generic kernel, for cross-checks)
+    if (la == Layout::Packed && lb == Layout::Packed && g.m && g.n && g.k && env_path() != Path::Simt) {
+        Result r = umma_gemm_requant_rows_i8(g, p, cmin, cmax);
+        if (r.status != kUnsupported) return r;
+    }
     EpiRequantRow epi{(const int32_t *)g.C, g.ldc, (const int32_t *)g.bias, (int8_t *)g.D, g.ldd, p.scale_a,
                       p.quant_channel_a, p.scale_b, p.scale_d, p.zero_point_d, cmin, cmax};
     return run_simt_layouts<EpiRequantRow, false>(g, la, lb, epi);

@@ -631,6 +631,25 @@ Result umma_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmi
     return launch_umma<BMode::I8, EpiKind::Req8, Dtype::F32>(a, (cudaStream_t)g.stream);
 }
 
+Result pair_gemm_i8_rows(const UmmaArgs &a, cudaStream_t st);
+
+// Mx1-bias requantising GEMM on packed operands: the CTA-pair kernel with a per-row epilogue (any m).
+Result umma_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &p, int cmin, int cmax)
+{
+    UmmaArgs a{};
+    if (!fill_common(a, g, 1, 128, 128)) return Result{kUnsupported, 0};
+    if (a.n_replicas) return Result{kUnsupported, 0};
+    a.cmin_i = cmin;
+    a.cmax_i = cmax;
+    a.rq_scale_rows = p.scale_a;
+    a.rq_per_tensor = p.quant_channel_a == 1;
+    a.rq_scale_a = p.scale_b;
+    a.rq_scale_d = p.scale_d;
+    a.rq_zp_d = p.zero_point_d;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k);
+    return pair_gemm_i8_rows(a, (cudaStream_t)g.stream);
+}
+
 Result umma_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
 {
     UmmaArgs a{};

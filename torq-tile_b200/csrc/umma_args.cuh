@@ -6,7 +6,7 @@
 namespace tqt {
 
 enum class BMode : int { I8 = 0, I4Cx = 1, I4C2 = 2 };
-enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3 };
+enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3, Req8Row = 4 };
 
 struct UmmaArgs {
     uint32_t m, n, k;
@@ -25,6 +25,7 @@ struct UmmaArgs {
     float rq_scale_a;
     const float *scale_b;  // requant: per channel; W4A8: per channel
     int rq_per_tensor;
+    const float *rq_scale_rows;  // per-row requant (Mx1 bias types): scale_a[m]; rq_scale_a then holds scale_b
     float rq_scale_d;
     int32_t rq_zp_d;
     // W4A8
@@ -37,6 +38,8 @@ struct UmmaArgs {
     uint32_t bl;
     uint32_t n_replicas;          // output replicas (see GemmCommon)
     long long replica_delta[7];
+    int pdl;          // launched with programmatic stream serialisation: wait for the preceding kernel after the prologue
+    uint32_t mt;      // tensor-memory kernels: activation rows per tile (0 = default)
     uint32_t band_m;  // tile order: activation-row tiles are walked in bands of this many (0 = one band)
     unsigned int *fault;
     long long *dbg;  // optional per-CTA role timing (diagnostic), 16 slots per CTA
@@ -68,6 +71,8 @@ struct OutType<EpiKind::S32, TD> { using type = int32_t; };
 template <Dtype TD>
 struct OutType<EpiKind::Req8, TD> { using type = int8_t; };
 template <Dtype TD>
+struct OutType<EpiKind::Req8Row, TD> { using type = int8_t; };
+template <Dtype TD>
 struct OutType<EpiKind::W4A8, TD> { using type = typename TdTraits<TD>::type; };
 template <Dtype TD>
 struct OutType<EpiKind::W4A16, TD> { using type = typename TdTraits<TD>::type; };
@@ -82,6 +87,7 @@ template <>
 __device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 long long *timing_buffer();
+bool pdl_enabled();   // programmatic dependent launch on (TQT_B200_PDL=0 switches it off)
 int sm_count_cached();
 
 }  // namespace tqt

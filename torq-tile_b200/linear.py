@@ -28,6 +28,33 @@ class _HostPipelined:
     Both host tensors must be pinned.  ``prepare`` is the operator's quantise+pack or pack step.
     """
 
+    def captured(self, A, gemm_only=False):
+        """A callable that replays, on the current stream, a CUDA graph of ``prepare(A)`` + ``gemm`` (or of
+        the GEMM alone) for this very input tensor: the per-call host work (argument marshalling, two
+        launches) drops to one graph launch, which matters once a call takes less GPU time than the host
+        needs to issue it (column shards on several GPUs).  The result is the workspace's output tensor,
+        available as ``.out`` on the callable.  A must stay alive and in place."""
+        m = A.shape[0]
+        key = ("captured", A.data_ptr(), m, bool(gemm_only))
+        fn = self._ws.get(key)
+        if fn is None:
+            self.prepare(A)          # allocates the workspace, leaves a valid packed A for a GEMM-only graph
+            out = self.gemm(m)
+            torch.cuda.current_stream().synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                if not gemm_only:
+                    self.prepare(A)
+                self.gemm(m)
+
+            def fn():
+                g.replay()
+                return out
+            fn.out = out
+            fn.graph = g
+            self._ws[key] = fn
+        return fn
+
     def _pipe(self, m, chunks, in_dtype):
         key = ("pipe", m, chunks)
         st = self._ws.get(key)
