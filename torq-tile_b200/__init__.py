@@ -18,7 +18,7 @@ import os
 import struct
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libtorq_tile_b200.so")
+LIB_PATH = os.environ.get("TQT_B200_LIB") or os.path.join(HERE, "libtorq_tile_b200.so")   # override: A/B comparisons of builds
 VARIANT = "128x128_sm100a"
 
 _sz, _vp = C.c_size_t, C.c_void_p

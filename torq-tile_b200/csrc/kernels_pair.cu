@@ -25,6 +25,7 @@
 //
 // Reference semantics of the epilogues: see kernels_umma.cu.
 #include <cstdlib>
+#include <type_traits>
 
 #include "epilogues.cuh"
 #include "ptx_sm100.cuh"
@@ -325,13 +326,16 @@ constexpr uint32_t kTsMTWide = 256;        // CTA pairs, launches of at most one
 constexpr uint32_t kTsThreads = 608;       // warp 0 producer (step 0 of each group), 1 MMA, 2..9 epilogue, 10..17 converters, 18 producer (step 1)
 constexpr uint32_t kTsT = 4;               // tensor-memory operand stages (4 x 32 columns)
 
-template <TsKind KD, bool PAIR>
+// WIDE (CTA pairs only): 256 activation rows per tile on one accumulator, for launches of at most one tile per pair.
+template <TsKind KD, bool PAIR, bool WIDE>
 struct TsCfg {
+    static_assert(PAIR || !WIDE, "the wide tile exists for CTA pairs only");
     static constexpr bool kF16 = KD == TsKind::W4A16;
-    static constexpr uint32_t NG = PAIR ? 4u : 3u;                 // shared-memory stage groups (two K steps each)
+    static constexpr uint32_t kMT = WIDE ? kTsMTWide : kTsMT;      // activation rows per tile (MMA N)
+    static constexpr uint32_t NG = PAIR ? (WIDE ? 4u : 5u) : 3u;   // shared-memory stage groups (two K steps each)
     static constexpr uint32_t S = NG * 2u;
-    static constexpr uint32_t kActRowsMax = PAIR ? 128u : 192u;    // activation rows this CTA stages per K step, at most
-    static constexpr uint32_t kActBytes = kActRowsMax * 128u;      // stage stride
+    static constexpr uint32_t kActRows = PAIR ? kMT / 2u : kMT;    // activation rows this CTA stages per K step
+    static constexpr uint32_t kActBytes = kActRows * 128u;         // stage stride
     static constexpr uint32_t kNibGroupBytes = kF16 ? 8192u : 2u * 8448u;   // int4 bytes per group of two K steps
     static constexpr uint32_t kUsed = 1024u + S * kActBytes + NG * kNibGroupBytes + 2u * 2u * 128u * 4u + 512u;
     // more than half of an SM's shared memory: one CTA per SM, which owns all 512 tensor-memory columns
@@ -342,18 +346,20 @@ struct TsCfg {
 // columns per weight row either way.  Steps are handled in groups of two: one tcgen05.commit per group
 // releases two shared-memory stages and two tensor-memory operand stages (a commit after MMAs that
 // read their M-side operand from tensor memory drains the MMA pipeline, so they are kept rare).
-template <TsKind KD, Dtype TD, bool PAIR>
+// REPL: the epilogue also stores into the output replicas (fused all-gather).  A separate instantiation: with the
+// replica stores compiled into the common kernel, even as a branch never taken, every launch ran 10 % slower
+// (code size: the strip loop is unrolled 32 times).
+template <TsKind KD, Dtype TD, bool PAIR, bool WIDE, bool REPL>
 __device__ __forceinline__ void ts_body(const UmmaArgs &args)
 {
-    using Cfg = TsCfg<KD, PAIR>;
+    using Cfg = TsCfg<KD, PAIR, WIDE>;
     using OutT = typename TdTraits<TD>::type;
     constexpr bool kF16 = Cfg::kF16;
     constexpr uint32_t S = Cfg::S, NG = Cfg::NG, T = kTsT;
     constexpr uint32_t kActBytes = Cfg::kActBytes;
     // activation rows per tile: 192 (two accumulators), or 256 for a CTA pair when the host found that every pair
     // then gets at most one tile (one accumulator of 256 columns at column 0; the operand stages stay at 384)
-    const uint32_t mt = (PAIR && args.mt == kTsMTWide) ? kTsMTWide : kTsMT;
-    const uint32_t kActRows = PAIR ? mt / 2u : mt;          // rows this CTA stages per K step
+    constexpr uint32_t mt = Cfg::kMT, kActRows = Cfg::kActRows;
     constexpr uint32_t kStepK = kF16 ? 64u : 128u;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -549,6 +555,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
         // shuffles, so the epilogue makes no shared-memory reads that would queue behind the MMA's.
         const uint32_t quad = warp & 3u, half = (warp - 2u) >> 2;
         const uint32_t row = quad * 32u + lane;             // weight row inside this CTA's block
+        constexpr bool replicate = REPL;
         uint32_t ti = 0;
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
@@ -594,27 +601,32 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 ptx::tmem_wait_ld();
                 if (args.dbg) wcyc[2] += clock64() - tl0;
                 OutT *dcol = static_cast<OutT *>(args.D) + (size_t)(m0 + c0) * args.ldd + n;
+                {
+                    constexpr bool kRepl = replicate;
 #pragma unroll
-                for (uint32_t j = 0; j < 32; ++j) {
-                    float v;
-                    if constexpr (!kF16) {
-                        const float sa = __shfl_sync(0xffffffffu, sa_l, j);
-                        const int32_t zp = __shfl_sync(0xffffffffu, zp_l, j);
-                        // operands were 16*q: the accumulator is an exact multiple of 16
-                        const int32_t a = (((int32_t)r[j]) >> 4) - zp * rs;
-                        v = __fmul_rn(__fmul_rn(__int2float_rn(a), sa), sb);
-                    } else {
-                        v = __uint_as_float(r[j]);
-                    }
-                    if (n_ok && j < nvalid) {
-                        if (args.C) v = __fadd_rn(v, TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n));
-                        if (args.bias) v = __fadd_rn(v, bv);
-                        v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
-                        const OutT o = cvt_out<OutT>(v);
-                        OutT *dst = dcol + (size_t)j * args.ldd;
-                        *dst = o;   // the warp writes 32 consecutive channels
-                        for (uint32_t rp = 0; rp < args.n_replicas; ++rp)   // peer-mapped copies of the output
-                            *reinterpret_cast<OutT *>(reinterpret_cast<char *>(dst) + args.replica_delta[rp]) = o;
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        float v;
+                        if constexpr (!kF16) {
+                            const float sa = __shfl_sync(0xffffffffu, sa_l, j);
+                            const int32_t zp = __shfl_sync(0xffffffffu, zp_l, j);
+                            // operands were 16*q: the accumulator is an exact multiple of 16
+                            const int32_t a = (((int32_t)r[j]) >> 4) - zp * rs;
+                            v = __fmul_rn(__fmul_rn(__int2float_rn(a), sa), sb);
+                        } else {
+                            v = __uint_as_float(r[j]);
+                        }
+                        if (n_ok && j < nvalid) {
+                            if (args.C) v = __fadd_rn(v, TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n));
+                            if (args.bias) v = __fadd_rn(v, bv);
+                            v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
+                            const OutT o = cvt_out<OutT>(v);
+                            OutT *dst = dcol + (size_t)j * args.ldd;
+                            *dst = o;   // the warp writes 32 consecutive channels
+                            if constexpr (kRepl) {
+                                for (uint32_t rp = 0; rp < args.n_replicas; ++rp)
+                                    *reinterpret_cast<OutT *>(reinterpret_cast<char *>(dst) + args.replica_delta[rp]) = o;
+                            }
+                        }
                     }
                 }
             }
@@ -844,17 +856,17 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     }
 }
 
-template <TsKind KD, Dtype TD>
+template <TsKind KD, Dtype TD, bool WIDE, bool REPL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1) gemm_ts_pair_kernel(const UmmaArgs args)
 {
-    ts_body<KD, TD, true>(args);
+    ts_body<KD, TD, true, WIDE, REPL>(args);
 }
 
 // Same kernel on one CTA (cta_group::1): the CTA stages all 192 activation rows itself.
 template <TsKind KD, Dtype TD>
 __global__ void __launch_bounds__(kTsThreads, 1) gemm_ts_kernel(const UmmaArgs args)
 {
-    ts_body<KD, TD, false>(args);
+    ts_body<KD, TD, false, false, false>(args);
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
@@ -928,9 +940,16 @@ static Result launch_ts(const UmmaArgs &a_in, bool pair, cudaStream_t st)
     a.mt = mt;
     a.pdl = pdl_enabled() ? 1 : 0;
     const uint32_t tiles = ((a.m + mt - 1) / mt) * (pair ? (nblocks + 1) / 2 : nblocks);
-    static bool set_p[64] = {false}, set_s[64] = {false};
-    if (pair) return launch_grid(gemm_ts_pair_kernel<KD, TD>, a, tiles, true, kTsThreads, TsCfg<KD, true>::kSmem, st, set_p);
-    return launch_grid(gemm_ts_kernel<KD, TD>, a, tiles, false, kTsThreads, TsCfg<KD, false>::kSmem, st, set_s);
+    static bool set_p[64] = {false}, set_s[64] = {false}, set_w[64] = {false}, set_pr[64] = {false}, set_wr[64] = {false};
+    constexpr uint32_t kSmemN = TsCfg<KD, true, false>::kSmem, kSmemW = TsCfg<KD, true, true>::kSmem;
+    if (a.n_replicas) {   // output replicas: CTA-pair kernels only
+        if (!pair) return Result{kUnsupported, 0};
+        if (mt == kTsMTWide) return launch_grid(gemm_ts_pair_kernel<KD, TD, true, true>, a, tiles, true, kTsThreads, kSmemW, st, set_wr);
+        return launch_grid(gemm_ts_pair_kernel<KD, TD, false, true>, a, tiles, true, kTsThreads, kSmemN, st, set_pr);
+    }
+    if (pair && mt == kTsMTWide) return launch_grid(gemm_ts_pair_kernel<KD, TD, true, false>, a, tiles, true, kTsThreads, kSmemW, st, set_w);
+    if (pair) return launch_grid(gemm_ts_pair_kernel<KD, TD, false, false>, a, tiles, true, kTsThreads, kSmemN, st, set_p);
+    return launch_grid(gemm_ts_kernel<KD, TD>, a, tiles, false, kTsThreads, TsCfg<KD, false, false>::kSmem, st, set_s);
 }
 
 Result ts_gemm_w4a8(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st)

@@ -665,7 +665,7 @@ Result umma_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float 
     cudaStream_t st = (cudaStream_t)g.stream;
     if (umma_variant() == 3) return ts_gemm_w4a8(a, td, false, st);
     if (use_pair(a.m, 96)) return ts_gemm_w4a8(a, td, true, st);
-    if (a.n_replicas) return ts_gemm_w4a8(a, td, false, st);   // only the tensor-memory kernels store replicas
+    if (a.n_replicas) return ts_gemm_w4a8(a, td, true, st);   // only the CTA-pair tensor-memory kernels store replicas
     switch (td) {
         case Dtype::F32: return launch_umma<BMode::I4Cx, EpiKind::W4A8, Dtype::F32>(a, st);
         case Dtype::F16: return launch_umma<BMode::I4Cx, EpiKind::W4A8, Dtype::F16>(a, st);
@@ -688,7 +688,7 @@ Result umma_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size
     cudaStream_t st = (cudaStream_t)g.stream;
     if (umma_variant() == 3) return ts_gemm_w4a16(a, td, false, st);
     if (use_pair(a.m, 96)) return ts_gemm_w4a16(a, td, true, st);
-    if (a.n_replicas) return ts_gemm_w4a16(a, td, false, st);
+    if (a.n_replicas) return ts_gemm_w4a16(a, td, true, st);
     if (td == Dtype::F16) return launch_umma<BMode::I4C2, EpiKind::W4A16, Dtype::F16>(a, st);
     return launch_umma<BMode::I4C2, EpiKind::W4A16, Dtype::F32>(a, st);
 }
