@@ -419,6 +419,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     long long wcyc[3] = {0, 0, 0};
     const long long t_role0 = args.dbg ? clock64() : 0;
+    bool conv_failed = false;   // a converter warp whose waits ran out does not help with the epilogue
 
     if (warp == 0 || warp == 18) {
         // ===================== producers (both CTAs) =====================
@@ -548,99 +549,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 }
             }
         }
-    } else if (warp < 10) {
-        // ===================== epilogue (8 warps per CTA): D^T, lane = output channel ==================
-        // Per-channel values (scale_b, bias, row sum) are per-thread constants; the per-row values
-        // (scale_a, zero_point_a) of a 32-column strip are loaded one per lane and broadcast with
-        // shuffles, so the epilogue makes no shared-memory reads that would queue behind the MMA's.
-        const uint32_t quad = warp & 3u, half = (warp - 2u) >> 2;
-        const uint32_t row = quad * 32u + lane;             // weight row inside this CTA's block
-        constexpr bool replicate = REPL;
-        uint32_t ti = 0;
-        bool ok = true;
-        for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
-            uint32_t tm, tn;
-            tile_coords(t, tmc, tnc, args.band_m, tm, tn);
-            const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
-            const uint32_t n = (PAIR ? tn * 2 + rank : tn) * 128u + row;
-            const bool n_ok = n < args.n;
-            const uint32_t hcols = mt / 2u;   // accumulator columns (activation rows) of this warp's half
-            const uint32_t m0 = tm * mt + half * hcols;
-            const uint32_t mcols = args.m > m0 ? min(hcols, args.m - m0) : 0u;
-            float sb = 0.0f;
-            if constexpr (!kF16) sb = n_ok ? args.scale_b[n] : 0.0f;
-            const float bv = (n_ok && args.bias) ? TdTraits<TD>::load(args.bias, n) : 0.0f;
-            if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait))) {
-                ok = false;
-                break;
-            }
-            int32_t rs = 0;
-            if constexpr (!kF16) {
-                if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kRsumFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait))) {
-                    ok = false;
-                    break;
-                }
-                rs = sRsum[acc * 256 + row] + sRsum[acc * 256 + 128 + row];
-            }
-            ptx::tc_fence_after();
-            const uint32_t t_addr = tmem_base + acc * mt + half * hcols + ((quad * 32u) << 16);
-            const uint32_t nchunks = (mcols + 31u) / 32u;
-            for (uint32_t ch = 0; ch < nchunks; ++ch) {
-                const uint32_t c0 = ch * 32u;
-                const uint32_t nvalid = min(32u, mcols - c0);
-                float sa_l = 0.0f;
-                int32_t zp_l = 0;
-                if constexpr (!kF16) {
-                    sa_l = lane < nvalid ? __ldg(args.scale_a + m0 + c0 + lane) : 0.0f;
-                    zp_l = lane < nvalid ? __ldg(args.zp_a + m0 + c0 + lane) : 0;
-                }
-                uint32_t r[32];
-                __syncwarp();
-                const long long tl0 = args.dbg ? clock64() : 0;
-                ptx::tmem_ld_32x32b_x32(t_addr + c0, r);
-                ptx::tmem_wait_ld();
-                if (args.dbg) wcyc[2] += clock64() - tl0;
-                OutT *dcol = static_cast<OutT *>(args.D) + (size_t)(m0 + c0) * args.ldd + n;
-                {
-                    constexpr bool kRepl = replicate;
-#pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) {
-                        float v;
-                        if constexpr (!kF16) {
-                            const float sa = __shfl_sync(0xffffffffu, sa_l, j);
-                            const int32_t zp = __shfl_sync(0xffffffffu, zp_l, j);
-                            // operands were 16*q: the accumulator is an exact multiple of 16
-                            const int32_t a = (((int32_t)r[j]) >> 4) - zp * rs;
-                            v = __fmul_rn(__fmul_rn(__int2float_rn(a), sa), sb);
-                        } else {
-                            v = __uint_as_float(r[j]);
-                        }
-                        if (n_ok && j < nvalid) {
-                            if (args.C) v = __fadd_rn(v, TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n));
-                            if (args.bias) v = __fadd_rn(v, bv);
-                            v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
-                            const OutT o = cvt_out<OutT>(v);
-                            OutT *dst = dcol + (size_t)j * args.ldd;
-                            *dst = o;   // the warp writes 32 consecutive channels
-                            if constexpr (kRepl) {
-                                for (uint32_t rp = 0; rp < args.n_replicas; ++rp)
-                                    *reinterpret_cast<OutT *>(reinterpret_cast<char *>(dst) + args.replica_delta[rp]) = o;
-                            }
-                        }
-                    }
-                }
-            }
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if (rank == 0)
-                    ptx::mbar_arrive(BAR(kTmemEmpty + acc));
-                else
-                    ptx::mbar_arrive_cluster(ptx::mapa(BAR(kTmemEmpty + acc), 0));
-                if constexpr (!kF16) ptx::mbar_arrive(BAR(kRsumEmpty + acc));
-            }
-        }
-    } else {
+    } else if (warp >= 10) {
         // ===================== converters (warps 10..17): int4 -> MMA operand type, into tensor memory ========
         // Two warps per tensor-memory lane quadrant: set 0 (warps 10..13) takes step 0 of every group, set 1
         // (warps 14..17) step 1.  A step is fetched and expanded into registers before the warp waits for its
@@ -833,6 +742,114 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 sRsum[acc * 256 + cset * 128 + row] = rsum;
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(BAR(kRsumFull + acc));
+            }
+        }
+        conv_failed = !ok;
+    }
+
+    if (warp >= 2 && warp < 18 && !conv_failed) {
+        // ===================== epilogue (8 warps per CTA): D^T, lane = output channel ==================
+        // The converter warps, idle once the last K step of their last tile is in tensor memory, come here
+        // too and take the upper half of that tile's column strips: the epilogue of the last tile overlaps no
+        // mainloop (it is the whole tail of a launch, and half of a single-wave launch), so it is spread over
+        // sixteen warps instead of eight.  Warp w and helper warp w + 8 share a lane quadrant and a column half.
+        // Per-channel values (scale_b, bias, row sum) are per-thread constants; the per-row values
+        // (scale_a, zero_point_a) of a 32-column strip are loaded one per lane and broadcast with
+        // shuffles, so the epilogue makes no shared-memory reads that would queue behind the MMA's.
+        const bool helper = warp >= 10;
+        const uint32_t ew = helper ? warp - 8u : warp;
+        const uint32_t quad = ew & 3u, half = (ew - 2u) >> 2;
+        const uint32_t row = quad * 32u + lane;             // weight row inside this CTA's block
+        constexpr bool replicate = REPL;
+        const uint32_t my_tiles = pair < num_tiles ? (num_tiles - pair + npairs - 1) / npairs : 0u;
+        uint32_t ti = helper ? (my_tiles ? my_tiles - 1u : 0u) : 0u;   // helpers: the last tile only
+        bool ok = true;
+        for (uint32_t t = pair + ti * npairs; t < num_tiles && ok; t += npairs, ++ti) {
+            const bool last = ti + 1u == my_tiles;
+            uint32_t tm, tn;
+            tile_coords(t, tmc, tnc, args.band_m, tm, tn);
+            const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
+            const uint32_t n = (PAIR ? tn * 2 + rank : tn) * 128u + row;
+            const bool n_ok = n < args.n;
+            const uint32_t hcols = mt / 2u;   // accumulator columns (activation rows) of this warp's half
+            const uint32_t m0 = tm * mt + half * hcols;
+            const uint32_t mcols = args.m > m0 ? min(hcols, args.m - m0) : 0u;
+            float sb = 0.0f;
+            if constexpr (!kF16) sb = n_ok ? args.scale_b[n] : 0.0f;
+            const float bv = (n_ok && args.bias) ? TdTraits<TD>::load(args.bias, n) : 0.0f;
+            if (!(helper ? ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)
+                         : TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)))) {
+                ok = false;
+                break;
+            }
+            int32_t rs = 0;
+            if constexpr (!kF16) {
+                if (!(helper ? ptx::mbar_wait(BAR(kRsumFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)
+                             : TQT_PTIMED(1, ptx::mbar_wait(BAR(kRsumFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)))) {
+                    ok = false;
+                    break;
+                }
+                rs = sRsum[acc * 256 + row] + sRsum[acc * 256 + 128 + row];
+            }
+            ptx::tc_fence_after();
+            const uint32_t t_addr = tmem_base + acc * mt + half * hcols + ((quad * 32u) << 16);
+            const uint32_t nchunks = (mcols + 31u) / 32u;
+            // the last tile's strips are split between this warp and its helper
+            const uint32_t split = (nchunks + 1u) / 2u;
+            const uint32_t ch_begin = helper ? split : 0u, ch_end = (last && !helper) ? split : nchunks;
+            for (uint32_t ch = ch_begin; ch < ch_end; ++ch) {
+                const uint32_t c0 = ch * 32u;
+                const uint32_t nvalid = min(32u, mcols - c0);
+                float sa_l = 0.0f;
+                int32_t zp_l = 0;
+                if constexpr (!kF16) {
+                    sa_l = lane < nvalid ? __ldg(args.scale_a + m0 + c0 + lane) : 0.0f;
+                    zp_l = lane < nvalid ? __ldg(args.zp_a + m0 + c0 + lane) : 0;
+                }
+                uint32_t r[32];
+                __syncwarp();
+                const long long tl0 = args.dbg ? clock64() : 0;
+                ptx::tmem_ld_32x32b_x32(t_addr + c0, r);
+                ptx::tmem_wait_ld();
+                if (args.dbg) wcyc[2] += clock64() - tl0;
+                OutT *dcol = static_cast<OutT *>(args.D) + (size_t)(m0 + c0) * args.ldd + n;
+                {
+                    constexpr bool kRepl = replicate;
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        float v;
+                        if constexpr (!kF16) {
+                            const float sa = __shfl_sync(0xffffffffu, sa_l, j);
+                            const int32_t zp = __shfl_sync(0xffffffffu, zp_l, j);
+                            // operands were 16*q: the accumulator is an exact multiple of 16
+                            const int32_t a = (((int32_t)r[j]) >> 4) - zp * rs;
+                            v = __fmul_rn(__fmul_rn(__int2float_rn(a), sa), sb);
+                        } else {
+                            v = __uint_as_float(r[j]);
+                        }
+                        if (n_ok && j < nvalid) {
+                            if (args.C) v = __fadd_rn(v, TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n));
+                            if (args.bias) v = __fadd_rn(v, bv);
+                            v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
+                            const OutT o = cvt_out<OutT>(v);
+                            OutT *dst = dcol + (size_t)j * args.ldd;
+                            *dst = o;   // the warp writes 32 consecutive channels
+                            if constexpr (kRepl) {
+                                for (uint32_t rp = 0; rp < args.n_replicas; ++rp)
+                                    *reinterpret_cast<OutT *>(reinterpret_cast<char *>(dst) + args.replica_delta[rp]) = o;
+                            }
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0 && !helper) {   // nobody waits for these after the last tile; helpers never arrive
+                if (rank == 0)
+                    ptx::mbar_arrive(BAR(kTmemEmpty + acc));
+                else
+                    ptx::mbar_arrive_cluster(ptx::mapa(BAR(kTmemEmpty + acc), 0));
+                if constexpr (!kF16) ptx::mbar_arrive(BAR(kRsumEmpty + acc));
             }
         }
     }
