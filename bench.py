@@ -404,7 +404,7 @@ def run_ours(args):
                "sample": f"{rows} of {M} rows x all N x K in {secs:.1f} s, oracle/tqt_oracle.c with {nthreads} OpenMP threads"}
 
     # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch, from the ncu captures summarised under profiles/
-    ncu_traffic = {"c3": 55.86e6, "c4": 33.78e6, "c5": None}[cfg] if world == 1 else None
+    ncu_traffic = {"c3": 56.2e6, "c4": 33.9e6, "c5": 1419.1e6}[cfg] if world == 1 else None
     int8_peak = 2.0 * peaks["bf16_sustained"] if cfg != "c5" else peaks["bf16_sustained"]
     achieved = ops_local / (ms_gemm * 1e-3) / 1e12
     line = {

@@ -48,3 +48,23 @@ def test_requant_forward_host_matches_device_call():
         want = layer(a_host.to(DEV)).cpu()
         sync_and_check()
         assert torch.equal(out_host, want)
+
+
+def test_captured_graph_matches_eager_call(oracle):
+    """captured(A): CUDA-graph replay of prepare + run_gemm (and of run_gemm alone) on new contents of A."""
+    lin = load_linear()
+    rng = np.random.default_rng(11)
+    m, n, k = 300, 384, 512
+    nib, sb = oracle.quantize_b_per_channel_sym_int4(rng.normal(0, 0.02, (n, k)).astype(np.float32))
+    layer = lin.W4A8Linear(to_dev(nib), to_dev(sb), k, "bf16")
+    a = torch.empty((m, k), dtype=torch.bfloat16, device=DEV)
+    step = layer.captured(a)
+    gemm = layer.captured(a, gemm_only=True)
+    for _ in range(3):
+        a.copy_(torch.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32)).to(torch.bfloat16))
+        got = step().clone()
+        again = gemm().clone()      # the packed activations of the step are still in the workspace
+        want = layer(a).clone()
+        sync_and_check()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+        assert torch.equal(again.view(torch.int16), want.view(torch.int16))
