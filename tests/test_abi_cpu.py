@@ -131,3 +131,22 @@ def test_status_word_without_gpu(pkg):
     assert pkg.lib().tqt_cuda_get_last_status() == 0
     assert pkg.lib().tqt_cuda_kernel_choice_w4a8(1, 4096, 4096) == 1
     assert pkg.lib().tqt_cuda_kernel_choice_w4a8(2048, 14336, 4096) == 0
+
+
+def test_output_replicas_argument_checks(pkg):
+    """tqt_cuda_set_output_replicas is host-side state: more than 7 replicas or missing pointers are refused,
+    an empty list clears it (no GPU needed)."""
+    import ctypes as C
+    lib = pkg.lib()
+    f = lib.tqt_cuda_set_output_replicas
+    f.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t]
+    f.restype = None
+    arr = (C.c_void_p * 8)(*[C.c_void_p(4096 * (i + 2)) for i in range(8)])
+    f(C.c_void_p(4096), arr, 8)
+    assert lib.tqt_cuda_get_last_status() != 0
+    f(None, arr, 2)
+    assert lib.tqt_cuda_get_last_status() != 0
+    f(C.c_void_p(4096), arr, 7)
+    assert lib.tqt_cuda_get_last_status() == 0
+    f(None, None, 0)
+    assert lib.tqt_cuda_get_last_status() == 0
