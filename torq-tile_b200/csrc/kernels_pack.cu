@@ -39,7 +39,7 @@ static inline Result check_launch()
 // One thread per 16-byte chunk of the destination.  grid.x covers chunks, ES = element size.
 template <int ES, bool TRANSPOSED>
 __global__ void pack_rows_kernel(size_t rows, size_t k, size_t ld_src, size_t kblocks_total, const uint8_t *__restrict__ src,
-                                 uint8_t *__restrict__ dst, size_t kblocks, size_t total_chunks)
+                                 uint8_t *__restrict__ dst, size_t kblocks, size_t total_chunks, size_t block_bytes)
 {
     constexpr uint32_t EPC = 16 / ES;          // elements per 16-byte chunk
     constexpr uint32_t KPB = 128 / ES;         // k elements per block row
@@ -73,7 +73,7 @@ __global__ void pack_rows_kernel(size_t rows, size_t k, size_t ld_src, size_t kb
                 for (int b = 0; b < ES; ++b) v[e * ES + b] = ok ? src[off * ES + b] : (uint8_t)0;
             }
         }
-        uint8_t *blk_base = dst + (tile * kblocks_total + kb) * kI8BlockBytes;
+        uint8_t *blk_base = dst + (tile * kblocks_total + kb) * block_bytes;
         *reinterpret_cast<uint4 *>(blk_base + sw128_byte(r, c * 16)) = *reinterpret_cast<const uint4 *>(v);
     }
 }
@@ -95,8 +95,49 @@ __global__ void unpack_rows_kernel(size_t rows, size_t k, size_t kblocks_total, 
     }
 }
 
+// One thread per (block, row): the int16 sum of the row's 128 int8 values (the swizzle permutes inside a row only).
+__global__ void block_row_sums_kernel(uint8_t *__restrict__ packed, size_t tiles, size_t kblocks, size_t kblocks_total)
+{
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= tiles * kblocks * 128) return;
+    const uint32_t r = (uint32_t)(idx & 127);
+    const size_t blk = idx >> 7, kb = blk % kblocks, tile = blk / kblocks;
+    uint8_t *base = packed + (tile * kblocks_total + kb) * kI8SumBlockBytes;
+    int32_t sum = 0;
+#pragma unroll
+    for (uint32_t c = 0; c < 8; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4 *>(base + r * 128u + c * 16u);
+        sum = __dp4a((int)v.x, 0x01010101, sum);
+        sum = __dp4a((int)v.y, 0x01010101, sum);
+        sum = __dp4a((int)v.z, 0x01010101, sum);
+        sum = __dp4a((int)v.w, 0x01010101, sum);
+    }
+    reinterpret_cast<int16_t *>(base + kI8BlockBytes)[r] = (int16_t)sum;
+}
+
+static Result pack_rows_impl(void *stream, size_t rows, size_t k, size_t ld_src, size_t ld_packed, const void *src,
+                             void *dst, int elem_size, bool transposed_src, size_t block_bytes);
+
 Result launch_pack_rows(void *stream, size_t rows, size_t k, size_t ld_src, size_t ld_packed, const void *src,
                         void *dst, int elem_size, bool transposed_src)
+{
+    return pack_rows_impl(stream, rows, k, ld_src, ld_packed, src, dst, elem_size, transposed_src, kI8BlockBytes);
+}
+
+Result launch_pack_rows_sums(void *stream, size_t rows, size_t k, size_t ld_src, size_t ld_packed, const void *src,
+                             void *dst, bool transposed_src)
+{
+    if (rows == 0 || k == 0) return Result{kOk, 0};
+    Result r = pack_rows_impl(stream, rows, k, ld_src, ld_packed, src, dst, 1, transposed_src, kI8SumBlockBytes);
+    if (r.status != kOk) return r;
+    const size_t tiles = ceil_div(rows, 128), kblocks = ceil_div(k, 128), total = tiles * kblocks * 128;
+    block_row_sums_kernel<<<(unsigned)ceil_div(total, 256), 256, 0, (cudaStream_t)stream>>>((uint8_t *)dst, tiles, kblocks,
+                                                                                          ceil_div(ld_packed, 128));
+    return check_launch();
+}
+
+static Result pack_rows_impl(void *stream, size_t rows, size_t k, size_t ld_src, size_t ld_packed, const void *src,
+                             void *dst, int elem_size, bool transposed_src, size_t block_bytes)
 {
     if (rows == 0 || k == 0) return Result{kOk, 0};
     const size_t kpb = 128 / elem_size;
@@ -110,14 +151,14 @@ Result launch_pack_rows(void *stream, size_t rows, size_t k, size_t ld_src, size
     uint8_t *d = (uint8_t *)dst;
     if (elem_size == 1) {
         if (transposed_src)
-            pack_rows_kernel<1, true><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks);
+            pack_rows_kernel<1, true><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
         else
-            pack_rows_kernel<1, false><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks);
+            pack_rows_kernel<1, false><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
     } else {
         if (transposed_src)
-            pack_rows_kernel<2, true><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks);
+            pack_rows_kernel<2, true><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
         else
-            pack_rows_kernel<2, false><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks);
+            pack_rows_kernel<2, false><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
     }
     return check_launch();
 }

@@ -49,10 +49,10 @@ constexpr uint32_t kI8Stages = 6;
 constexpr uint32_t kI8Threads = 352;   // warp 0 producer (even K steps), warp 1 MMA / relay, warps 2..9 epilogue, warp 10 producer (odd K steps)
 constexpr uint32_t kI8Smem = 1024 + kI8Stages * 32768 + 8 * 3 * 128 * 4 + 256;
 
-template <EpiKind EK>
+template <EpiKind EK, Dtype TD = Dtype::F32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_pair_i8_kernel(const UmmaArgs args)
 {
-    using OutT = typename OutType<EK, Dtype::F32>::type;
+    using OutT = typename OutType<EK, TD>::type;
     constexpr uint32_t S = kI8Stages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -116,8 +116,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
             const bool a_valid = mtile < tiles_m;
             const uint32_t b_bytes = nblk == 2 ? 16384u : 8192u;
             const uint8_t *a_src = args.A + (size_t)mtile * args.a_kblocks_total * kI8BlockBytes;
-            const uint8_t *b_src = nblk == 2 ? args.B + (size_t)(tn * 2 + rank) * args.b_kblocks_total * kI8BlockBytes
-                                             : args.B + (size_t)(tn * 2) * args.b_kblocks_total * kI8BlockBytes + rank * 8192u;
+            const size_t bbb = args.b_block_bytes;   // 16 KiB, or 16 KiB + the block's row sums
+            const uint8_t *b_src = nblk == 2 ? args.B + (size_t)(tn * 2 + rank) * args.b_kblocks_total * bbb
+                                             : args.B + (size_t)(tn * 2) * args.b_kblocks_total * bbb + rank * 8192u;
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
                 if ((it & 1u) != pw) continue;
                 const uint32_t s = it % S, ph = (it / S) & 1u;
@@ -129,7 +130,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                 __syncwarp();
                 // two lanes issue one bulk copy each in the same instruction
                 if (lane == 0) {
-                    ptx::bulk_g2s(ptx::smem_u32(sB + s * 16384), b_src + (size_t)kb * kI8BlockBytes, b_bytes, BAR(kFull + s));
+                    ptx::bulk_g2s(ptx::smem_u32(sB + s * 16384), b_src + (size_t)kb * bbb, b_bytes, BAR(kFull + s));
                 } else if (lane == 1 && a_valid) {
                     ptx::bulk_g2s(ptx::smem_u32(sA + s * 16384), a_src + (size_t)kb * kI8BlockBytes, 16384u, BAR(kFull + s));
                 }
@@ -228,6 +229,31 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                     sCol[256 + c] = (cok && args.bias) ? static_cast<const int32_t *>(args.bias)[n0 + c] : 0;
                 }
             }
+            // dynamic-activation W8A8 with float output: per column the row sum of B (from the packed blocks' tails),
+            // scale_b and the bias; per row (= this thread) scale_a and zero_point_a
+            float row_sa = 0.0f;
+            int32_t row_zp = 0;
+            if constexpr (EK == EpiKind::DxCx) {
+                const uint32_t blk = tn * 2u + half;   // this warp's 128 columns are one 128-row block tile of B
+                for (uint32_t c = lane; c < 128u; c += 32u) {
+                    const bool cok = c < ncols;
+                    int32_t rsum = 0;
+                    if (cok) {
+                        const uint8_t *tail = args.B + (size_t)blk * args.b_kblocks_total * args.b_block_bytes + kI8BlockBytes + c * 2u;
+                        for (uint32_t kb = 0; kb < KB; ++kb)
+                            rsum += (int32_t) * reinterpret_cast<const int16_t *>(tail + (size_t)kb * args.b_block_bytes);
+                    }
+                    sCol[c] = rsum;
+                    sCol[128 + c] = cok ? __float_as_int(args.scale_b[n0 + c]) : 0;
+                    float bv = 0.0f;
+                    if (cok && args.bias) bv = TdTraits<TD>::load(args.bias, n0 + c);
+                    sCol[256 + c] = __float_as_int(bv);
+                }
+                if (row_ok) {
+                    row_sa = args.scale_a[mrow];
+                    row_zp = args.zp_a[mrow];
+                }
+            }
             // per-row requantisation (Mx1 bias types): this thread's row has one multiplier, shift and bias
             int32_t row_mult = 0, row_rsh = 0, row_bias = 0;
             if constexpr (EK == EpiKind::Req8Row) {
@@ -264,6 +290,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                             if (args.C && j < nvalid)
                                 v = (int32_t)((uint32_t)v + (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c]);
                             out[j] = max(args.cmin_i, min(args.cmax_i, v));
+                        } else if constexpr (EK == EpiKind::DxCx) {
+                            // acc - zp_a * rowsum(b), then r = (float)acc * (scale_b * scale_a); f32: + bias, clamp;
+                            // f16: narrow first, then add the bias and clamp in f16 (as EpiDxCx in epilogues.cuh)
+                            const int32_t a = (int32_t)(r[j] - (uint32_t)row_zp * (uint32_t)sCol[c]);
+                            const float sc = __fmul_rn(__int_as_float(sCol[128 + c]), row_sa);
+                            float v = __fmul_rn(__int2float_rn(a), sc);
+                            const float bv = __int_as_float(sCol[256 + c]);
+                            if constexpr (TD == Dtype::F32) {
+                                if (args.bias) v = __fadd_rn(v, bv);
+                                v = v < args.cmin_f ? args.cmin_f : v;
+                                v = v > args.cmax_f ? args.cmax_f : v;
+                                out[j] = v;
+                            } else {
+                                float h = __half2float(__float2half_rn(v));
+                                if (args.bias) h = __half2float(__float2half_rn(__fadd_rn(h, bv)));
+                                h = h < args.cmin_f ? args.cmin_f : h;
+                                h = h > args.cmax_f ? args.cmax_f : h;
+                                out[j] = __float2half_rn(h);
+                            }
                         } else if constexpr (EK == EpiKind::Req8Row) {
                             uint32_t u = r[j];
                             if (args.C && j < nvalid) u += (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c];
@@ -924,6 +969,15 @@ static Result launch_grid(Kern kern, const UmmaArgs &a, uint32_t num_tiles, bool
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
     return Result{kOk, 0};
+}
+
+Result pair_gemm_i8_dxcx(const UmmaArgs &a, Dtype td, cudaStream_t st)
+{
+    const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
+    static bool set_f32[64] = {false}, set_f16[64] = {false};
+    if (td == Dtype::F32)
+        return launch_grid(gemm_pair_i8_kernel<EpiKind::DxCx, Dtype::F32>, a, tiles, true, kI8Threads, kI8Smem, st, set_f32);
+    return launch_grid(gemm_pair_i8_kernel<EpiKind::DxCx, Dtype::F16>, a, tiles, true, kI8Threads, kI8Smem, st, set_f16);
 }
 
 Result pair_gemm_i8_rows(const UmmaArgs &a, cudaStream_t st)

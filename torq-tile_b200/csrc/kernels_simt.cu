@@ -18,12 +18,13 @@ struct ColMajorI8 {  // stored [k, rows]: element (row, k) at p[k * ld + row]
     size_t ld;
     __device__ int8_t get(size_t r, size_t k) const { return p[k * ld + r]; }
 };
-struct PackedI8 {  // swizzled 128 x 128 blocks
+struct PackedI8 {  // swizzled 128 x 128 blocks, block_bytes apart (16 KiB, or 16 KiB + row sums)
     const int8_t *p;
     size_t kblocks_total;
+    size_t block_bytes = kI8BlockBytes;
     __device__ int8_t get(size_t r, size_t k) const
     {
-        return p[((r >> 7) * kblocks_total + (k >> 7)) * kI8BlockBytes + sw128_byte((uint32_t)(r & 127), (uint32_t)(k & 127))];
+        return p[((r >> 7) * kblocks_total + (k >> 7)) * block_bytes + sw128_byte((uint32_t)(r & 127), (uint32_t)(k & 127))];
     }
 };
 struct PackedI4Cx {  // qsi4cx blocks, returns the signed value q
@@ -174,20 +175,21 @@ Result simt_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float 
 // ---- sibling kernel types: any operand layout -------------------------------------------------------------
 // Calls f(accessor) with the int8 accessor that matches the layout.
 template <class F>
-static Result with_i8_layout(Layout l, const void *p, size_t ld, F f)
+static Result with_i8_layout(Layout l, const void *p, size_t ld, F f, size_t block_bytes = kI8BlockBytes)
 {
     switch (l) {
-        case Layout::Packed: return f(PackedI8{(const int8_t *)p, ceil_div(ld, 128)});
+        case Layout::Packed: return f(PackedI8{(const int8_t *)p, ceil_div(ld, 128), block_bytes});
         case Layout::RowMajor: return f(RowMajorI8{(const int8_t *)p, ld});
         default: return f(ColMajorI8{(const int8_t *)p, ld});
     }
 }
 
 template <class Epi, bool RSUM>
-static Result run_simt_layouts(const GemmCommon &g, Layout la, Layout lb, Epi epi)
+static Result run_simt_layouts(const GemmCommon &g, Layout la, Layout lb, Epi epi, size_t b_block_bytes = kI8BlockBytes)
 {
     return with_i8_layout(la, g.A, g.lda, [&](auto a) {
-        return with_i8_layout(lb, g.B, g.ldb, [&](auto b) { return run_simt<decltype(a), decltype(b), Epi, RSUM>(g, a, b, epi); });
+        return with_i8_layout(lb, g.B, g.ldb,
+                              [&](auto b) { return run_simt<decltype(a), decltype(b), Epi, RSUM>(g, a, b, epi); }, b_block_bytes);
     });
 }
 
@@ -214,16 +216,24 @@ Result launch_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &
     return run_simt_layouts<EpiRequantRow, false>(g, la, lb, epi);
 }
 
+Result umma_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax);
+
 Result launch_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax, Layout la,
                         Layout lb)
 {
+    if (td != Dtype::F32 && td != Dtype::F16) return Result{kUnsupported, 0};
+    // both operands packed: tensor cores (TQT_B200_PATH=simt keeps the generic kernel, for cross-checks)
+    if (la == Layout::Packed && lb == Layout::Packed && g.m && g.n && g.k && env_path() != Path::Simt) {
+        Result r = umma_gemm_dxcx(g, p, td, cmin, cmax);
+        if (r.status != kUnsupported) return r;
+    }
+    const size_t bb = lb == Layout::Packed ? kI8SumBlockBytes : kI8BlockBytes;   // packed B of these types carries row sums
     if (td == Dtype::F32) {
         EpiDxCx<Dtype::F32> epi{g.bias, g.D, g.ldd, p.scale_a, p.zp_a, p.scale_b, cmin, cmax};
-        return run_simt_layouts<EpiDxCx<Dtype::F32>, true>(g, la, lb, epi);
+        return run_simt_layouts<EpiDxCx<Dtype::F32>, true>(g, la, lb, epi, bb);
     }
-    if (td != Dtype::F16) return Result{kUnsupported, 0};
     EpiDxCx<Dtype::F16> epi{g.bias, g.D, g.ldd, p.scale_a, p.zp_a, p.scale_b, cmin, cmax};
-    return run_simt_layouts<EpiDxCx<Dtype::F16>, true>(g, la, lb, epi);
+    return run_simt_layouts<EpiDxCx<Dtype::F16>, true>(g, la, lb, epi, bb);
 }
 
 template <Dtype TD>

@@ -551,6 +551,7 @@ static bool fill_common(UmmaArgs &a, const GemmCommon &g, size_t out_elem, size_
     a.B = (const uint8_t *)g.B;
     a.a_kblocks_total = (uint32_t)ceil_div(g.lda, a_kblk);
     a.b_kblocks_total = (uint32_t)ceil_div(g.ldb, b_kblk);
+    a.b_block_bytes = (uint32_t)kI8BlockBytes;
     a.C = g.C;
     a.ldc = g.ldc;
     a.D = g.D;
@@ -632,6 +633,23 @@ Result umma_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmi
 }
 
 Result pair_gemm_i8_rows(const UmmaArgs &a, cudaStream_t st);
+Result pair_gemm_i8_dxcx(const UmmaArgs &a, Dtype td, cudaStream_t st);
+
+// qai8dxp x qsi8cxp with float output on packed operands (B blocks carry their row sums): the CTA-pair kernel.
+Result umma_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
+{
+    UmmaArgs a{};
+    if (!fill_common(a, g, td == Dtype::F32 ? 4 : 2, 128, 128)) return Result{kUnsupported, 0};
+    if (a.n_replicas) return Result{kUnsupported, 0};
+    a.b_block_bytes = (uint32_t)kI8SumBlockBytes;
+    a.scale_a = p.scale_a;
+    a.zp_a = p.zp_a;
+    a.scale_b = p.scale_b;
+    a.cmin_f = cmin;
+    a.cmax_f = cmax;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k);
+    return pair_gemm_i8_dxcx(a, td, (cudaStream_t)g.stream);
+}
 
 // Mx1-bias requantising GEMM on packed operands: the CTA-pair kernel with a per-row epilogue (any m).
 Result umma_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &p, int cmin, int cmax)

@@ -12,6 +12,7 @@ namespace tqt {
 constexpr size_t kTileRows = 128;
 constexpr size_t kI8BlockK = 128;        // int8 elements per block row (128 bytes)
 constexpr size_t kI8BlockBytes = 16384;  // 128 rows x 128 B, 128-byte-swizzled
+constexpr size_t kI8SumBlockBytes = kI8BlockBytes + 256;  // int8 block + 128 int16 partial row sums (qsi8cxp of the dynamic-activation types)
 constexpr size_t kF16BlockK = 64;        // f16 elements per block row (128 bytes)
 constexpr size_t kF16BlockBytes = 16384;
 constexpr size_t kI4BlockK = 128;        // int4 elements per block row (64 bytes)
@@ -35,6 +36,10 @@ struct Result {
 // elem_size 1 (int8) or 2 (f16).  transposed_src: source is [k, rows] row-major (run_b_pack).
 Result launch_pack_rows(void *stream, size_t rows, size_t k, size_t ld_src, size_t ld_packed, const void *src,
                         void *dst, int elem_size, bool transposed_src);
+// int8 rows into blocks of kI8SumBlockBytes, then the int16 partial row sums of every block (the zero-point
+// correction term of the qai8dxp x qsi8cxp types).
+Result launch_pack_rows_sums(void *stream, size_t rows, size_t k, size_t ld_src, size_t ld_packed, const void *src,
+                             void *dst, bool transposed_src);
 Result launch_unpack_rows(void *stream, size_t rows, size_t k, size_t ld_packed, const void *src, void *dst,
                           size_t ld_dst, int elem_size);
 // int4: src [n, k/2] bytes, row stride ld_src_bytes.  c2 = qsi4c2 ordering (no row sums).
@@ -115,7 +120,8 @@ struct RowRequantParams {
 Result launch_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &p, int clamp_min, int clamp_max,
                                    Layout la, Layout lb);
 
-// qai8dx x qsi8cx, float output of type td (F32 or F16); C is ignored, bias typed like D.
+// qai8dx x qsi8cx, float output of type td (F32 or F16); C is ignored, bias typed like D.  A packed B is in
+// the blocks-with-sums layout (kI8SumBlockBytes).
 Result launch_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float clamp_min, float clamp_max,
                         Layout la, Layout lb);
 

@@ -6,7 +6,7 @@
 namespace tqt {
 
 enum class BMode : int { I8 = 0, I4Cx = 1, I4C2 = 2 };
-enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3, Req8Row = 4 };
+enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3, Req8Row = 4, DxCx = 5 };
 
 struct UmmaArgs {
     uint32_t m, n, k;
@@ -14,6 +14,7 @@ struct UmmaArgs {
     const uint8_t *B;
     uint32_t a_kblocks_total;  // blocks per row-tile in the A buffer
     uint32_t b_kblocks_total;  // blocks per row-tile in the B buffer
+    uint32_t b_block_bytes;    // int8 CTA-pair kernel: distance between B blocks (16 KiB, or 16 KiB + row sums)
     const void *C;
     size_t ldc;
     void *D;
@@ -72,6 +73,8 @@ template <Dtype TD>
 struct OutType<EpiKind::Req8, TD> { using type = int8_t; };
 template <Dtype TD>
 struct OutType<EpiKind::Req8Row, TD> { using type = int8_t; };
+template <Dtype TD>
+struct OutType<EpiKind::DxCx, TD> { using type = typename TdTraits<TD>::type; };
 template <Dtype TD>
 struct OutType<EpiKind::W4A8, TD> { using type = typename TdTraits<TD>::type; };
 template <Dtype TD>
