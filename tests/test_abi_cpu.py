@@ -150,3 +150,48 @@ def test_output_replicas_argument_checks(pkg):
     assert lib.tqt_cuda_get_last_status() == 0
     f(None, None, 0)
     assert lib.tqt_cuda_get_last_status() == 0
+
+
+def test_headers_compile_as_c_and_cxx(tmp_path):
+    """The boundary is a C ABI: every header under include/ must be accepted by a C11 and a C++17 compiler,
+    with the 16-bit float prototypes and without them (TQT_B200_NO_HALF_TYPES)."""
+    import subprocess
+    inc = os.path.join(ROOT, "include")
+    headers = sorted(f for f in os.listdir(inc) if f.endswith(".h"))
+    body = "".join(f'#include "{h}"\n' for h in headers) + \
+        "int main(void) { return (int)tqt_get_m_step_gemm_clamp_i32_i8_i8_128x128_sm100a(); }\n"
+    for name, cc, std in (("t.c", "/usr/bin/gcc", "-std=c11"), ("t.cpp", "/usr/bin/g++", "-std=c++17")):
+        src = tmp_path / name
+        src.write_text(body)
+        for extra in ([], ["-DTQT_B200_NO_HALF_TYPES"]):
+            r = subprocess.run([cc, std, "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-I", inc] + extra + [str(src)],
+                               capture_output=True, text=True)
+            assert r.returncode == 0, r.stderr
+
+
+def test_c_program_links_and_calls_helpers(pkg, tmp_path):
+    """A plain C caller links the library and uses the size / offset helpers (no GPU needed for those)."""
+    import subprocess
+    libdir = os.path.join(ROOT, "torq-tile_b200")
+    src = tmp_path / "caller.c"
+    src.write_text('''
+#include <stdio.h>
+#include "tqt_b200_gemm_i8_i4.h"
+#include "tqt_b200_gemm_siblings.h"
+int main(void) {
+    printf("%zu %zu %zu %zu\\n",
+           tqt_get_n_step_gemm_1xnbias_clamp_bf16_qai8dxp_qsi4cxp_128x128_sm100a(),
+           tqt_get_b_packed_size_gemm_1xnbias_clamp_bf16_qai8dxp_qsi4cxp_128x128_sm100a(256, 256),
+           tqt_get_b_packed_size_gemm_1xnbias_clamp_f32_qai8dxp_qsi8cxp_128x128_sm100a(128, 128),
+           tqt_get_b_offset_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a(128, 64, 512));
+    return 0;
+}
+''')
+    exe = tmp_path / "caller"
+    r = subprocess.run(["/usr/bin/gcc", "-std=c11", "-I", os.path.join(ROOT, "include"), str(src), "-L", libdir,
+                        "-ltorq_tile_b200", f"-Wl,-rpath,{libdir}", "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    # 2 x 2 qsi4cx blocks of 8448 B; one int8 block with its row sums; nibble offset n_idx * (ldb / 2) + k_idx / 2
+    assert out.stdout.split() == ["128", str(4 * 8448), str(16384 + 256), str(128 * 256 + 32)]
