@@ -319,8 +319,11 @@ def run_ours(args):
 
     def step_e2e(i):
         layers[i % R].forward_host(a_host, out_host)
+    # PCIe-bound and therefore sensitive to what else the host is doing: five batches, the median batch is reported
     e2e_steps = max(3, min(args.steps, 10))
-    ms_e2e = timed(step_e2e, e2e_steps, max(3, min(args.warmup, 3)))
+    timed(step_e2e, 1, 3)
+    e2e_batches = sorted(timed(step_e2e, e2e_steps, 0) for _ in range(5))
+    ms_e2e = e2e_batches[len(e2e_batches) // 2]
 
     # ---- optional: the full output on every GPU -------------------------------------------------------
     # (a) the step followed by an NCCL all-gather of the column shards; (b) the fused form: the GEMM's epilogue
@@ -426,7 +429,8 @@ def run_ours(args):
                               " (int8 tensor rate is twice the bf16 rate)") if cfg != "c5" else
                              "run_gemm kernel alone, per GPU; peak = bf16_tflops_sustained of " + peaks["source"]},
         "e2e": {"value": ops / (ms_e2e * 1e-3) / 1e12, "unit": unit, "h2d_bytes_per_step": in_bytes,
-                "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e},
+                "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e,
+                "batches_ms": e2e_batches, "note": f"median of 5 batches of {e2e_steps} steps"},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clocks, "device_fault": fault,
     }
