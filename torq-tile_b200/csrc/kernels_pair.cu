@@ -806,6 +806,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
         const uint32_t quad = ew & 3u, half = (ew - 2u) >> 2;
         const uint32_t row = quad * 32u + lane;             // weight row inside this CTA's block
         constexpr bool replicate = REPL;
+        const bool has_c = args.C != nullptr, has_bias = args.bias != nullptr;
         const uint32_t my_tiles = pair < num_tiles ? (num_tiles - pair + npairs - 1) / npairs : 0u;
         uint32_t ti = helper ? (my_tiles ? my_tiles - 1u : 0u) : 0u;   // helpers: the last tile only
         bool ok = true;
@@ -872,14 +873,18 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                         } else {
                             v = __uint_as_float(r[j]);
                         }
-                        if (n_ok && j < nvalid) {
-                            if (args.C) v = __fadd_rn(v, TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n));
-                            if (args.bias) v = __fadd_rn(v, bv);
-                            v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
-                            const OutT o = cvt_out<OutT>(v);
-                            OutT *dst = dcol + (size_t)j * args.ldd;
-                            *dst = o;   // the warp writes 32 consecutive channels
-                            if constexpr (kRepl) {
+                        // branch-free per element: selects and a predicated load / store instead of three branches
+                        const bool live = n_ok && j < nvalid;
+                        float cv = 0.0f;
+                        if (has_c && live) cv = TdTraits<TD>::load(args.C, (size_t)(m0 + c0 + j) * args.ldc + n);
+                        v = has_c ? __fadd_rn(v, cv) : v;
+                        v = has_bias ? __fadd_rn(v, bv) : v;
+                        v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
+                        const OutT o = cvt_out<OutT>(v);
+                        OutT *dst = dcol + (size_t)j * args.ldd;
+                        if (live) *dst = o;   // the warp writes 32 consecutive channels
+                        if constexpr (kRepl) {
+                            if (live) {
                                 for (uint32_t rp = 0; rp < args.n_replicas; ++rp)
                                     *reinterpret_cast<OutT *>(reinterpret_cast<char *>(dst) + args.replica_delta[rp]) = o;
                             }
