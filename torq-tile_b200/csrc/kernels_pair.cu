@@ -271,6 +271,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
             ptx::tc_fence_after();
             const uint32_t t_addr = tmem_base + acc * 256u + half * 128u + ((quad * 32u) << 16);
             const uint32_t nchunks = (ncols + 31u) / 32u;
+            const bool has_bias = args.bias != nullptr;
             for (uint32_t ch = 0; ch < nchunks; ++ch) {
                 uint32_t r[32];
                 __syncwarp();
@@ -282,13 +283,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                     const uint32_t c0 = ch * 32u;
                     const uint32_t nvalid = min(32u, ncols - c0);
                     alignas(16) OutT out[32];
+                    if constexpr (EK != EpiKind::DxCx) {
+                        // the optional C operand: one uniform branch per strip, so the loop below has none
+                        if (args.C) {
+                            const int32_t *crow = static_cast<const int32_t *>(args.C) + mrow * args.ldc + n0 + c0;
+#pragma unroll
+                            for (uint32_t j = 0; j < 32; ++j)
+                                if (j < nvalid) r[j] += (uint32_t)crow[j];
+                        }
+                    }
 #pragma unroll
                     for (uint32_t j = 0; j < 32; ++j) {
                         const uint32_t c = c0 + j;
                         if constexpr (EK == EpiKind::S32) {
-                            int32_t v = (int32_t)r[j];
-                            if (args.C && j < nvalid)
-                                v = (int32_t)((uint32_t)v + (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c]);
+                            const int32_t v = (int32_t)r[j];
                             out[j] = max(args.cmin_i, min(args.cmax_i, v));
                         } else if constexpr (EK == EpiKind::DxCx) {
                             // acc - zp_a * rowsum(b), then r = (float)acc * (scale_b * scale_a); f32: + bias, clamp;
@@ -298,25 +306,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                             float v = __fmul_rn(__int2float_rn(a), sc);
                             const float bv = __int_as_float(sCol[256 + c]);
                             if constexpr (TD == Dtype::F32) {
-                                if (args.bias) v = __fadd_rn(v, bv);
+                                v = has_bias ? __fadd_rn(v, bv) : v;
                                 v = v < args.cmin_f ? args.cmin_f : v;
                                 v = v > args.cmax_f ? args.cmax_f : v;
                                 out[j] = v;
                             } else {
                                 float h = __half2float(__float2half_rn(v));
-                                if (args.bias) h = __half2float(__float2half_rn(__fadd_rn(h, bv)));
+                                h = has_bias ? __half2float(__float2half_rn(__fadd_rn(h, bv))) : h;
                                 h = h < args.cmin_f ? args.cmin_f : h;
                                 h = h > args.cmax_f ? args.cmax_f : h;
                                 out[j] = __float2half_rn(h);
                             }
                         } else if constexpr (EK == EpiKind::Req8Row) {
                             uint32_t u = r[j];
-                            if (args.C && j < nvalid) u += (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c];
                             u += (uint32_t)row_bias;
                             out[j] = (int8_t)requant_value((int32_t)u, row_mult, row_rsh, args.rq_zp_d, args.cmin_i, args.cmax_i);
                         } else {
                             uint32_t u = r[j];
-                            if (args.C && j < nvalid) u += (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c];
                             u += (uint32_t)sCol[256 + c];
                             out[j] = (int8_t)requant_value((int32_t)u, sCol[c], sCol[128 + c], args.rq_zp_d, args.cmin_i, args.cmax_i);
                         }
