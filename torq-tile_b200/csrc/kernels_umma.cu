@@ -317,6 +317,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             ptx::tc_fence_after();
             const uint32_t t_addr = tmem_base + acc * 256u + ((quad * 32u) << 16);
             const uint32_t nchunks = (ncols + 31u) / 32u;
+            const bool has_c = args.C != nullptr, has_bias = args.bias != nullptr;
             for (uint32_t ch = 0; ch < nchunks; ++ch) {
                 uint32_t r[32];
                 __syncwarp();  // tcgen05.ld is warp-collective: issue it converged
@@ -326,19 +327,25 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                     const uint32_t c0 = ch * 32u;
                     const uint32_t nvalid = min(32u, ncols - c0);
                     alignas(16) OutT out[32];
+                    if constexpr (EK == EpiKind::S32 || EK == EpiKind::Req8) {
+                        // the optional C operand: one uniform branch per strip, so the loop below has none
+                        if (args.C) {
+                            const int32_t *crow = static_cast<const int32_t *>(args.C) + mrow * args.ldc + n0 + c0;
+#pragma unroll
+                            for (uint32_t j = 0; j < 32; ++j)
+                                if (j < nvalid) r[j] += (uint32_t)crow[j];
+                        }
+                    }
 #pragma unroll
                     for (uint32_t j = 0; j < 32; ++j) {
                         const uint32_t c = c0 + j;
                         if constexpr (EK == EpiKind::S32) {
                             int32_t v = (int32_t)r[j];
-                            if (args.C && j < nvalid)
-                                v = (int32_t)((uint32_t)v + (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c]);
                             v = v < args.cmin_i ? args.cmin_i : v;
                             v = v > args.cmax_i ? args.cmax_i : v;
                             out[j] = v;
                         } else if constexpr (EK == EpiKind::Req8) {
                             uint32_t u = r[j];
-                            if (args.C && j < nvalid) u += (uint32_t) static_cast<const int32_t *>(args.C)[mrow * args.ldc + n0 + c];
                             u += (uint32_t)sColI[512 + c];
                             out[j] = (int8_t)requant_value((int32_t)u, sColI[c], sColI[256 + c], args.rq_zp_d, args.cmin_i, args.cmax_i);
                         } else if constexpr (EK == EpiKind::W4A8) {
@@ -346,14 +353,16 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                             int32_t a = ((int32_t)r[j]) >> 4;
                             a -= zp * sRsum[acc * 256 + c];
                             float cv = 0.0f;
-                            if (args.C && j < nvalid) cv = TdTraits<TD>::load(args.C, mrow * args.ldc + n0 + c);
-                            const float v = w4a8_epilogue(a, sa, sColF[c], args.C != nullptr, cv, args.bias != nullptr,
+                            if (has_c && j < nvalid) cv = TdTraits<TD>::load(args.C, mrow * args.ldc + n0 + c);
+                            const float v = w4a8_epilogue(a, sa, sColF[c], has_c, cv, has_bias,
                                                           sColF[256 + c], args.cmin_f, args.cmax_f);
                             out[j] = cvt_out<OutT>(v);
                         } else {
                             float v = __uint_as_float(r[j]);
-                            if (args.C && j < nvalid) v = __fadd_rn(v, TdTraits<TD>::load(args.C, mrow * args.ldc + n0 + c));
-                            if (args.bias) v = __fadd_rn(v, sColF[256 + c]);
+                            float cv = 0.0f;
+                            if (has_c && j < nvalid) cv = TdTraits<TD>::load(args.C, mrow * args.ldc + n0 + c);
+                            v = has_c ? __fadd_rn(v, cv) : v;
+                            v = has_bias ? __fadd_rn(v, sColF[256 + c]) : v;
                             v = v < args.cmin_f ? args.cmin_f : v;
                             v = v > args.cmax_f ? args.cmax_f : v;
                             out[j] = cvt_out<OutT>(v);
