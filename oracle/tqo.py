@@ -74,6 +74,29 @@ class Oracle:
         lib.tqo_gemm_qai8dx_qsi8cx.argtypes = [_sz, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int, _vp, _vp,
                                                _vp, _vp, _vp, _sz, C.c_float, C.c_float, C.c_int]
 
+        lib.tqo_fill_uniform_f32.argtypes = [_vp, _sz, C.c_float, C.c_float, C.c_uint32]
+        lib.tqo_fill_uniform_i8.argtypes = [_vp, _sz, C.c_int, C.c_int, C.c_uint32]
+        lib.tqo_fill_uniform_i32.argtypes = [_vp, _sz, C.c_int32, C.c_int32, C.c_uint32]
+        lib.tqo_fill_normal_f32.argtypes = [_vp, _sz, C.c_float, C.c_float, C.c_uint32]
+
+    # ---- seeded generators (std::mt19937, the engine and seeds of the reference's suites) ----
+    def fill_uniform(self, shape, dtype, lo, hi, seed):
+        a = np.empty(shape, dtype)
+        if dtype == np.float32:
+            self.lib.tqo_fill_uniform_f32(_ptr(a), a.size, float(lo), float(hi), int(seed))
+        elif dtype == np.int8:
+            self.lib.tqo_fill_uniform_i8(_ptr(a), a.size, int(lo), int(hi), int(seed))
+        elif dtype == np.int32:
+            self.lib.tqo_fill_uniform_i32(_ptr(a), a.size, int(lo), int(hi), int(seed))
+        else:
+            raise TypeError(dtype)
+        return a
+
+    def fill_normal(self, shape, mean, sigma, seed):
+        a = np.empty(shape, np.float32)
+        self.lib.tqo_fill_normal_f32(_ptr(a), a.size, float(mean), float(sigma), int(seed))
+        return a
+
     # ---- helpers -----------------------------------------------------------------------
     def max_threads(self) -> int:
         return int(self.lib.tqo_max_threads())
@@ -211,6 +234,42 @@ class Reference:
         lib.ref_fill_uniform_f16.argtypes = [_vp, _sz, _sz, C.c_float, C.c_float, C.c_uint32]
         lib.ref_fill_uniform_i8.argtypes = [_vp, _sz, _sz, C.c_int, C.c_int, C.c_uint32]
         lib.ref_fill_uniform_i32.argtypes = [_vp, _sz, _sz, C.c_int32, C.c_int32, C.c_uint32]
+        if hasattr(lib, "ref_w4a8_gemm"):
+            lib.ref_fill_uniform_bf16.argtypes = [_vp, _sz, _sz, C.c_float, C.c_float, C.c_uint32]
+            lib.ref_w4a8_quantize_a_per_row_asym.argtypes = [_vp, _sz, _sz, _vp, _vp, _vp]
+            lib.ref_w4a8_quantize_b_per_channel_sym_int4.argtypes = [_vp, _sz, _sz, _vp, _vp]
+            lib.ref_w4a8_gemm.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_float,
+                                          C.c_float, C.c_int]
+
+    def has_w4a8(self) -> bool:
+        """True when the library carries the W4A8 helpers cut out of the reference's gtest suite."""
+        return self.lib is not None and hasattr(self.lib, "ref_w4a8_gemm")
+
+    def w4a8_quantize_a_per_row_asym(self, A_f32):
+        m, k = A_f32.shape
+        q = np.empty((m, k), np.int8)
+        s = np.empty(m, np.float32)
+        z = np.empty(m, np.int32)
+        self.lib.ref_w4a8_quantize_a_per_row_asym(_ptr(A_f32), m, k, _ptr(q), _ptr(s), _ptr(z))
+        return q, s, z
+
+    def w4a8_quantize_b_per_channel_sym_int4(self, B_f32):
+        n, k = B_f32.shape
+        nib = np.empty((n, k // 2), np.uint8)
+        s = np.empty(n, np.float32)
+        self.lib.ref_w4a8_quantize_b_per_channel_sym_int4(_ptr(B_f32), n, k, _ptr(nib), _ptr(s))
+        return nib, s
+
+    def w4a8_gemm(self, A_i8, B_nib, scale_a, zp_a, scale_b, td, Cm=None, bias=None,
+                  clamp=(-3.4028234663852886e38, 3.4028234663852886e38)):
+        """w4a8_reference_fp32 narrowed through the output type; C, bias, result: f32 arrays or
+        uint16 bit patterns per ``td``."""
+        m, k = A_i8.shape
+        n = B_nib.shape[0]
+        D = np.empty((m, n), np.float32 if td == TD_F32 else np.uint16)
+        self.lib.ref_w4a8_gemm(m, n, k, _ptr(A_i8), _ptr(B_nib), _ptr(scale_a), _ptr(zp_a), _ptr(scale_b),
+                               _ptr(Cm), _ptr(bias), _ptr(D), float(clamp[0]), float(clamp[1]), td)
+        return D
 
     def available(self) -> bool:
         return self.lib is not None
@@ -259,6 +318,9 @@ class Reference:
         elif dtype == np.float16:
             a = np.empty(shape, np.float16)
             self.lib.ref_fill_uniform_f16(_ptr(a), rows, cols, lo, hi, seed)
+        elif dtype == "bf16":
+            a = np.empty(shape, np.uint16)
+            self.lib.ref_fill_uniform_bf16(_ptr(a), rows, cols, lo, hi, seed)
         elif dtype == np.int8:
             a = np.empty(shape, np.int8)
             self.lib.ref_fill_uniform_i8(_ptr(a), rows, cols, int(lo), int(hi), seed)

@@ -14,7 +14,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
-from oracle.tqo import TD_F16, TD_F32, Reference  # noqa: E402
+from oracle.tqo import TD_BF16, TD_F16, TD_F32, Reference  # noqa: E402
 
 I8_SHAPES = [(32, 32, 32, False), (3, 8, 11, False), (5, 11, 10, False), (9, 19, 23, False),
              (15, 32, 25, False), (60, 63, 127, False), (32, 32, 32, True), (60, 63, 127, True)]
@@ -25,6 +25,11 @@ W4A16_CASES = [(8, 8, 4, 2, 0, 0, None), (16, 16, 8, 2, 0, 0, None), (32, 32, 32
                (60, 61, 128, 32, 0, 0, None), (32, 32, 32, 2, 1, 0, None), (17, 19, 24, 4, 1, 0, None),
                (32, 32, 32, 4, 0, 0, (-0.5, 0.5)), (32, 32, 32, 4, 0, 1, None),
                (32, 32, 32, 4, 1, 1, (-0.5, 0.5))]
+# test/gemm/test_gemm_i8_i4_rvv.cpp:164-179: (m, n, k, bias, c, clamp)
+W4A8_CASES = [(8, 8, 8, 0, 0, None), (16, 16, 16, 0, 0, None), (32, 32, 32, 0, 0, None), (5, 11, 16, 0, 0, None),
+              (7, 3, 8, 0, 0, None), (17, 19, 24, 0, 0, None), (31, 35, 64, 0, 0, None), (60, 61, 128, 0, 0, None),
+              (32, 32, 32, 1, 0, None), (17, 19, 24, 1, 0, None), (32, 32, 32, 0, 0, (-0.5, 0.5)),
+              (32, 32, 32, 0, 1, None), (32, 32, 32, 1, 1, (-0.5, 0.5))]
 MULTIPLIERS = [0.0025, 0.0, 1.0, 0.5, 0.75, 1e-12, 1e-9, 2.0 ** -31, 2.0 ** -32, 2.0 ** -33, 123.456,
                0.05 * 0.001 / 0.1, 0.05 * 0.01 / 0.1, 0.9999999999, 0.99999999999999989,
                1.0 - 2.0 ** -31, 1.0 - 2.0 ** -32, 0.5 + 2.0 ** -32, 0.5 + 3 * 2.0 ** -33,
@@ -103,6 +108,58 @@ def main():
             out[f"w4a16_{idx}_D_{tag}"] = ref.gemm_w4a16(A.view(np.uint16), nib, sc, bl, td, cv, bv, cl_td)
     out["w4a16_cases"] = np.array([(m, n, k, bl, b, c, 0 if cl is None else 1)
                                    for m, n, k, bl, b, c, cl in W4A16_CASES], np.int64)
+    # ---- W4A8: the helpers of test/gemm/test_gemm_i8_i4_rvv.cpp:36-158, compiled from the reference -----
+    # Inputs as run_w4a8_packed_gemm_test draws them (:337-367): one generator U(-1,1) seed 42 fills A then B;
+    # C in TD U(-2,2) seed 42; bias in TD U(-0.5,0.5) seed 7.
+    assert ref.has_w4a8(), "oracle/_ref was built without the W4A8 helpers: make -C oracle ref REF=..."
+    FMAX = 3.4028234663852886e38
+    for idx, (m, n, k, has_bias, has_c, clamp) in enumerate(W4A8_CASES):
+        AB = ref.fill_uniform((1, m * k + n * k), np.float32, -1.0, 1.0, 42).reshape(-1)
+        A, W = AB[:m * k].reshape(m, k).copy(), AB[m * k:].reshape(n, k).copy()
+        q, sa, zp = ref.w4a8_quantize_a_per_row_asym(A)
+        nib, sb = ref.w4a8_quantize_b_per_channel_sym_int4(W)
+        out[f"w4a8_{idx}_A"], out[f"w4a8_{idx}_W"] = A, W
+        out[f"w4a8_{idx}_q"], out[f"w4a8_{idx}_sa"], out[f"w4a8_{idx}_zp"] = q, sa, zp
+        out[f"w4a8_{idx}_nib"], out[f"w4a8_{idx}_sb"] = nib, sb
+        cl = clamp if clamp else (-FMAX, FMAX)
+        for td, tag, dt in ((TD_F32, "f32", np.float32), (TD_F16, "f16", np.float16), (TD_BF16, "bf16", "bf16")):
+            Cm = ref.fill_uniform((m, n), dt, -2.0, 2.0, 42) if has_c else None
+            bias = ref.fill_uniform((1, n), dt, -0.5, 0.5, 7).reshape(n) if has_bias else None
+            if Cm is not None and Cm.dtype == np.float16:
+                Cm = Cm.view(np.uint16)
+            if bias is not None and bias.dtype == np.float16:
+                bias = bias.view(np.uint16)
+            if has_c:
+                out[f"w4a8_{idx}_C_{tag}"] = Cm
+            if has_bias:
+                out[f"w4a8_{idx}_bias_{tag}"] = bias
+            out[f"w4a8_{idx}_D_{tag}"] = ref.w4a8_gemm(q, nib, sa, zp, sb, td, Cm, bias, cl)
+    out["w4a8_cases"] = np.array([(m, n, k, b, c, 0 if cl is None else 1) for m, n, k, b, c, cl in W4A8_CASES],
+                                 np.int64)
+    # rows that exercise the quantiser's branches: all-zero, all-positive, all-negative, tiny range, huge range,
+    # values on rounding boundaries of x / s
+    rng2 = np.random.default_rng(17)
+    Aq = rng2.normal(0, 1, (24, 40)).astype(np.float32)
+    Aq[0] = 0.0
+    Aq[1] = np.abs(Aq[1])
+    Aq[2] = -np.abs(Aq[2])
+    Aq[3] *= np.float32(1e-30)
+    Aq[4] *= np.float32(1e30)
+    Aq[5] = np.float32(0.25)
+    Aq[6, :] = np.linspace(-1.0, 1.0, 40, dtype=np.float32) * np.float32(127.5)
+    Aq[7] = np.round(Aq[7] * 8) / 8
+    Aq[8] *= np.float32(1e-41)          # subnormal row
+    out["w4a8_edge_A"] = Aq
+    q, sa, zp = ref.w4a8_quantize_a_per_row_asym(Aq)
+    out["w4a8_edge_q"], out["w4a8_edge_sa"], out["w4a8_edge_zp"] = q, sa, zp
+    Wq = rng2.normal(0, 0.02, (12, 40)).astype(np.float32)
+    Wq[0] = 0.0
+    Wq[1] = np.float32(0.5)
+    Wq[2, ::2] = np.float32(-1.0)
+    Wq[3] = np.round(Wq[3] * 400) / 400
+    out["w4a8_edge_W"] = Wq
+    nib, sb = ref.w4a8_quantize_b_per_channel_sym_int4(Wq)
+    out["w4a8_edge_nib"], out["w4a8_edge_sb"] = nib, sb
     path = os.path.join(HERE, "ref_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

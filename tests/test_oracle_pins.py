@@ -9,6 +9,10 @@ import pytest
 from oracle.tqo import TD_BF16, TD_F16, TD_F32, Reference
 
 FMAX = 3.4028234663852886e38
+# first draws of std::mt19937(42) through libstdc++'s uniform_int_distribution<int8_t>(-128, 127) and
+# normal_distribution<float>(0, 1)
+KNOWN_I8_SEED42 = [-33, 75, 115, -82]
+KNOWN_NORMAL_SEED42 = np.array([1.2219213247299194, -0.5169641375541687, 0.8696359395980835], np.float32)
 
 
 def test_known_answer_quantize_multiplier(oracle):
@@ -70,6 +74,103 @@ def test_w4a16_golden(oracle, golden):
             D = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, int(bl), td, Cm, bias, clamp)
             want = golden[f"w4a16_{idx}_D_{tag}"]
             assert np.array_equal(D.view(np.uint8), want.view(np.uint8)), (idx, tag)
+
+
+def _w4a8_bits(a):
+    return a.view(np.uint32) if a.dtype == np.float32 else a
+
+
+def test_w4a8_golden(oracle, golden):
+    """The W4A8 quantisers and GEMM restatement against outputs of the reference's own helpers
+    (test/gemm/test_gemm_i8_i4_rvv.cpp:36-158, compiled by oracle/Makefile ref), on the suite's shape
+    list with its bias / C / clamp options and all three output types, bit for bit."""
+    for idx, (m, n, k, has_bias, has_c, has_clamp) in enumerate(golden["w4a8_cases"]):
+        A, W = golden[f"w4a8_{idx}_A"], golden[f"w4a8_{idx}_W"]
+        q, sa, zp = oracle.quantize_a_per_row_asym(A)
+        assert np.array_equal(q, golden[f"w4a8_{idx}_q"])
+        assert np.array_equal(sa.view(np.uint32), golden[f"w4a8_{idx}_sa"].view(np.uint32))
+        assert np.array_equal(zp, golden[f"w4a8_{idx}_zp"])
+        nib, sb = oracle.quantize_b_per_channel_sym_int4(W)
+        assert np.array_equal(nib, golden[f"w4a8_{idx}_nib"])
+        assert np.array_equal(sb.view(np.uint32), golden[f"w4a8_{idx}_sb"].view(np.uint32))
+        clamp = (-0.5, 0.5) if has_clamp else (-FMAX, FMAX)
+        for td, tag in ((TD_F32, "f32"), (TD_F16, "f16"), (TD_BF16, "bf16")):
+            Cm = golden[f"w4a8_{idx}_C_{tag}"] if has_c else None
+            bias = golden[f"w4a8_{idx}_bias_{tag}"] if has_bias else None
+            D = oracle.gemm_w4a8(q, nib, sa, zp, sb, td, Cm, bias, clamp)
+            assert np.array_equal(_w4a8_bits(D), _w4a8_bits(golden[f"w4a8_{idx}_D_{tag}"])), (idx, tag)
+
+
+def test_w4a8_quantiser_edge_rows_golden(oracle, golden):
+    """All-zero, one-signed, tiny, huge, subnormal and boundary rows through both quantisers."""
+    q, sa, zp = oracle.quantize_a_per_row_asym(golden["w4a8_edge_A"])
+    assert np.array_equal(q, golden["w4a8_edge_q"])
+    assert np.array_equal(sa.view(np.uint32), golden["w4a8_edge_sa"].view(np.uint32))
+    assert np.array_equal(zp, golden["w4a8_edge_zp"])
+    nib, sb = oracle.quantize_b_per_channel_sym_int4(golden["w4a8_edge_W"])
+    assert np.array_equal(nib, golden["w4a8_edge_nib"])
+    assert np.array_equal(sb.view(np.uint32), golden["w4a8_edge_sb"].view(np.uint32))
+
+
+def test_w4a8_live_reference_when_built(oracle):
+    """Larger random cases and 16-bit activations against the reference's helpers where oracle/_ref exists."""
+    ref = Reference()
+    if not ref.has_w4a8():
+        pytest.skip("oracle/_ref (with the W4A8 helpers) not built on this machine")
+    rng = np.random.default_rng(23)
+    for (m, n, k) in [(33, 70, 96), (128, 130, 256), (3, 257, 1024)]:
+        A = rng.normal(0, 1, (m, k)).astype(np.float32)
+        W = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+        q, sa, zp = oracle.quantize_a_per_row_asym(A)
+        rq, rsa, rzp = ref.w4a8_quantize_a_per_row_asym(A)
+        assert np.array_equal(q, rq) and np.array_equal(sa, rsa) and np.array_equal(zp, rzp)
+        nib, sb = oracle.quantize_b_per_channel_sym_int4(W)
+        rnib, rsb = ref.w4a8_quantize_b_per_channel_sym_int4(W)
+        assert np.array_equal(nib, rnib) and np.array_equal(sb, rsb)
+        bias = rng.normal(0, 0.1, n).astype(np.float32)
+        Cm = rng.uniform(-2, 2, (m, n)).astype(np.float32)
+        for td in (TD_F32, TD_F16, TD_BF16):
+            if td == TD_F32:
+                b, c = bias, Cm
+            elif td == TD_F16:
+                b, c = bias.astype(np.float16).view(np.uint16), Cm.astype(np.float16).view(np.uint16)
+            else:
+                b = np.array([oracle.lib.tqo_f32_to_bf16(float(x)) for x in bias], np.uint16)
+                c = np.array([oracle.lib.tqo_f32_to_bf16(float(x)) for x in Cm.ravel()], np.uint16).reshape(m, n)
+            for cl in ((-FMAX, FMAX), (-0.25, 0.3)):
+                D = oracle.gemm_w4a8(q, nib, sa, zp, sb, td, c, b, cl)
+                R = ref.w4a8_gemm(q, nib, sa, zp, sb, td, c, b, cl)
+                assert np.array_equal(_w4a8_bits(D), _w4a8_bits(R)), (m, n, k, td, cl)
+        # 16-bit activation rows: the oracle widens them (exactly) before the same arithmetic
+        a16 = A.astype(np.float16)
+        q16, s16, z16 = oracle.quantize_a_per_row_asym(a16.view(np.uint16), TD_F16)
+        rq, rsa, rzp = ref.w4a8_quantize_a_per_row_asym(a16.astype(np.float32))
+        assert np.array_equal(q16, rq) and np.array_equal(s16, rsa) and np.array_equal(z16, rzp)
+        ab = np.array([oracle.lib.tqo_f32_to_bf16(float(x)) for x in A.ravel()[:m * 64]], np.uint16).reshape(m, 64)
+        qb, sbb, zb = oracle.quantize_a_per_row_asym(ab, TD_BF16)
+        abf = (ab.astype(np.uint32) << 16).view(np.float32)
+        rq, rsa, rzp = ref.w4a8_quantize_a_per_row_asym(abf)
+        assert np.array_equal(qb, rq) and np.array_equal(sbb, rsa) and np.array_equal(zb, rzp)
+
+
+def test_seeded_generators_match_the_reference(oracle):
+    """tqo_fill_uniform_* reproduce test/common/data_generator.cpp's streams (same engine, seed, distribution)."""
+    ref = Reference()
+    if not ref.available():
+        pytest.skip("oracle/_ref not built on this machine")
+    assert np.array_equal(oracle.fill_uniform((7, 33), np.int8, -128, 127, 42), ref.fill_uniform((7, 33), np.int8, -128, 127, 42))
+    assert np.array_equal(oracle.fill_uniform((5, 19), np.int8, -50, 50, 123), ref.fill_uniform((5, 19), np.int8, -50, 50, 123))
+    assert np.array_equal(oracle.fill_uniform((3, 41), np.int32, -1000, 1000, 7), ref.fill_uniform((3, 41), np.int32, -1000, 1000, 7))
+    assert np.array_equal(oracle.fill_uniform((9, 21), np.float32, -1.0, 1.0, 42), ref.fill_uniform((9, 21), np.float32, -1.0, 1.0, 42))
+
+
+def test_seeded_generators_known_stream(oracle):
+    """First draws of the seeded streams, so that a box with another standard library is noticed
+    (mt19937 is specified exactly; the distributions' algorithms are the library's)."""
+    a = oracle.fill_uniform((1, 4), np.int8, -128, 127, 42).ravel().tolist()
+    b = oracle.fill_normal((1, 3), 0.0, 1.0, 42).ravel()
+    assert a == KNOWN_I8_SEED42, a
+    assert np.allclose(b, KNOWN_NORMAL_SEED42, rtol=0, atol=0), b.tolist()
 
 
 def test_w4a8_integer_core_against_i32_golden(oracle, golden):
