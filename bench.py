@@ -6,8 +6,10 @@
 Prints ONE JSON line.  Headline workload ("c3"): the W4A8 prefill GEMM of the Llama-3-8B MLP
 up-projection shape (M=2048, K=4096, N=14336; bf16 activations dynamically quantised per row to
 int8, per-channel int4 weights, bf16 output), metric int8 TOPS = 2*M*N*K / step time.  One step =
-quantise+pack the activations, then run_gemm, through the C ABI.  The same line carries the decode
-GEMV (M=1, K=N=4096, f32) as HBM GB/s under "decode_gemv".
+quantise+pack the activations, then run_gemm, through the C ABI.  On one GPU the same line carries
+the other two prefill configurations under "c4" (static W8A8 with int8 requantisation) and "c5"
+(W4A16 block-quant), measured the same way with fewer steps, the decode GEMV (M=1, K=N=4096, f32) as
+HBM GB/s under "decode_gemv" (with an M=16 row), and the layout kernels' HBM fractions under "layout".
 
 Inputs are seeded synthetic data with the shapes and value distributions the configurations state
 (there are no datasets or checkpoints involved).
@@ -18,9 +20,10 @@ replicated; no collective is on the data path.  --gather additionally times an N
 of the output column shards and the fused form (peer stores from the GEMM epilogue), reported
 separately under "gather", not part of "value".
 
---impl reference times the CPU implementation of the same path on the host cores (the oracle port
-built from oracle/tqt_oracle.c; the reference's W4A8 code lives in a gtest translation unit that
-cannot be compiled off RISC-V), on a bounded sample of rows.
+--impl reference times the CPU implementation of the same path on the host cores, on a bounded sample
+of rows: the reference's own w4a8_reference_fp32 (test/gemm/test_gemm_i8_i4_rvv.cpp:122-156, compiled
+into oracle/_ref by oracle/Makefile; single-threaded code, run here on disjoint row slices from one
+thread per core) when that library is present, else the oracle port built from oracle/tqt_oracle.c.
 """
 from __future__ import annotations
 
@@ -106,22 +109,36 @@ class ClockSampler:
 # CPU arm
 # ---------------------------------------------------------------------------------------------------
 def cpu_w4a8_sample(M, K, N, budget_s=12.0, threads=None):
-    """Times the oracle's W4A8 GEMM on the host cores for `rows` rows of the workload (all of N and K)
-    chosen so that the run takes roughly budget_s.  Returns (tops, rows, seconds, threads)."""
-    from oracle.tqo import TD_BF16, Oracle
+    """Times the CPU W4A8 GEMM on the host cores for `rows` rows of the workload (all of N and K) chosen
+    so that the run takes roughly budget_s.  Returns (tops, rows, seconds, threads, kind): kind
+    "reference" = the reference's own w4a8_reference_fp32 from oracle/_ref, one thread per core on
+    disjoint row slices (the function itself is single-threaded); "port" = the oracle restatement with
+    OpenMP."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    from oracle.tqo import TD_BF16, Oracle, Reference
     orc = Oracle(native=True)
     nthreads = threads or orc.max_threads()
     orc.set_threads(nthreads)
+    ref = Reference(native=True)
+    kind = "reference" if ref.has_w4a8() else "port"
     rng = np.random.default_rng(1)
     nib = rng.integers(0, 256, (N, K // 2), dtype=np.uint8)
     sb = rng.uniform(0.001, 0.01, N).astype(np.float32)
+    pool = ThreadPoolExecutor(nthreads) if kind == "reference" else None
 
     def run(rows):
         q = rng.integers(-128, 128, (rows, K), dtype=np.int8)
         sa = rng.uniform(0.01, 0.05, rows).astype(np.float32)
         zp = rng.integers(-20, 20, rows).astype(np.int32)
         t0 = time.perf_counter()
-        orc.gemm_w4a8(q, nib, sa, zp, sb, TD_BF16, None, None, (-65504.0, 65504.0))
+        if kind == "reference":
+            per = -(-rows // nthreads)
+            parts = [(r0, min(rows, r0 + per)) for r0 in range(0, rows, per)]
+            list(pool.map(lambda b: ref.w4a8_gemm(q[b[0]:b[1]], nib, sa[b[0]:b[1]], zp[b[0]:b[1]], sb, TD_BF16, None, None,
+                                                  (-65504.0, 65504.0)), parts))
+        else:
+            orc.gemm_w4a8(q, nib, sa, zp, sb, TD_BF16, None, None, (-65504.0, 65504.0))
         return time.perf_counter() - t0
 
     probe_rows = max(nthreads, 16)
@@ -129,31 +146,81 @@ def cpu_w4a8_sample(M, K, N, budget_s=12.0, threads=None):
     rows = int(min(M, max(probe_rows, probe_rows * budget_s / max(t_probe, 1e-6))))
     rows = max(nthreads, rows - rows % nthreads)
     t = run(rows)
-    return 2.0 * rows * N * K / t / 1e12, rows, t, nthreads
+    if pool is not None:
+        pool.shutdown()
+    return 2.0 * rows * N * K / t / 1e12, rows, t, nthreads, kind
+
+
+def cpu_sample_text(rows, M, N, K, nthreads, kind, secs=None):
+    what = ("the reference's w4a8_reference_fp32 (oracle/_ref), one thread per core on disjoint row slices" if kind == "reference"
+            else "oracle/tqt_oracle.c with OpenMP")
+    t = "" if secs is None else f" in {secs:.1f} s"
+    return f"{rows} of {M} rows x all N={N} x K={K}{t} (int8 x int4 -> f32 epilogue -> bf16), {what}, {nthreads} threads"
+
+
+def workload_config(cfg, world, n_local, R, set_bytes, graphs=True):
+    """The `config` object of the JSON line; both arms (ours, reference) print the same one."""
+    return {"workload": CONFIGS[cfg][3],
+            "step": "activation quantise+pack (or pack) kernel + run_gemm, weights packed once outside" +
+                    ("; the two launches replayed as one CUDA graph" if graphs else ""),
+            "parallelism": f"N-sharded x{world}, no collective" if world > 1 else "single GPU",
+            "n_per_gpu": n_local,
+            "l2": f"rotating {R} weight/output sets per rank ({R * set_bytes / 1e6:.0f} MB) > 126 MB L2"}
+
+
+def set_bytes_of(cfg, n_local):
+    """Bytes of one rotating set on a rank: packed weights + output (what has to exceed L2 R times over)."""
+    M, K, N, _ = CONFIGS[cfg]
+    if cfg == "c3":
+        return -(-n_local // 128) * (K // 128) * 8448 + M * n_local * 2
+    if cfg == "c4":
+        return n_local * K + M * n_local
+    return n_local * K // 2 + M * n_local * 2
+
+
+def rotation(cfg, n_local, requested):
+    """Number of rotating weight/output sets: at least the requested count, and enough that together they are
+    well above the 126 MB L2 at every shard size."""
+    need = int(math.ceil(1.5 * 126e6 / set_bytes_of(cfg, n_local)))
+    return max(requested, need)
+
+
+def shard_plan(n, world, rank):
+    """Same split as tqt_shard_plan_n (contiguous ranges of 128-column blocks), for the arm that does not load the library."""
+    blocks = -(-n // 128)
+    base, extra = divmod(blocks, world)
+    b0 = rank * base + min(rank, extra)
+    nb = base + (1 if rank < extra else 0)
+    return min(b0 * 128, n), min((b0 + nb) * 128, n) - min(b0 * 128, n)
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     M, K, N, desc = CONFIGS["c3"]
     per_step = []
     rows = 0
     nthreads = 0
+    kind = "port"
     budget = max(0.5, min(8.0, 150.0 / max(1, args.steps + args.warmup)))
     for i in range(args.warmup + args.steps):
-        tops, rows, secs, nthreads = cpu_w4a8_sample(M, K, N, budget_s=budget if i >= args.warmup else 2.0)
+        tops, rows, secs, nthreads, kind = cpu_w4a8_sample(M, K, N, budget_s=budget if i >= args.warmup else 2.0)
         if i >= args.warmup:
             per_step.append((tops, secs))
     tops = float(np.mean([p[0] for p in per_step]))
     ms = float(np.mean([p[1] for p in per_step]) * 1e3)
-    sample = f"{rows} of {M} rows x all N={N} x K={K} per step (int8 x int4 -> f32 epilogue -> bf16), {nthreads} OpenMP threads"
+    sample = cpu_sample_text(rows, M, N, K, nthreads, kind) + " per step"
+    _, n_local = shard_plan(N, world, 0)
+    R = rotation("c3", n_local, args.rotate)
     line = {
         "impl": "reference", "metric": "w4a8_gemm_int8_tops", "value": tops, "unit": "TOPS", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": CONFIGS["c3"][3], "sample": sample},
-        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": nthreads, "kind": "port", "sample": sample},
+        "config": workload_config("c3", world, n_local, R, set_bytes_of("c3", n_local), graphs=not args.no_graphs),
+        "note": "CPU arm: the config names the workload of both arms; this arm runs its rows on the host cores, no GPU, no graphs",
+        "cpu_baseline": {"value": tops, "unit": "TOPS", "cores": nthreads, "kind": kind, "sample": sample},
         "e2e": {"value": tops, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -163,6 +230,88 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------------
+# Rate at which tcgen05.mma actually issues on this part (measured with a loop of MMAs on static operands:
+# kind::i8 M128 x N192 x K32 every 102.5 cycles per SM, 148 SMs, 1965 MHz); kind::f16 runs at half of it.
+ISSUE_RATE_INT8_TOPS = 2.0 * 128 * 192 * 32 / 102.5 * 148 * 1.965e9 / 1e12   # 4.46e3
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE run_gemm launch from the ncu captures summarised under
+# profiles/ (file named beside each figure): taken under ncu on an earlier run of the same kernels, NOT measured by
+# the run that prints the line.
+NCU_TRAFFIC = {"c3": (56.2e6, "profiles/gemm_ts_pair_w4a8_c3.txt"), "c4": (33.9e6, "profiles/gemm_pair_i8_c4.txt"),
+               "c5": (1419.1e6, "profiles/gemm_ts_pair_w4a16_c5.txt")}
+
+
+def algorithmic_bytes(cfg, n_local):
+    """Bytes one run_gemm launch must move: packed A + packed B (+ scales, bias) in, D out."""
+    M, K, N, _ = CONFIGS[cfg]
+    if cfg == "c3":
+        return M * K + -(-n_local // 128) * (K // 128) * 8448 + 8 * M + 4 * n_local + 2 * n_local + 2 * M * n_local
+    if cfg == "c4":
+        return M * K + n_local * K + 4 * n_local + 4 * n_local + M * n_local
+    return 2 * M * K + n_local * K // 2 + 2 * n_local * (K // 32) + 2 * n_local + 2 * M * n_local
+
+
+def build_layers(torch, lin, cfg, n_local, R, dev, gen):
+    """R rotating weight sets of this rank's column shard + the activations; returns the pieces of one step."""
+    M, K, N, _ = CONFIGS[cfg]
+    layers = []
+    if cfg == "c3":
+        for r in range(R):
+            # int4 weights of W ~ N(0, 0.02) quantised per channel: nibble = clamp(round(w / (absmax/8)), -8, 7) + 8
+            w = torch.randn((n_local, K), generator=gen, device=dev) * 0.02
+            sc = w.abs().amax(dim=1) / 8.0
+            q = torch.clamp(torch.round(w / sc[:, None]), -8, 7).to(torch.int16) + 8
+            nib = (q[:, 0::2] | (q[:, 1::2] << 4)).to(torch.uint8)
+            layers.append(lin.W4A8Linear(nib, sc, K, "bf16", bias=torch.zeros(n_local, dtype=torch.bfloat16, device=dev),
+                                         clamp=(-65504.0, 65504.0)))
+            del w, q, nib
+        a_host = torch.randn((M, K), dtype=torch.float32).to(torch.bfloat16).pin_memory()
+        prepare, in_bytes, out_bytes, dtype = "quantize", M * K * 2, M * n_local * 2, "int8"
+    elif cfg == "c4":
+        for r in range(R):
+            w = torch.randint(-127, 128, (n_local, K), generator=gen, device=dev, dtype=torch.int8)
+            sb = torch.rand(n_local, generator=gen, device=dev) * 0.009 + 0.001
+            bias = torch.randint(-1000, 1001, (n_local,), generator=gen, device=dev, dtype=torch.int32)
+            fused = bias - 3 * w.to(torch.int32).sum(dim=1, dtype=torch.int32)
+            layers.append(lin.W8A8RequantLinear(w, sb, 0.05, 3, 0.1, -5, fused))
+            del w
+        a_host = torch.randint(-128, 128, (M, K), dtype=torch.int8).pin_memory()
+        prepare, in_bytes, out_bytes, dtype = "pack", M * K, M * n_local, "int8"
+    else:  # c5
+        bl = 32
+        for r in range(R):
+            nib = torch.randint(0, 256, (n_local, K // 2), generator=gen, device=dev, dtype=torch.uint8)
+            sc = (torch.rand((n_local, K // bl), generator=gen, device=dev) * 0.005 + 0.001).to(torch.float16)
+            bias = (torch.randn(n_local, generator=gen, device=dev) * 0.1).to(torch.float16)
+            layers.append(lin.W4A16Linear(nib, sc, K, bl, "f16", bias=bias))
+            del nib
+        a_host = torch.randn((M, K), dtype=torch.float32).to(torch.float16).pin_memory()
+        prepare, in_bytes, out_bytes, dtype = "pack", M * K * 2, M * n_local * 2, "f16"
+    return layers, a_host, prepare, in_bytes, out_bytes, dtype
+
+
+def roofline_of(cfg, peaks, ops_local, ms_gemm, ms_sustained_step, n_local, world):
+    """Tensor roofline of the run_gemm kernel: the burst loop (milliseconds) against the burst peak, the sustained
+    step loop (seconds, power cap included) against the sustained peak, and against the MMA issue rate."""
+    mult = 2.0 if cfg != "c5" else 1.0      # the int8 tensor rate is twice the bf16 rate (the file has no int8 figure)
+    peak_burst, peak_sust = mult * peaks["bf16"], mult * peaks["bf16_sustained"]
+    achieved = ops_local / (ms_gemm * 1e-3) / 1e12
+    issue = ISSUE_RATE_INT8_TOPS * (1.0 if cfg != "c5" else 0.5)
+    r = {"bound": "tensor", "achieved": achieved, "peak": peak_burst, "unit": "TFLOP/s", "frac": achieved / peak_burst,
+         "frac_of_issue_rate": achieved / issue, "issue_rate": issue,
+         "algorithmic_bytes": algorithmic_bytes(cfg, n_local),
+         "traffic": NCU_TRAFFIC[cfg][0] if world == 1 else None,
+         "traffic_source": (f"ncu capture of an earlier run summarised in {NCU_TRAFFIC[cfg][1]} (one launch, dram read + write); "
+                            "not measured by this run") if world == 1 else None,
+         "note": (f"run_gemm kernel alone (a loop of milliseconds), per GPU; peak = {mult:g} x bf16_tflops (burst) of {peaks['source']}"
+                  + ("; the int8 tensor rate is twice the bf16 rate" if cfg != "c5" else "")
+                  + "; frac_of_issue_rate = achieved / the rate tcgen05.mma issues at (what ncu's tensor-pipe counter shows)")}
+    if ms_sustained_step:
+        a_s = ops_local / (ms_sustained_step * 1e-3) / 1e12
+        r["sustained"] = {"achieved": a_s, "peak": peak_sust, "frac": a_s / peak_sust,
+                          "note": f"whole step (prepare + run_gemm) continued for seconds; peak = {mult:g} x bf16_tflops_sustained of {peaks['source']}"}
+    return r
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -194,100 +343,6 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    cfg = args.config
-    M, K, N, desc = CONFIGS[cfg]
-    n_begin, n_local = pkg.shard_plan_n(N, world, rank)
-    gen = torch.Generator(device=dev)
-    gen.manual_seed(1234 + rank)
-
-    # ---- build R rotating weight sets for this rank's column shard -------------------------------
-    R = args.rotate
-    layers = []
-    if cfg == "c3":
-        for r in range(R):
-            # int4 weights of W ~ N(0, 0.02) quantised per channel: nibble = clamp(round(w / (absmax/8)), -8, 7) + 8
-            w = torch.randn((n_local, K), generator=gen, device=dev) * 0.02
-            s = w.abs().amax(dim=1) / 8.0
-            q = torch.clamp(torch.round(w / s[:, None]), -8, 7).to(torch.int16) + 8
-            nib = (q[:, 0::2] | (q[:, 1::2] << 4)).to(torch.uint8)
-            layers.append(lin.W4A8Linear(nib, s, K, "bf16", bias=torch.zeros(n_local, dtype=torch.bfloat16, device=dev)))
-            del w, q, nib
-        a_host = torch.randn((M, K), dtype=torch.float32).to(torch.bfloat16).pin_memory()
-        a_dev = a_host.to(dev)
-        in_bytes = M * K * 2
-        out_bytes = M * n_local * 2
-
-        def step_device(i):
-            L = layers[i % R]
-            L.quantize(a_dev)
-            return L.gemm(M)
-
-        def gemm_only(i):
-            return layers[i % R].gemm(M)
-        launches_per_step = 2
-        dtype = "int8"
-    elif cfg == "c4":
-        for r in range(R):
-            w = torch.randint(-127, 128, (n_local, K), generator=gen, device=dev, dtype=torch.int8)
-            sb = torch.rand(n_local, generator=gen, device=dev) * 0.009 + 0.001
-            bias = torch.randint(-1000, 1001, (n_local,), generator=gen, device=dev, dtype=torch.int32)
-            fused = bias - 3 * w.to(torch.int32).sum(dim=1, dtype=torch.int32)
-            layers.append(lin.W8A8RequantLinear(w, sb, 0.05, 3, 0.1, -5, fused))
-            del w
-        a_host = torch.randint(-128, 128, (M, K), dtype=torch.int8).pin_memory()
-        a_dev = a_host.to(dev)
-        in_bytes = M * K
-        out_bytes = M * n_local
-
-        def step_device(i):
-            L = layers[i % R]
-            L.pack(a_dev)
-            return L.gemm(M)
-
-        def gemm_only(i):
-            return layers[i % R].gemm(M)
-        launches_per_step = 2
-        dtype = "int8"
-    else:  # c5
-        bl = 32
-        for r in range(R):
-            nib = torch.randint(0, 256, (n_local, K // 2), generator=gen, device=dev, dtype=torch.uint8)
-            sc = (torch.rand((n_local, K // bl), generator=gen, device=dev) * 0.005 + 0.001).to(torch.float16)
-            bias = (torch.randn(n_local, generator=gen, device=dev) * 0.1).to(torch.float16)
-            layers.append(lin.W4A16Linear(nib, sc, K, bl, "f16", bias=bias))
-            del nib
-        a_host = torch.randn((M, K), dtype=torch.float32).to(torch.float16).pin_memory()
-        a_dev = a_host.to(dev)
-        in_bytes = M * K * 2
-        out_bytes = M * n_local * 2
-
-        def step_device(i):
-            L = layers[i % R]
-            L.pack(a_dev)
-            return L.gemm(M)
-
-        def gemm_only(i):
-            return layers[i % R].gemm(M)
-        launches_per_step = 2
-        dtype = "f16"
-
-    # The step's two launches replayed as one CUDA graph per weight set: the host then needs ~10 us per step
-    # instead of ~100 us of Python argument marshalling, which otherwise bounds the column shards on 2-8 GPUs.
-    eager_step, eager_gemm = step_device, gemm_only
-    if not args.no_graphs:
-        step_graphs = [L.captured(a_dev) for L in layers]
-        gemm_graphs = [L.captured(a_dev, gemm_only=True) for L in layers]
-
-        def step_device(i):   # noqa: F811
-            return step_graphs[i % R]()
-
-        def gemm_only(i):   # noqa: F811
-            return gemm_graphs[i % R]()
-
-    ops = 2.0 * M * N * K               # whole job (all ranks)
-    ops_local = 2.0 * M * n_local * K
-    unit = "TOPS" if cfg != "c5" else "TFLOP/s"
-
     def timed(fn, steps, warmup):
         for i in range(warmup):
             fn(i)
@@ -300,99 +355,171 @@ def run_ours(args):
         barrier()
         return max_over_ranks(e0.elapsed_time(e1) / steps)
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    ms_step = timed(step_device, args.steps, args.warmup)
-    ms_gemm = timed(gemm_only, args.steps, args.warmup)
-    # the timed region lasts milliseconds; keep the same step loop running for about a second and a half so that
-    # the clock samples (and the sustained figure) describe the kernels under load, power cap included
-    sustain_steps = int(min(20000, max(args.steps, math.ceil(args.sustain_s * 1e3 / ms_step)))) if args.sustain_s > 0 else 0
-    ms_sustained = timed(step_device, sustain_steps, 0) if sustain_steps else None
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None:
-        clocks["note"] = (f"sampled every {ClockSampler.PERIOD_MS} ms from the start of the timed region to the end of a "
-                          f"{sustain_steps}-step continuation of the same step loop")
+    def measure(cfg, steps, warmup, sustain_s, with_e2e, with_gather):
+        """One prefill configuration on this rank's column shard: device-timed step, run_gemm alone, sustained loop
+        with clock samples, optionally the host-to-host step and the gathered-output variants."""
+        M, K, N, desc = CONFIGS[cfg]
+        n_begin, n_local = pkg.shard_plan_n(N, world, rank)
+        R = rotation(cfg, n_local, args.rotate)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(1234 + rank)
+        layers, a_host, prepare, in_bytes, out_bytes, dtype = build_layers(torch, lin, cfg, n_local, R, dev, gen)
+        a_dev = a_host.to(dev)
 
-    # ---- end to end: pinned host activations in, result back to the host, every step --------------
-    out_host = torch.empty((M, n_local), dtype=layers[0].workspace(M)["out"].dtype).pin_memory()
-
-    def step_e2e(i):
-        layers[i % R].forward_host(a_host, out_host)
-    # PCIe-bound and therefore sensitive to what else the host is doing: five batches, the median batch is reported
-    e2e_steps = max(3, min(args.steps, 10))
-    timed(step_e2e, 1, 3)
-    e2e_batches = sorted(timed(step_e2e, e2e_steps, 0) for _ in range(5))
-    ms_e2e = e2e_batches[len(e2e_batches) // 2]
-
-    # ---- optional: the full output on every GPU -------------------------------------------------------
-    # (a) the step followed by an NCCL all-gather of the column shards; (b) the fused form: the GEMM's epilogue
-    # stores every tile into the peer-mapped output buffers of all ranks (tqt_cuda_set_output_replicas), no collective.
-    gather = None
-    if world > 1 and args.gather and cfg in ("c3", "c5"):
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only: no multicast binding
-        import torch.distributed._symmetric_memory as symm
-        out_local = layers[0].workspace(M)["out"]
-        staged = torch.empty((world * M, n_local), dtype=out_local.dtype, device=dev)
-        full = symm.empty((M, N), dtype=out_local.dtype, device=dev)
-        hdl = symm.rendezvous(full, dist.group.WORLD.group_name)
-        peers = [int(hdl.buffer_ptrs[r]) for r in range(world) if r != rank]
-        g_steps, g_warm = max(3, min(args.steps, 50)), 3
-
-        def step_nccl(i):
-            out = step_device(i)
-            dist.all_gather_into_tensor(staged, out)
-
-        def step_fused(i):
+        def step_device(i):
             L = layers[i % R]
-            (L.quantize if cfg == "c3" else L.pack)(a_dev)
-            pkg.set_output_replicas(full.data_ptr(), peers)
-            try:
-                L.gemm(M, out=full[:, n_begin:n_begin + n_local])
-            finally:
-                pkg.set_output_replicas(0, [])
+            getattr(L, prepare)(a_dev)
+            return L.gemm(M)
 
-        if not args.no_graphs:   # the fused step replayed as a graph too (the replica offsets are kernel arguments)
-            eager_fused, fused_graphs = step_fused, []
-            for li in range(R):
-                eager_fused(li)
-                torch.cuda.current_stream().synchronize()
-                gr = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(gr):
+        def gemm_only(i):
+            return layers[i % R].gemm(M)
+
+        # The step's two launches replayed as one CUDA graph per weight set: the host then needs ~10 us per step
+        # instead of ~100 us of Python argument marshalling, which otherwise bounds the column shards on 2-8 GPUs.
+        eager_step = step_device
+        if not args.no_graphs:
+            step_graphs = [L.captured(a_dev) for L in layers]
+            gemm_graphs = [L.captured(a_dev, gemm_only=True) for L in layers]
+
+            def step_device(i):   # noqa: F811
+                return step_graphs[i % R]()
+
+            def gemm_only(i):   # noqa: F811
+                return gemm_graphs[i % R]()
+
+        ops = 2.0 * M * N * K               # whole job (all ranks)
+        ops_local = 2.0 * M * n_local * K
+        unit = "TOPS" if cfg != "c5" else "TFLOP/s"
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        ms_step = timed(step_device, steps, warmup)
+        ms_gemm = timed(gemm_only, steps, warmup)
+        # the timed region lasts milliseconds; keep the same step loop running for a second or so, so that the clock
+        # samples (and the sustained figure) describe the kernels under load, power cap included
+        sustain_steps = int(min(20000, max(steps, math.ceil(sustain_s * 1e3 / ms_step)))) if sustain_s > 0 else 0
+        ms_sustained = timed(step_device, sustain_steps, 0) if sustain_steps else None
+        clocks = sampler.stop() if rank == 0 else None
+        if clocks is not None:
+            clocks["note"] = (f"sampled every {ClockSampler.PERIOD_MS} ms from the start of the timed region to the end of a "
+                              f"{sustain_steps}-step continuation of the same step loop")
+        rec = {
+            "metric": {"c3": "w4a8_gemm_int8_tops", "c4": "w8a8_gemm_int8_tops", "c5": "w4a16_gemm_f16_tflops"}[cfg],
+            "value": ops / (ms_step * 1e-3) / 1e12, "unit": unit, "ms_per_step": ms_step, "dtype": dtype,
+            "config": workload_config(cfg, world, n_local, R, set_bytes_of(cfg, n_local), graphs=not args.no_graphs),
+            "gemm_only_ms": ms_gemm,
+            "sustained": None if ms_sustained is None else {"steps": sustain_steps, "ms_per_step": ms_sustained,
+                                                            "value": ops / (ms_sustained * 1e-3) / 1e12, "unit": unit},
+            "roofline": roofline_of(cfg, peaks, ops_local, ms_gemm, ms_sustained, n_local, world),
+            "gpu_launches": 2 * steps, "clocks": clocks,
+        }
+
+        if with_e2e:
+            # ---- end to end: pinned host activations in, result back to the host, every step --------------
+            out_host = torch.empty((M, n_local), dtype=layers[0].workspace(M)["out"].dtype).pin_memory()
+
+            def step_e2e(i):
+                layers[i % R].forward_host(a_host, out_host)
+            # PCIe-bound and therefore sensitive to what else the host is doing: five batches, the median batch is reported
+            e2e_steps = max(3, min(steps, 10))
+            timed(step_e2e, 1, 3)
+            e2e_batches = sorted(timed(step_e2e, e2e_steps, 0) for _ in range(5))
+            ms_e2e = e2e_batches[len(e2e_batches) // 2]
+            # the same bytes over the same three streams with no kernel in between: what PCIe alone allows
+            floor = pcie_floor(torch, layers[0], a_host, out_host, timed, e2e_steps)
+            rec["e2e"] = {"value": ops / (ms_e2e * 1e-3) / 1e12, "unit": unit, "h2d_bytes_per_step": in_bytes,
+                          "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e, "batches_ms": e2e_batches,
+                          "pcie_floor_ms": floor,
+                          "note": f"median of 5 batches of {e2e_steps} steps; pcie_floor_ms = the step's host-to-device and "
+                                  "device-to-host copies alone (same chunks, same streams, no kernels), median of 5 batches"}
+
+        # ---- optional: the full output on every GPU -------------------------------------------------------
+        # (a) the step followed by an NCCL all-gather of the column shards; (b) the fused form: the GEMM's epilogue
+        # stores every tile into the peer-mapped output buffers of all ranks (tqt_cuda_set_output_replicas), no collective.
+        if with_gather and world > 1 and cfg in ("c3", "c5"):
+            import torch.distributed._symmetric_memory as symm
+            out_local = layers[0].workspace(M)["out"]
+            staged = torch.empty((world * M, n_local), dtype=out_local.dtype, device=dev)
+            full = symm.empty((M, N), dtype=out_local.dtype, device=dev)
+            hdl = symm.rendezvous(full, dist.group.WORLD.group_name)
+            peers = [int(hdl.buffer_ptrs[r]) for r in range(world) if r != rank]
+            done = torch.zeros(1, dtype=torch.int32, device=dev)
+            g_steps, g_warm = max(3, min(steps, 50)), 3
+
+            def step_nccl(i):
+                out = step_device(i)
+                dist.all_gather_into_tensor(staged, out)
+
+            def fused_kernels(i):
+                L = layers[i % R]
+                getattr(L, prepare)(a_dev)
+                with pkg.output_replicas(full.data_ptr(), full.numel() * full.element_size(), peers):
+                    L.gemm(M, out=full[:, n_begin:n_begin + n_local])
+
+            if not args.no_graphs:   # the fused step replayed as a graph too (the replica offsets are kernel arguments)
+                eager_fused, fused_graphs = fused_kernels, []
+                for li in range(R):
                     eager_fused(li)
-                fused_graphs.append(gr)
+                    torch.cuda.current_stream().synchronize()
+                    gr = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(gr):
+                        eager_fused(li)
+                    fused_graphs.append(gr)
 
-            def step_fused(i):   # noqa: F811
-                fused_graphs[i % R].replay()
+                def fused_kernels(i):   # noqa: F811
+                    fused_graphs[i % R].replay()
 
-        ms_nccl = timed(step_nccl, g_steps, g_warm)
-        ms_fused = timed(step_fused, g_steps, g_warm)
-        # the two forms must agree: run step 0 both ways and compare every rank's copy of the full output
-        full.zero_()
-        barrier()
-        step_fused(0)
-        barrier()
-        step_nccl(0)
-        barrier()
-        same = all(torch.equal(full[:, r * n_local:(r + 1) * n_local], staged[r * M:(r + 1) * M]) for r in range(world))
-        flag = torch.tensor([1 if same else 0], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        gather = {"nccl_step_ms": ms_nccl, "fused_step_ms": ms_fused, "outputs_equal_on_all_ranks": bool(flag.item()),
-                  "bytes_per_rank": M * n_local * out_local.element_size(),
-                  "note": "nccl: step + all_gather_into_tensor of the column shards; fused: the GEMM epilogue stores "
-                          "each tile into every rank's output buffer (peer stores over NVLink), no collective"}
+            def step_fused(i):
+                # peers may read the full output only when every rank's kernel has completed: the cross-rank completion
+                # signal (a one-int all-reduce) is part of the timed step, as the all-gather's own synchronisation is
+                fused_kernels(i)
+                dist.all_reduce(done)
 
+            ms_nccl = timed(step_nccl, g_steps, g_warm)
+            ms_fused = timed(step_fused, g_steps, g_warm)
+            ms_fused_kernels = timed(fused_kernels, g_steps, g_warm)
+            # the two forms must agree: run step 0 both ways and compare every rank's copy of the full output
+            full.zero_()
+            barrier()
+            step_fused(0)
+            barrier()
+            step_nccl(0)
+            barrier()
+            same = all(torch.equal(full[:, r * n_local:(r + 1) * n_local], staged[r * M:(r + 1) * M]) for r in range(world))
+            flag = torch.tensor([1 if same else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            rec["gather"] = {"nccl_step_ms": ms_nccl, "fused_step_ms": ms_fused, "fused_kernels_only_ms": ms_fused_kernels,
+                             "outputs_equal_on_all_ranks": bool(flag.item()),
+                             "bytes_per_rank": M * n_local * out_local.element_size(),
+                             "note": "nccl: step + all_gather_into_tensor of the column shards; fused: the GEMM epilogue stores "
+                                     "each tile into every rank's output buffer (peer stores over NVLink) + a one-int all-reduce "
+                                     "as the cross-rank completion signal; fused_kernels_only_ms leaves that signal out"}
+        del layers
+        torch.cuda.empty_cache()
+        return rec
+
+    cfg = args.config
+    M, K, N, desc = CONFIGS[cfg]
+    head = measure(cfg, args.steps, args.warmup, args.sustain_s, with_e2e=True, with_gather=args.gather)
     fault = pkg.read_device_fault()
 
-    # ---- decode GEMV (M=1, K=N=4096, f32), captured in a CUDA graph over rotating weights ----------
+    # ---- the other two prefill configurations, the decode GEMV and the layout kernels (one GPU, headline run) ---
+    extra = {}
+    if cfg == "c3" and world == 1 and not args.no_extra:
+        for c in ("c4", "c5"):
+            extra[c] = measure(c, max(3, min(args.steps, 20)), 3, min(args.sustain_s, 0.7), with_e2e=False, with_gather=False)
+        extra["layout"] = bench_layout(torch, pkg, dev, peaks)
     decode = None
     if cfg == "c3" and rank == 0 and not args.no_decode:
         decode = bench_decode(torch, lin, pkg, dev, peaks)
+        d16 = bench_decode(torch, lin, pkg, dev, peaks, M=16)
+        decode["m16"] = {k: d16[k] for k in ("workload", "value", "unit", "us_per_gemv", "bytes_per_gemv", "read_ceiling", "roofline")}
         decode["other_shapes"] = []
         for (K2, N2, c2) in ((4096, 14336, 16), (8192, 28672, 6)):   # the prefill configs' weight shapes at M=1
             d2 = bench_decode(torch, lin, pkg, dev, peaks, K=K2, N=N2, copies=c2)
             decode["other_shapes"].append({"workload": d2["workload"], "gbs": d2["value"], "us_per_gemv": d2["us_per_gemv"],
                                            "frac": d2["roofline"]["frac"], "read_ceiling_gbs": d2["read_ceiling"]["gbs"]})
+    fault = fault or pkg.read_device_fault()
 
     if rank != 0:
         if world > 1:
@@ -402,47 +529,98 @@ def run_ours(args):
     # ---- CPU baseline on a bounded sample (rank 0, N=1 only) -------------------------------------------
     cpu = None
     if world == 1 and not args.no_cpu and cfg == "c3":
-        tops, rows, secs, nthreads = cpu_w4a8_sample(M, K, N, budget_s=12.0)
-        cpu = {"value": tops, "unit": "TOPS", "cores": nthreads, "kind": "port",
-               "sample": f"{rows} of {M} rows x all N x K in {secs:.1f} s, oracle/tqt_oracle.c with {nthreads} OpenMP threads"}
+        tops, rows, secs, nthreads, kind = cpu_w4a8_sample(M, K, N, budget_s=12.0)
+        cpu = {"value": tops, "unit": "TOPS", "cores": nthreads, "kind": kind,
+               "sample": cpu_sample_text(rows, M, N, K, nthreads, kind, secs)}
 
-    # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch, from the ncu captures summarised under profiles/
-    ncu_traffic = {"c3": 56.2e6, "c4": 33.9e6, "c5": 1419.1e6}[cfg] if world == 1 else None
-    int8_peak = 2.0 * peaks["bf16_sustained"] if cfg != "c5" else peaks["bf16_sustained"]
-    achieved = ops_local / (ms_gemm * 1e-3) / 1e12
     line = {
-        "metric": "w4a8_gemm_int8_tops" if cfg == "c3" else ("w8a8_gemm_int8_tops" if cfg == "c4" else "w4a16_gemm_f16_tflops"),
-        "value": ops / (ms_step * 1e-3) / 1e12, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype,
-        "data": "synthetic",
-        "config": {"workload": desc, "step": "activation quantise+pack (or pack) kernel + run_gemm, weights packed once outside" +
-                           ("" if args.no_graphs else "; the two launches replayed as one CUDA graph"),
-                   "parallelism": f"N-sharded x{world}, no collective" if world > 1 else "single GPU",
-                   "n_per_gpu": n_local,
-                   "l2": f"rotating {R} weight/output sets per rank ({R * (layers[0].b_packed.numel() + out_bytes) / 1e6:.0f} MB) > 126 MB L2"},
-        "gemm_only_ms": ms_gemm,
-        "sustained": None if ms_sustained is None else {"steps": sustain_steps, "ms_per_step": ms_sustained,
-                                                        "value": ops / (ms_sustained * 1e-3) / 1e12, "unit": unit},
-        "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
-                     "frac": achieved / int8_peak, "traffic": ncu_traffic,
-                     "note": ("run_gemm kernel alone, per GPU; peak = 2 x bf16_tflops_sustained of " + peaks["source"] +
-                              " (int8 tensor rate is twice the bf16 rate)") if cfg != "c5" else
-                             "run_gemm kernel alone, per GPU; peak = bf16_tflops_sustained of " + peaks["source"]},
-        "e2e": {"value": ops / (ms_e2e * 1e-3) / 1e12, "unit": unit, "h2d_bytes_per_step": in_bytes,
-                "d2h_bytes_per_step": out_bytes, "ms_per_step": ms_e2e,
-                "batches_ms": e2e_batches, "note": f"median of 5 batches of {e2e_steps} steps"},
-        "gpu_launches": launches_per_step * args.steps,
-        "clocks": clocks, "device_fault": fault,
+        "metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": head["dtype"], "data": "synthetic", "config": head["config"],
+        "gemm_only_ms": head["gemm_only_ms"], "sustained": head["sustained"], "roofline": head["roofline"],
+        "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "clocks": head["clocks"], "device_fault": fault,
     }
-    if gather is not None:
-        line["gather"] = gather
+    if "gather" in head:
+        line["gather"] = head["gather"]
     if cpu:
         line["cpu_baseline"] = cpu
+    for c in ("c4", "c5", "layout"):
+        if c in extra:
+            line[c] = extra[c]
     if decode:
         line["decode_gemv"] = decode
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def pcie_floor(torch, layer, a_host, out_host, timed, steps):
+    """The host<->device copies of one forward_host call and nothing else: the same row chunks on the same copy
+    streams, a chunk's result copy ordered after its input copy as in the real step, no kernel."""
+    m = a_host.shape[0]
+    st = layer._pipe(m, 4, a_host.dtype)
+    evs = [torch.cuda.Event() for _ in st["bounds"]]
+
+    def copies(i):
+        cur = torch.cuda.current_stream()
+        st["s_in"].wait_stream(cur)
+        st["s_out"].wait_stream(cur)
+        for c, (r0, r1) in enumerate(st["bounds"]):
+            with torch.cuda.stream(st["s_in"]):
+                st["a_dev"][r0:r1].copy_(a_host[r0:r1], non_blocking=True)
+                evs[c].record()
+            with torch.cuda.stream(st["s_out"]):
+                st["s_out"].wait_event(evs[c])
+                out_host[r0:r1].copy_(st["out_dev"][r0:r1], non_blocking=True)
+        cur.wait_stream(st["s_in"])
+        cur.wait_stream(st["s_out"])
+
+    timed(copies, 1, 2)
+    batches = sorted(timed(copies, steps, 0) for _ in range(5))
+    return batches[len(batches) // 2]
+
+
+def bench_layout(torch, pkg, dev, peaks):
+    """The layout kernels of the C3 shapes as HBM GB/s: the one-time RHS pack (nibbles [14336, 2048 bytes] ->
+    packed blocks with row sums) and the per-step activation quantise+pack (bf16 [2048, 4096] -> int8 blocks + scale,
+    zero point).  Each is timed over rotating buffer sets larger than L2, CUDA events on the current stream."""
+    M, K, N, _ = CONFIGS["c3"]
+    uk = pkg.GemmW4A8("bf16")
+    pkg.use_current_torch_stream()
+    out = {}
+
+    def time_us(fn, sets, reps=3):
+        for i in range(sets):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for r in range(reps):
+            for i in range(sets):
+                fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * sets)
+
+    sets = 6
+    nibs = [torch.randint(0, 256, (N, K // 2), device=dev, dtype=torch.uint8) for _ in range(sets)]
+    packed = [torch.empty(uk.get_b_packed_size(N, K), dtype=torch.uint8, device=dev) for _ in range(sets)]
+    us = time_us(lambda i: uk.run_bt_pack(N, K, K, K, 0, nibs[i], packed[i]), sets)
+    nbytes = N * K // 2 + packed[0].numel()
+    out["rhs_pack_qsi4cxp"] = {"workload": f"run_bt_pack qsi4cx N={N} K={K}", "us": us, "bytes": nbytes,
+                               "gbs": nbytes / (us * 1e-6) / 1e9, "frac": nbytes / (us * 1e-6) / 1e9 / peaks["hbm"]}
+    del nibs, packed
+    sets = 8
+    acts = [torch.randn((M, K), device=dev).to(torch.bfloat16) for _ in range(sets)]
+    ap = [torch.empty(uk.get_a_packed_size(M, K), dtype=torch.uint8, device=dev) for _ in range(sets)]
+    sa = torch.empty(M, dtype=torch.float32, device=dev)
+    zp = torch.empty(M, dtype=torch.int32, device=dev)
+    us = time_us(lambda i: pkg.quant_pack_qai8dxp(acts[i], ap[i], sa, zp), sets, reps=6)
+    nbytes = M * K * 3 + 8 * M
+    out["quant_pack_qai8dxp_bf16"] = {"workload": f"tqt_run_quant_pack_qai8dxp_bf16 M={M} K={K}", "us": us, "bytes": nbytes,
+                                      "gbs": nbytes / (us * 1e-6) / 1e9, "frac": nbytes / (us * 1e-6) / 1e9 / peaks["hbm"]}
+    out["note"] = f"bytes in + bytes out per launch / CUDA-event time over rotating buffer sets (> 126 MB); frac of hbm_gbs of {peaks['source']}"
+    return out
 
 
 def _graph_time_us(torch, stream, launch_all, launches, reps):
@@ -465,12 +643,12 @@ def _graph_time_us(torch, stream, launch_all, launches, reps):
     return e0.elapsed_time(e1) * 1e3 / (reps * launches)
 
 
-def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20):
-    """GEMV M=1 f32: one CUDA graph replays `copies` GEMVs over distinct weight sets (together larger
-    than L2), so every launch streams its weights from HBM.  `read_ceiling` is a kernel with the same
+def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20, M=1):
+    """GEMV, M rows (decode batch), f32: one CUDA graph replays `copies` GEMVs over distinct weight sets (together
+    larger than L2), so every launch streams its weights from HBM.  `read_ceiling` is a kernel with the same
     launch shape that only reads the same number of bytes from the same buffers, timed the same way."""
     import ctypes
-    nbytes = N * K // 2 + 3 * 4 * N + K + 8   # weights + scale_b, bias, D + int8 row + (scale, zp)
+    nbytes = N * K // 2 + 2 * 4 * N + M * (4 * N + K + 8)   # weights + scale_b, bias + per row: D, int8 row, (scale, zp)
     gen = torch.Generator(device=dev)
     gen.manual_seed(7)
     layers = []
@@ -478,16 +656,16 @@ def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20
         nib = torch.randint(0, 256, (N, K // 2), generator=gen, device=dev, dtype=torch.uint8)
         sb = torch.rand(N, generator=gen, device=dev) * 0.01
         layers.append(lin.W4A8Linear(nib, sb, K, "f32", bias=torch.randn(N, generator=gen, device=dev) * 0.1))
-    a = torch.randn((1, K), generator=gen, device=dev)
+    a = torch.randn((M, K), generator=gen, device=dev)
     for L in layers:
         L.quantize(a)
-        L.gemm(1)
+        L.gemm(M)
     torch.cuda.synchronize()
     stream = torch.cuda.Stream()
 
     def gemvs():
         for L in layers:
-            L.gemm(1)
+            L.gemm(M)
 
     us = _graph_time_us(torch, stream, gemvs, copies, reps)
     lib = pkg.lib()
@@ -504,12 +682,15 @@ def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20
     pkg.set_stream(torch.cuda.current_stream().cuda_stream)
     gbs = nbytes / (us * 1e-6) / 1e9
     return {"metric": "w4a8_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "us_per_gemv": us,
-            "workload": f"gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp decode M=1 K={K} N={N}",
+            "workload": f"gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp decode M={M} K={K} N={N}",
             "bytes_per_gemv": nbytes, "gpu_launches": reps * copies,
             "read_ceiling": {"gbs": rd / (us_read * 1e-6) / 1e9, "us": us_read,
                              "note": "a kernel with the GEMV's launch shape that only reads the same bytes, same graph"},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
-                         "frac": gbs / peaks["hbm"], "traffic": 8.698e6 if (K, N) == (4096, 4096) else None,
+                         "frac": gbs / peaks["hbm"], "algorithmic_bytes": nbytes,
+                         "traffic": 8.698e6 if (K, N, M) == (4096, 4096, 1) else None,
+                         "traffic_source": ("ncu capture of an earlier run summarised in profiles/gemv_w4a8_c2.txt (one launch, dram "
+                                            "read + write); not measured by this run") if (K, N, M) == (4096, 4096, 1) else None,
                          "note": f"CUDA-graph replay of {copies} back-to-back GEMVs over distinct weights; peak = hbm_gbs of {peaks['source']}"}}
 
 
@@ -526,6 +707,7 @@ def main():
     ap.add_argument("--no-graphs", action="store_true", help="issue the step's launches from Python instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="headline configuration only: skip the c4 / c5 / layout sub-records")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -59,19 +59,40 @@ void tqt_run_a_unpack_f16_128x128_sm100a(size_t m, size_t k, const void *A_packe
 void tqt_shard_plan_n(size_t n, size_t world, size_t rank, size_t *n_begin, size_t *n_count);
 
 /* Output replicas for the calling thread's following run_gemm calls (fused GEMM -> all-gather): every
- * element a kernel stores at address x inside the buffer that starts at local_base is also stored at
- * replica_bases[i] + (x - local_base), i < count <= 7.  The replicas are copies of the same output buffer
+ * element a kernel stores at address x inside the buffer [local_base, local_base + local_bytes) is also
+ * stored at replica_bases[i] + (x - local_base), i < count <= 7; every replica buffer must be at least
+ * local_bytes long.  While replicas are set, a run_gemm whose output range [D, D + ((m-1)*ldd + n) * sizeof(TD))
+ * is not inside the registered buffer is refused with TQT_CUDA_INVALID_ARGUMENT and launches nothing (its
+ * replica stores would land at arbitrary addresses of other GPUs).  The setting stays until it is cleared:
+ * clear it (count = 0) in the same scope that set it, also on error paths.  The replicas are copies of the same output buffer
  * mapped from other GPUs (CUDA IPC or symmetric memory): the epilogue writes each tile to all of them with
  * plain peer stores while the mainloop of the next tile runs, so no separate collective is needed.  The
  * stores are visible to the peers once the kernel has completed; ordering against the peers' readers is the
  * caller's (a barrier after the call).  count = 0 switches it off.  Honoured by the packed W4A8 and W4A16
  * kernel types on their tensor-core path; any other run_gemm reports TQT_CUDA_UNSUPPORTED while replicas
  * are set.  No counterpart in the reference, whose kernels write one buffer. */
-void tqt_cuda_set_output_replicas(const void *local_base, void *const *replica_bases, size_t count);
+void tqt_cuda_set_output_replicas(const void *local_base, size_t local_bytes, void *const *replica_bases, size_t count);
 
 /* Which device kernel a run_gemm call of the given shape would launch: 0 = tcgen05 tensor-core
- * GEMM, 1 = HBM-streaming GEMV (m <= 8), 2 = generic CUDA-core kernel (unpacked operands). */
+ * GEMM, 1 = HBM-streaming GEMV (m <= 16), 2 = generic CUDA-core kernel (unpacked operands). */
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k);
+
+/* Test switch: force a kernel path ("auto" | "umma" | "gemv" | "simt") and a tensor-core kernel ("single" |
+ * "pair" | "ts"; NULL = automatic) for all later run_gemm calls of the process, replacing what the environment
+ * variables TQT_B200_PATH / TQT_B200_UMMA (read once, at the first call) gave.  A forced path that cannot take a
+ * call reports TQT_CUDA_UNSUPPORTED. */
+void tqt_cuda_debug_set_path(const char *path, const char *umma);
+
+/* Test knob for the failure path.  Every wait inside the tensor-core kernels (on an mbarrier that a bulk copy,
+ * an MMA or another warp completes) is bounded: a wait that runs out records a code that
+ * tqt_cuda_read_device_fault() returns (0x100 producer, 0x200 / 0x300 MMA issuer, 0x400 epilogue, 0x500
+ * converter, 0x700 producer draining its copies), the CTA stops issuing work, lets its copies land, frees its
+ * tensor memory and returns without storing the tile; the context stays usable.  wait_shift shortens every
+ * limit (about one second) by that many binary orders of magnitude; flags bit 0 makes one producer warp of the
+ * packed W4A8 / W4A16 tensor-memory kernels withhold the copies and the barrier arrive of its first stage, so
+ * that the waits downstream of it run out.  Process-wide, for the launches that follow; (0, 0) restores normal
+ * operation.  Nothing traps, faults or spins without a limit. */
+void tqt_cuda_debug_inject_wait_failure(unsigned wait_shift, unsigned flags);
 
 /* Diagnostic: install a caller-owned device buffer of 16 int64 per CTA (148 CTAs at most) that the
  * tensor-core GEMM fills with the cycles each warp role spent waiting (producer, MMA issuer, one

@@ -23,3 +23,17 @@ def oracle():
 def golden():
     import numpy as np
     return np.load(os.path.join(ROOT, "tests", "golden", "ref_vectors.npz"))
+
+
+@pytest.fixture
+def force_path():
+    """Returns a function force(path, umma=None) that forces a kernel path / tensor-core kernel of the library
+    for the rest of the test (tqt_cuda_debug_set_path); the automatic choice is restored afterwards."""
+    from __graft_entry__ import load
+    pkg = load()
+
+    def force(path, umma=None):
+        pkg.debug_set_path(path, umma)
+
+    yield force
+    pkg.debug_set_path(None, None)

@@ -139,17 +139,45 @@ def test_output_replicas_argument_checks(pkg):
     import ctypes as C
     lib = pkg.lib()
     f = lib.tqt_cuda_set_output_replicas
-    f.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t]
+    f.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_size_t]
     f.restype = None
-    arr = (C.c_void_p * 8)(*[C.c_void_p(4096 * (i + 2)) for i in range(8)])
-    f(C.c_void_p(4096), arr, 8)
+    arr = (C.c_void_p * 8)(*[C.c_void_p(1 << (20 + i)) for i in range(8)])
+    f(C.c_void_p(4096), 4096, arr, 8)
     assert lib.tqt_cuda_get_last_status() != 0
-    f(None, arr, 2)
+    f(None, 4096, arr, 2)
     assert lib.tqt_cuda_get_last_status() != 0
-    f(C.c_void_p(4096), arr, 7)
+    f(C.c_void_p(4096), 0, arr, 2)          # a registered buffer needs its size
+    assert lib.tqt_cuda_get_last_status() != 0
+    f(C.c_void_p(4096), 4096, arr, 7)
     assert lib.tqt_cuda_get_last_status() == 0
-    f(None, None, 0)
+    f(None, 0, None, 0)
     assert lib.tqt_cuda_get_last_status() == 0
+
+
+def test_output_replicas_refuse_an_output_outside_the_registered_buffer(pkg):
+    """While replicas are set, a run_gemm whose output range is not inside [local_base, local_base + local_bytes)
+    is refused before anything is launched (host-side check: fake addresses, no GPU needed).  The refusal is what
+    is tested: the accepted case is covered on a GPU."""
+    base, size = 1 << 30, 64 * 256 * 2          # a 64 x 256 bf16 output buffer
+    peers = [1 << 31, (1 << 31) + (1 << 24)]
+    w = pkg.GemmW4A8("bf16")
+    p = pkg.QaI8DxQsI4CxParams(16, 16, 16)
+    try:
+        pkg.set_output_replicas(base, size, peers)
+        for (m, n, D, ldd) in ((64, 256, base - 512, 256),          # starts before the buffer
+                               (64, 256, base + 512, 256),          # runs past its end
+                               (65, 256, base, 256),                # one row too many
+                               (64, 128, base + 2 * 200, 256),      # column slice that overhangs the last row
+                               (64, 256, 1 << 29, 256)):            # another buffer altogether
+            with pytest.raises(pkg.TqtError):
+                w.run_gemm(m, n, 128, 16, 128, 0, 16, 128, 0, None, n, D, ldd, None, -1.0, 1.0, p)
+            assert pkg.lib().tqt_cuda_get_last_status() == 1
+        w16 = pkg.GemmW4A16("f16")
+        with pytest.raises(pkg.TqtError):
+            w16.run_gemm(64, 256, 128, 32, 16, 128, 0, 16, 128, 0, 16, 4, None, 256, base + 512, 256, None, -1.0, 1.0)
+        assert pkg.lib().tqt_cuda_get_last_status() == 1
+    finally:
+        pkg.set_output_replicas(0, 0, [])
 
 
 def test_headers_compile_as_c_and_cxx(tmp_path):

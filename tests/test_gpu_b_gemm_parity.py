@@ -6,15 +6,16 @@ as well (the stated bars, rel 1e-3 for f32 and 2e-2 for f16/bf16, are implied). 
 f16 products in f32 in a different order than the oracle: tolerance rel 2e-2 with an RMS floor,
 plus the reference's own thresholds (abs 1.0, cosine 0.9999; test/common/test_common.h:47-66).
 
-Each packed kernel type is run on the path run_gemm picks by itself and, through TQT_B200_PATH, on
-the generic CUDA-core path, so that the tensor-core, GEMV and CUDA-core kernels check each other.
+Each packed kernel type is run on the path run_gemm picks by itself and, through the library's path switch
+(tqt_cuda_debug_set_path), on the generic CUDA-core path, so that the tensor-core, GEMV and CUDA-core kernels
+check each other.
 """
 import numpy as np
 import pytest
 
 from oracle.tqo import TD_BF16, TD_F16, TD_F32
-from tqt_testlib import (FMAX, bf16_bits_to_f32, cosine, f16_bits_to_f32, f32_to_bf16_bits, rel_err, run_i32_packed,
-                         run_i32_unpacked, run_requant, run_w4a16, run_w4a8)
+from tqt_testlib import (FMAX, bf16_bits_to_f32, cosine, f16_bits_to_f32, f32_to_bf16_bits, rel_err, requant_acceptance_case,
+                         requant_acceptance_check, run_i32_packed, run_i32_unpacked, run_requant, run_w4a16, run_w4a8)
 
 pytestmark = pytest.mark.gpu
 
@@ -27,8 +28,8 @@ PATHS = ["auto", "simt"]
 
 
 @pytest.fixture(params=PATHS)
-def path(request, monkeypatch):
-    monkeypatch.setenv("TQT_B200_PATH", request.param)
+def path(request, force_path):
+    force_path(request.param)
     return request.param
 
 
@@ -84,6 +85,17 @@ def test_requant_bit_exact(oracle, path, m, n, k, scale_d):
     assert np.array_equal(got, want)
     if scale_d == 30.0:
         assert (np.abs(want.astype(np.int32)) < 127).mean() > 0.5
+
+
+@pytest.mark.parametrize("m,n,k", I8_SHAPES + [(200, 300, 1000)])
+def test_requant_reference_acceptance(oracle, path, m, n, k):
+    """The reference's own test of this kernel type, inputs and criterion (quantized_gemm_test_runner.h:193-306),
+    beside the bit-exact comparison with the oracle."""
+    c = requant_acceptance_case(oracle, m, n, k)
+    got = run_requant(c["A"], c["B"], c["scale_a"], c["scale_b"], c["scale_d"], c["zp_d"], c["bias_fused"])
+    requant_acceptance_check(got, c)
+    want = oracle.gemm_reqi32toi8(c["A"], c["B"], True, c["scale_a"], c["scale_b"], c["scale_d"], c["zp_d"], c["bias_fused"])
+    assert np.array_equal(got, want)
 
 
 def test_requant_options(oracle, path):
@@ -147,18 +159,31 @@ def test_w4a8_options(oracle, path, td, has_c, has_bias, clamp, m, n, k):
     assert np.array_equal(got, want)
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 11, 16])
-@pytest.mark.parametrize("n,k", [(128, 128), (130, 258), (512, 1024), (1000, 384), (4096, 4096)])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8, 9, 11, 16, 17])
+@pytest.mark.parametrize("n,k", [(128, 128), (130, 258), (512, 1024), (1000, 384), (4096, 4096), (8, 128), (24, 256), (5000, 640)])
 def test_w4a8_decode_gemv(oracle, m, n, k):
-    """m <= 16 takes the HBM-streaming GEMV; integer combine makes it bit-exact like the GEMM."""
+    """m <= 16 takes the HBM-streaming GEMV (17 is the first tensor-core size); the integer combine makes it
+    bit-exact like the GEMM.  Column counts that are not multiples of 16 leave the last CTA half a set."""
     rng = np.random.default_rng(m * 100 + n + k)
     q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, m, n, k, "f32", m % 2 == 0, True, None)
     got = run_w4a8("f32", q, sa, zp, nib, sb, Cm, bias, clamp)
     assert np.array_equal(got, want)
 
 
-def test_w4a8_decode_on_the_tensor_core_path(oracle, monkeypatch):
-    monkeypatch.setenv("TQT_B200_PATH", "umma")
+@pytest.mark.parametrize("td", ["f16", "bf16"])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (7, 520, 384), (16, 1000, 512), (12, 14336, 256)])
+def test_w4a8_decode_gemv_forced(oracle, force_path, td, m, n, k):
+    """The GEMV forced through the path switch (so that nothing falls through to the GEMM), 16-bit outputs,
+    a column count whose 8-column groups need more than one round of CTAs."""
+    force_path("gemv")
+    rng = np.random.default_rng(m + n + k)
+    q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, m, n, k, td, m % 2 == 1, True, (-0.75, 0.5))
+    got = run_w4a8(td, q, sa, zp, nib, sb, Cm, bias, clamp)
+    assert np.array_equal(got, want)
+
+
+def test_w4a8_decode_on_the_tensor_core_path(oracle, force_path):
+    force_path("umma")
     rng = np.random.default_rng(77)
     q, sa, zp, nib, sb, Cm, bias, clamp, want = _w4a8_case(oracle, rng, 3, 300, 512, "bf16", False, True, None)
     assert np.array_equal(run_w4a8("bf16", q, sa, zp, nib, sb, Cm, bias, clamp), want)
@@ -213,10 +238,9 @@ def test_w4a16_big(oracle, path, m, n, k, bl):
 
 # ---- the two tensor-core kernels against each other and the oracle ---------------------------------------
 @pytest.fixture(params=["single", "pair"])
-def umma_variant(request, monkeypatch):
-    """TQT_B200_UMMA forces the single-CTA or the CTA-pair (cta_group::2) kernel whatever the shape."""
-    monkeypatch.setenv("TQT_B200_PATH", "umma")
-    monkeypatch.setenv("TQT_B200_UMMA", request.param)
+def umma_variant(request, force_path):
+    """Forces the single-CTA or the CTA-pair (cta_group::2) kernel whatever the shape."""
+    force_path("umma", request.param)
     return request.param
 
 
@@ -234,11 +258,10 @@ def test_i8_kernels_forced(oracle, umma_variant, m, n, k):
 
 
 @pytest.fixture(params=["single", "pair", "ts"])
-def w4a8_variant(request, monkeypatch):
+def w4a8_variant(request, force_path):
     """single: weights expanded in shared memory; pair / ts: weights expanded into tensor memory, on a
     CTA pair or on one CTA."""
-    monkeypatch.setenv("TQT_B200_PATH", "umma")
-    monkeypatch.setenv("TQT_B200_UMMA", request.param)
+    force_path("umma", request.param)
     return request.param
 
 

@@ -23,13 +23,17 @@ def test_w4a8_stores_replicas_of_a_column_shard(oracle, m):
     a = torch.from_numpy(rng.normal(0, 1, (m, k)).astype(np.float32)).to(DEV).to(torch.bfloat16)
     want = layer(a).clone()
     bufs = [torch.full((m, n_total), 5.0, dtype=torch.bfloat16, device=DEV) for _ in range(3)]
-    pkg.set_output_replicas(bufs[0].data_ptr(), [b.data_ptr() for b in bufs[1:]])
-    try:
+    nbytes = bufs[0].numel() * 2
+    with pkg.output_replicas(bufs[0].data_ptr(), nbytes, [b.data_ptr() for b in bufs[1:]]):
         layer.quantize(a)
         layer.gemm(m, out=bufs[0][:, n0:n0 + n])
         sync_and_check()
-    finally:
-        pkg.set_output_replicas(0, [])
+        # an output that is not inside the registered buffer is refused and nothing is launched
+        stray = torch.full((m, n), 3.0, dtype=torch.bfloat16, device=DEV)
+        with pytest.raises(pkg.TqtError):
+            layer.gemm(m, out=stray)
+        sync_and_check()
+        assert torch.all(stray == 3.0)
     for b in bufs:
         assert torch.equal(b[:, n0:n0 + n].view(torch.int16), want.view(torch.int16))
         assert torch.all(b[:, :n0] == 5.0) and torch.all(b[:, n0 + n:] == 5.0)
@@ -42,11 +46,8 @@ def test_other_paths_refuse_replicas():
     b = torch.zeros((16, 8), dtype=torch.int8, device=DEV)
     d = torch.zeros((8, 8), dtype=torch.int32, device=DEV)
     other = torch.zeros((8, 8), dtype=torch.int32, device=DEV)
-    pkg.set_output_replicas(d.data_ptr(), [other.data_ptr()])
-    try:
+    with pkg.output_replicas(d.data_ptr(), d.numel() * 4, [other.data_ptr()]):
         with pytest.raises(pkg.TqtError):
             uk.run_gemm(8, 8, 16, a, 16, 0, b, 8, 0, None, 8, d, 8, -2**31, 2**31 - 1)
-    finally:
-        pkg.set_output_replicas(0, [])
     uk.run_gemm(8, 8, 16, a, 16, 0, b, 8, 0, None, 8, d, 8, -2**31, 2**31 - 1)
     sync_and_check()

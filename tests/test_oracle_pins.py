@@ -275,6 +275,21 @@ def test_requant_tail_semantics(oracle):
     assert np.array_equal(D1, oracle.gemm_reqi32toi8(A, Bt, True, 0.05, sb0, 3.0, -5, bias))
 
 
+@pytest.mark.parametrize("m,n,k", [(32, 32, 32), (3, 8, 11), (5, 11, 10), (9, 19, 23), (15, 32, 25), (60, 63, 127)])
+def test_requant_restatement_passes_the_reference_acceptance_test(oracle, m, n, k):
+    """The integer tail of the requantising kernels exists only as RVV instructions in the reference, so its
+    restatement cannot be pinned bit for bit ("parity unpinned" for the int8 bit pattern).  What the reference's
+    own suite checks of these kernels is checked here of the restatement: same inputs, same criterion, on the
+    suite's shape list (test_gemm_i8_i8_rvv.cpp:31-41)."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from tqt_testlib import requant_acceptance_case, requant_acceptance_check
+    c = requant_acceptance_case(oracle, m, n, k)
+    D = oracle.gemm_reqi32toi8(c["A"], c["B"], True, c["scale_a"], c["scale_b"], c["scale_d"], c["zp_d"], c["bias_fused"])
+    requant_acceptance_check(D, c)
+
+
 def test_live_reference_when_built(oracle):
     ref = Reference()
     if not ref.available():

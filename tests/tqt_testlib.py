@@ -182,6 +182,49 @@ def run_w4a16(td, A_bits, nib, scale_bits, bl, Cm=None, bias=None, clamp=None):
     return d.cpu().numpy() if td == "f32" else bits16(d)
 
 
+def requant_acceptance_case(oracle, m, n, k):
+    """Inputs of the reference's own test of the 1xN-bias requantising GEMM (run_1xnbias_reqi32toi8_gemm_test,
+    test/common/quantized_gemm_test_runner.h:193-306): real-valued A, B ~ U(-1,1) from one mt19937(42) stream,
+    bias ~ U(-10,10) seed 123; A quantised asymmetrically per tensor, B symmetrically per channel, bias to int32 at
+    scale_a * scale_b[n] with the activation zero point fused in; the output scale / zero point from the range of
+    the real-valued result.  Returns the quantised operands, the params and that real-valued result (no GPU)."""
+    f32 = np.float32
+    AB = oracle.fill_uniform((m * k + n * k,), np.float32, -1.0, 1.0, 42)
+    A, B = AB[:m * k].reshape(m, k), AB[m * k:].reshape(n, k)
+    bias = oracle.fill_uniform((n,), np.float32, -10.0, 10.0, 123)
+
+    def asym(x):   # compute_asym_quant_params_i8 (:37-65)
+        fmin, fmax = f32(min(x.min(), 0.0)), f32(max(x.max(), 0.0))
+        sc = f32(f32(fmax - fmin) / f32(255.0))
+        if sc == 0:
+            return f32(1.0), 0
+        zp = int(np.rint(f32(-128.0) - f32(fmin / sc)))
+        return sc, (-127 if zp == -128 else zp)
+
+    def quant(x, sc, zp):   # quantize_i8 (test_common.h:232-240)
+        return np.clip(np.rint((x / f32(sc)).astype(f32)) + f32(zp), -128, 127).astype(np.int8)
+
+    sa, zpa = asym(A)
+    absmax = np.abs(B).max(axis=1).astype(f32)
+    sb = (f32(2.0) * absmax / f32(255.0)).astype(f32)   # compute_sym_quant_params_i8 (:69-86)
+    sb[sb == 0] = 1.0
+    Aq = quant(A, sa, zpa)
+    Bq = np.stack([quant(B[j], sb[j], 0) for j in range(n)])
+    bias_i32 = np.clip(np.rint((bias / (f32(sa) * sb)).astype(f32)), -2147483648.0, 2147483647.0).astype(np.int64).astype(np.int32)
+    fused = oracle.fuse_zp_to_bias(bias_i32, Bq, zpa)
+    real = (A.astype(np.float64) @ B.T.astype(np.float64) + bias.astype(np.float64)[None, :]).astype(f32)
+    sd, zpd = asym(real)
+    return dict(A=Aq, B=Bq, scale_a=float(sa), zp_a=zpa, scale_b=sb, bias_fused=fused, scale_d=float(sd), zp_d=zpd, real=real)
+
+
+def requant_acceptance_check(D_i8, case):
+    """The reference's pass criterion: dequantised output against the real-valued GEMM, max abs error 1.0 and
+    cosine similarity 0.999 (quantized_gemm_test_runner.h:294-302)."""
+    deq = (D_i8.astype(np.float32) - np.float32(case["zp_d"])) * np.float32(case["scale_d"])
+    assert np.max(np.abs(deq - case["real"])) <= 1.0
+    assert cosine(deq, case["real"]) >= 0.999
+
+
 def rel_err(got, want):
     """max |got - want| / max(|want|, rms(want)): relative error with an RMS floor against 0/0."""
     got = got.astype(np.float64)

@@ -106,16 +106,50 @@ def use_current_torch_stream() -> None:
     set_stream(torch.cuda.current_stream())
 
 
-def set_output_replicas(local_base: int, replica_bases) -> None:
+def set_output_replicas(local_base: int, local_bytes: int, replica_bases) -> None:
     """Also store the output of the following run_gemm calls at the same offsets inside the buffers that
-    start at ``replica_bases`` (device addresses, e.g. peer-mapped copies); an empty list switches it off."""
+    start at ``replica_bases`` (device addresses, e.g. peer-mapped copies, each at least ``local_bytes``
+    long); the output of every such call must lie inside [local_base, local_base + local_bytes).  An empty
+    list switches it off."""
     n = len(replica_bases)
     arr = (C.c_void_p * max(n, 1))(*[C.c_void_p(int(b)) for b in replica_bases])
     f = lib().tqt_cuda_set_output_replicas
-    f.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_size_t]
+    f.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_size_t]
     f.restype = None
-    f(C.c_void_p(int(local_base)) if n else None, arr if n else None, n)
+    f(C.c_void_p(int(local_base)) if n else None, int(local_bytes) if n else 0, arr if n else None, n)
     check("set_output_replicas")
+
+
+class output_replicas:
+    """Context manager around set_output_replicas: the setting is cleared on the way out, also when the body raises."""
+
+    def __init__(self, local_base: int, local_bytes: int, replica_bases):
+        self.args = (local_base, local_bytes, list(replica_bases))
+
+    def __enter__(self):
+        set_output_replicas(*self.args)
+        return self
+
+    def __exit__(self, *exc):
+        set_output_replicas(0, 0, [])
+        return False
+
+
+def debug_inject_wait_failure(wait_shift: int = 0, flags: int = 0) -> None:
+    """Test knob of the bounded waits (tqt_cuda_debug_inject_wait_failure); (0, 0) = normal operation."""
+    f = lib().tqt_cuda_debug_inject_wait_failure
+    f.argtypes = [C.c_uint, C.c_uint]
+    f.restype = None
+    f(int(wait_shift), int(flags))
+
+
+def debug_set_path(path=None, umma=None) -> None:
+    """Force a kernel path ("auto", "umma", "gemv", "simt") and a tensor-core kernel ("single", "pair", "ts")
+    for all later run_gemm calls of the process; None = automatic choice."""
+    f = lib().tqt_cuda_debug_set_path
+    f.argtypes = [C.c_char_p, C.c_char_p]
+    f.restype = None
+    f(None if path is None else path.encode(), None if umma is None else umma.encode())
 
 
 def read_device_fault() -> int:
@@ -459,7 +493,7 @@ EXTENSION_SYMBOLS = (
     ["tqt_cuda_set_stream", "tqt_cuda_get_stream", "tqt_cuda_get_last_status", "tqt_cuda_get_last_cuda_error",
      "tqt_cuda_read_device_fault", "tqt_cuda_version", "tqt_shard_plan_n", "tqt_cuda_kernel_choice_w4a8",
      "tqt_cuda_debug_f16_bits", "tqt_cuda_debug_bf16_bits", "tqt_cuda_debug_set_timing_buffer",
-     "tqt_cuda_debug_stream_read", "tqt_cuda_set_output_replicas"]
+     "tqt_cuda_debug_stream_read", "tqt_cuda_set_output_replicas", "tqt_cuda_debug_set_path", "tqt_cuda_debug_inject_wait_failure"]
     + [f"tqt_run_quant_pack_qai8dxp_{t}_{VARIANT}" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_quant_qai8dx_{t}_sm100a" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_{n}_{VARIANT}" for n in ("a_unpack_i8", "a_unpack_f16", "bt_unpack_qsi4cxp", "bt_unpack_qsi4c2p")]

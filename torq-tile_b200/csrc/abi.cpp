@@ -18,6 +18,7 @@ thread_local int t_status = TQT_CUDA_OK;
 thread_local int t_cuda_error = 0;
 thread_local size_t t_n_replicas = 0;
 thread_local const char *t_replica_local = nullptr;
+thread_local size_t t_replica_bytes = 0;
 thread_local long long t_replica_delta[7] = {0, 0, 0, 0, 0, 0, 0};
 
 inline void set_result(Result r)
@@ -61,6 +62,18 @@ inline bool ptrs_ok(size_t m, size_t n, const void *A, const void *B, const void
     return m == 0 || n == 0 || (A && B && D);
 }
 
+// While output replicas are set, every element the call stores, [D, D + ((m-1)*ldd + n) * elem), must lie inside
+// the registered local buffer: the replica stores go to the same offsets of buffers on other GPUs, so an output
+// outside the registered range would be written at arbitrary peer addresses.
+inline bool replicas_cover(size_t m, size_t n, const void *D, size_t ldd, size_t elem)
+{
+    if (t_n_replicas == 0 || m == 0 || n == 0) return true;
+    const char *d0 = static_cast<const char *>(D);
+    const size_t span = ((m - 1) * ldd + n) * elem;
+    return d0 >= t_replica_local && span <= t_replica_bytes &&
+           (size_t)(d0 - t_replica_local) <= t_replica_bytes - span;
+}
+
 void run_pack_a_i8(size_t m, size_t k, size_t lda, size_t lda_packed, size_t k_idx, const void *A, void *A_packed)
 {
     if ((m && k && (!A || !A_packed)) || k_idx % K_STEP) return set_invalid();
@@ -83,15 +96,21 @@ void run_pack_bt_i4(size_t n, size_t k, size_t ldb, size_t ldb_packed, size_t k_
     set_result(launch_pack_i4(t_stream, n, k, ldb / 2, ldb_packed, B, B_packed, c2));
 }
 
-void run_w4a8(size_t m, size_t n, size_t k, const void *A_packed, const void *B_packed, const void *C, size_t ldc,
-              void *D, size_t ldd, const void *bias, float cmin, float cmax,
+void run_w4a8(size_t m, size_t n, size_t k, const void *A_packed, size_t lda, const void *B_packed, size_t ldb,
+              const void *C, size_t ldc, void *D, size_t ldd, const void *bias, float cmin, float cmax,
               const struct tqt_qai8dx_qsi4cx_params *params, Dtype td)
 {
     if (!params) return set_ok();  // the reference returns silently
     if (!ptrs_ok(m, n, A_packed, B_packed, D) || (k & 1)) return set_invalid();
     if (m && n && (!params->scale_a || !params->zero_point_a || !params->scale_b)) return set_invalid();
-    // Packed A / B are addressed with the call's k, not lda / ldb, as the reference does.
-    GemmCommon g = common(m, n, k, A_packed, k, B_packed, k, C, ldc, D, ldd, bias);
+    // The reference strides the packed operands by the call's k and ignores lda / ldb, which is the same
+    // thing whenever lda == ldb == k, the only way its callers use this kernel type.  Here a larger lda / ldb
+    // names the K extent the packed buffers were built for, so that a K-slab call (k < lda, operands offset
+    // with get_*_packed_offset(idx, k_idx, ld, ...)) finds its blocks; smaller values fall back to k.
+    if (lda < k) lda = k;
+    if (ldb < k) ldb = k;
+    if (!replicas_cover(m, n, D, ldd, td == Dtype::F32 ? 4 : 2)) return set_invalid();
+    GemmCommon g = common(m, n, k, A_packed, lda, B_packed, ldb, C, ldc, D, ldd, bias);
     W4A8Params p{params->scale_a, params->zero_point_a, params->scale_b};
     set_result(launch_gemm_w4a8(g, p, td, cmin, cmax, env_path()));
 }
@@ -102,6 +121,7 @@ void run_w4a16(size_t m, size_t n, size_t k, size_t bl, const void *A_packed, si
 {
     if (!ptrs_ok(m, n, A_packed, B_packed, D)) return set_invalid();
     if (bl < 2 || (bl & 1) || (k % bl) || (m && n && k && !scale_b)) return set_invalid();
+    if (!replicas_cover(m, n, D, ldd, td == Dtype::F32 ? 4 : 2)) return set_invalid();
     GemmCommon g = common(m, n, k, A_packed, lda, B_packed, ldb, C, ldc, D, ldd, bias);
     set_result(launch_gemm_w4a16(g, bl, scale_b, ldsb, td, cmin, cmax, env_path()));
 }
@@ -295,9 +315,9 @@ void tqt_run_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8p_qsi8cxp_128x128_sm100a(
         size_t ldb, size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias,                  \
         TDTYPE clamp_min, TDTYPE clamp_max, const struct tqt_qai8dx_qsi4cx_params *params)                             \
     {                                                                                                                  \
-        (void)lda; (void)ldb; (void)k_idx_a; (void)k_idx_b;                                                            \
-        run_w4a8(m, n, k, A_packed, B_packed, C, ldc, D, ldd, bias, (float)clamp_min, (float)clamp_max, params,        \
-                 TDENUM);                                                                                              \
+        (void)k_idx_a; (void)k_idx_b;                                                                                  \
+        run_w4a8(m, n, k, A_packed, lda, B_packed, ldb, C, ldc, D, ldd, bias, (float)clamp_min, (float)clamp_max,      \
+                 params, TDENUM);                                                                                      \
     }
 
 TQT_DEFINE_W4A8_PACKED(f32, float, Dtype::F32, sizeof(float))
@@ -458,13 +478,20 @@ uint16_t tqt_cuda_debug_bf16_bits(bfloat16_t v)
 
 void tqt_cuda_debug_set_timing_buffer(void *dev_ptr) { set_timing_buffer(dev_ptr); }
 
+void tqt_cuda_debug_set_path(const char *path, const char *umma) { set_path_switches(path, umma); }
+
+void tqt_cuda_debug_inject_wait_failure(unsigned wait_shift, unsigned flags) { set_failure_injection(wait_shift, flags); }
+
 void tqt_cuda_debug_stream_read(const void *src, size_t bytes, void *sink) { set_result(stream_read(src, bytes, sink, t_stream)); }
 
-void tqt_cuda_set_output_replicas(const void *local_base, void *const *replica_bases, size_t count)
+void tqt_cuda_set_output_replicas(const void *local_base, size_t local_bytes, void *const *replica_bases, size_t count)
 {
-    if (count > 7 || (count && (!local_base || !replica_bases))) return set_invalid();
+    if (count > 7 || (count && (!local_base || !replica_bases || local_bytes == 0))) return set_invalid();
+    for (size_t i = 0; i < count; ++i)
+        if (!replica_bases[i]) return set_invalid();
     t_n_replicas = count;
     t_replica_local = static_cast<const char *>(local_base);
+    t_replica_bytes = count ? local_bytes : 0;
     for (size_t i = 0; i < count; ++i)
         t_replica_delta[i] = (long long)(static_cast<const char *>(replica_bases[i]) - t_replica_local);
     set_ok();
@@ -476,7 +503,7 @@ int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k)
 {
     (void)n;
     if (k == 0) return 2;
-    return m <= 8 ? 1 : 0;
+    return m <= 16 ? 1 : 0;
 }
 
 }  // extern "C"

@@ -1,4 +1,4 @@
-// HBM-streaming W4A8 GEMV for decode (m <= 8; more rows run on the tensor-core kernel): no tensor
+// HBM-streaming W4A8 GEMV for decode (m <= 16; more rows run on the tensor-core kernel): no tensor
 // cores, no clusters, no shared-memory staging of weights, no scratch memory.
 //
 // A CTA owns 8 consecutive output columns (8 rows of one 128-row block tile of B_packed) and loops
@@ -36,10 +36,11 @@ int sm_count_cached();
 
 constexpr uint32_t kGemvThreads = 256;
 constexpr uint32_t kGemvWarpRows = 8;   // output columns per warp
+constexpr uint32_t kGemvMaxRows = 16;  // activation rows the GEMV takes (decode batch)
 
 struct GemvArgs {
     uint32_t m, n, k;
-    const uint8_t *A;  // packed int8 blocks (row-tile 0 only: m <= 8)
+    const uint8_t *A;  // packed int8 blocks (row-tile 0 only: m <= 16)
     const uint8_t *B;  // packed qsi4cx blocks
     uint32_t b_kblocks_total;
     const void *C;
@@ -67,14 +68,20 @@ __device__ __forceinline__ uint4 ldg_stream(const void *p)
 constexpr uint32_t kGemvSlices = kGemvThreads / 32;   // warps of a CTA = interleaved K slices
 constexpr uint32_t kGemvChunk = 4;                   // loads in flight per thread
 
-template <int MR>
-constexpr int gemv_min_ctas() { return MR <= 2 ? 4 : 3; }
+// G = 8-column groups a CTA works on at the same time.  With G = 1 a launch of N / 8 CTAs fills up to four
+// CTA slots per SM; a decode-sized launch (N = 4096: 512 CTAs on 592 slots) then leaves its successor nowhere
+// to become resident, so the successor's weight loads start only when this kernel's CTAs exit and the memory
+// phases of back-to-back GEMVs do not overlap.  With G = 2 a CTA streams 16 columns (eight 128-bit loads in
+// flight per thread, the activation words shared by both groups), the launch takes two slots per SM, and the
+// next GEMV of the chain is resident and has its weights in flight while this one runs its post-wait tail.
+template <int MR, int G>
+constexpr int gemv_min_ctas() { return G == 2 ? 2 : (MR <= 2 ? 4 : (MR <= 8 ? 3 : 2)); }
 
-template <int MR, Dtype TD>
-__global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR>()) gemv_w4a8_kernel(const GemvArgs args)
+template <int MR, int G, Dtype TD>
+__global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a8_kernel(const GemvArgs args)
 {
     constexpr uint32_t S = kGemvSlices, CH = kGemvChunk;
-    __shared__ int32_t sRed[(S - 1) * kGemvWarpRows * (MR + 1)];
+    __shared__ int32_t sRed[(S - 1) * G * kGemvWarpRows * (MR + 1)];
     const uint32_t tid = threadIdx.x, ks = tid >> 5, lane = tid & 31u;
     const uint32_t rr = lane >> 2;                                 // row inside the group
     const uint32_t pos = lane & 3u;                                // physical 16-byte segment
@@ -82,42 +89,56 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR>()) gemv_w4a8_k
     const uint32_t KB = (args.k + 127) / 128;
     const uint32_t T = KB > ks ? (KB - ks + S - 1) / S : 0;        // K blocks of this warp: ks, ks+S, ...
     const uint32_t groups = (args.n + kGemvWarpRows - 1) / kGemvWarpRows;
+    const uint32_t sgroups = (groups + G - 1) / G;                 // sets of G groups: the unit a CTA takes
 
     if (args.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     constexpr size_t kWStep = (size_t)S * kI4CxBlockBytes;
-    const uint8_t *wp, *rp;   // this thread's weight segment / int16 partial row sum in its first K block
-    auto set_group = [&](uint32_t grp) {
-        const uint32_t row0 = grp * kGemvWarpRows, tile = row0 >> 7, r_blk = (row0 & 127u) + rr;
-        const uint8_t *blk = args.B + ((size_t)tile * args.b_kblocks_total + ks) * kI4CxBlockBytes;
-        wp = blk + r_blk * 64u + pos * 16u;
-        rp = blk + kI4NibBytes + r_blk * 2u;   // tail of every packed block: the zero-point correction terms
-    };
-    uint4 w[CH];
-    int32_t rsv[CH];
-    auto load_one = [&](uint32_t i, uint32_t t) {   // K block number t of this warp into slot i
-        const bool ok = t < T;
-        w[i] = ok ? ldg_stream(wp + (size_t)t * kWStep) : make_uint4(0, 0, 0, 0);
-        rsv[i] = (ok && pos == 0) ? (int32_t)__ldg(reinterpret_cast<const int16_t *>(rp + (size_t)t * kWStep)) : 0;
-    };
-    auto load_chunk = [&](uint32_t t0) {
+    const uint8_t *wp[G], *rp[G];   // this thread's weight segment / int16 partial row sum in its first K block
+    bool gok[G];                    // the group exists (the last set of a launch may be short)
+    auto set_group = [&](uint32_t sg) {
 #pragma unroll
-        for (uint32_t i = 0; i < CH; ++i) load_one(i, t0 + i);
-    };
-    uint32_t grp = blockIdx.x;
-    set_group(grp);
-    load_chunk(0);
-    // per-column constants of the first group: static like the weights, so fetched before the wait
-    const bool finisher = ks == 0 && pos == 0;
-    float sb = 0.0f, bv = 0.0f;
-    auto load_column_constants = [&](uint32_t g) {
-        const uint32_t n = g * kGemvWarpRows + rr;
-        if (finisher && n < args.n) {
-            sb = args.scale_b[n];
-            bv = args.bias ? TdTraits<TD>::load(args.bias, n) : 0.0f;
+        for (int gi = 0; gi < G; ++gi) {
+            const uint32_t grp = sg * G + gi;
+            gok[gi] = grp < groups;
+            const uint32_t row0 = (gok[gi] ? grp : 0u) * kGemvWarpRows, tile = row0 >> 7, r_blk = (row0 & 127u) + rr;
+            const uint8_t *blk = args.B + ((size_t)tile * args.b_kblocks_total + ks) * kI4CxBlockBytes;
+            wp[gi] = blk + r_blk * 64u + pos * 16u;
+            rp[gi] = blk + kI4NibBytes + r_blk * 2u;   // tail of every packed block: the zero-point correction terms
         }
     };
-    load_column_constants(grp);
+    uint4 w[G][CH];
+    int32_t rsv[G][CH];
+    auto load_chunk = [&](uint32_t t0) {   // K blocks t0 .. t0 + CH - 1 of this warp
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) {
+                const bool ok = gok[gi] && t0 + i < T;
+                w[gi][i] = ok ? ldg_stream(wp[gi] + (size_t)(t0 + i) * kWStep) : make_uint4(0, 0, 0, 0);
+                rsv[gi][i] = (ok && pos == 0) ? (int32_t)__ldg(reinterpret_cast<const int16_t *>(rp[gi] + (size_t)(t0 + i) * kWStep)) : 0;
+            }
+        }
+    };
+    uint32_t sg = blockIdx.x;
+    set_group(sg);
+    load_chunk(0);
+    // per-column constants of the first set: static like the weights, so fetched before the wait
+    const bool finisher = ks == 0 && pos == 0;
+    float sb[G], bv[G];
+    auto load_column_constants = [&](uint32_t sg_) {
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            const uint32_t n = (sg_ * G + gi) * kGemvWarpRows + rr;
+            sb[gi] = 0.0f;
+            bv[gi] = 0.0f;
+            if (finisher && n < args.n) {
+                sb[gi] = args.scale_b[n];
+                bv[gi] = args.bias ? TdTraits<TD>::load(args.bias, n) : 0.0f;
+            }
+        }
+    };
+    load_column_constants(sg);
     // everything else may have been produced by the preceding kernel
     if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
 
@@ -135,10 +156,14 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR>()) gemv_w4a8_k
     constexpr size_t kAStep = (size_t)S * kI8BlockBytes;
 
     while (true) {
-        int32_t acc[MR];
+        int32_t acc[G][MR];
+        int32_t rsum[G];   // sum of q over this row's K blocks of this warp (lanes with pos == 0)
 #pragma unroll
-        for (int i = 0; i < MR; ++i) acc[i] = 0;
-        int32_t rsum = 0;   // sum of q over this row's K blocks of this warp (lanes with pos == 0)
+        for (int gi = 0; gi < G; ++gi) {
+            rsum[gi] = 0;
+#pragma unroll
+            for (int i = 0; i < MR; ++i) acc[gi][i] = 0;
+        }
 
         for (uint32_t t0 = 0; t0 < T; t0 += CH) {
 #pragma unroll
@@ -157,72 +182,90 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR>()) gemv_w4a8_k
                     }
 #pragma unroll
                     for (uint32_t i = 0; i < CH; ++i) {
-                        const uint32_t ws[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
                         const uint32_t al[4] = {av[i][0].x, av[i][0].y, av[i][0].z, av[i][0].w};
                         const uint32_t ah[4] = {av[i][1].x, av[i][1].y, av[i][1].z, av[i][1].w};
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint32_t lo = (ws[j] << 4) & 0xF0F0F0F0u;   // 16*q for k = 32*seg + 4j .. +3
-                            const uint32_t hi = ws[j] & 0xF0F0F0F0u;          // 16*q for k = 32*seg + 16 + 4j .. +3
-                            acc[mi] = __dp4a((int)al[j], (int)lo, acc[mi]);
-                            acc[mi] = __dp4a((int)ah[j], (int)hi, acc[mi]);
+                        for (int gi = 0; gi < G; ++gi) {
+                            const uint32_t ws[4] = {w[gi][i].x, w[gi][i].y, w[gi][i].z, w[gi][i].w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t lo = (ws[j] << 4) & 0xF0F0F0F0u;   // 16*q for k = 32*seg + 4j .. +3
+                                const uint32_t hi = ws[j] & 0xF0F0F0F0u;          // 16*q for k = 32*seg + 16 + 4j .. +3
+                                acc[gi][mi] = __dp4a((int)al[j], (int)lo, acc[gi][mi]);
+                                acc[gi][mi] = __dp4a((int)ah[j], (int)hi, acc[gi][mi]);
+                            }
                         }
                     }
                 }
             }
 #pragma unroll
-            for (uint32_t i = 0; i < CH; ++i) rsum += rsv[i];   // slots past T hold 0
+            for (int gi = 0; gi < G; ++gi) {
+#pragma unroll
+                for (uint32_t i = 0; i < CH; ++i) rsum[gi] += rsv[gi][i];   // slots past T hold 0
+            }
             if (t0 + CH < T) load_chunk(t0 + CH);
         }
 
-        // request the next group's first chunk before combining this one: the registers are free
-        const uint32_t n = grp * kGemvWarpRows + rr;
-        const uint32_t next = grp + gridDim.x;
-        if (next < groups) {
+        // request the next set's first chunk before combining this one: the registers are free
+        const uint32_t cur = sg;
+        const uint32_t next = sg + gridDim.x;
+        if (next < sgroups) {
             set_group(next);
             load_chunk(0);
         }
 
         // combine the four segments of each row (lanes that differ in their low two bits) ...
 #pragma unroll
-        for (int mi = 0; mi < MR; ++mi) {
-            int32_t v = acc[mi];
-            v += __shfl_xor_sync(0xffffffffu, v, 1);
-            v += __shfl_xor_sync(0xffffffffu, v, 2);
-            acc[mi] = v;
+        for (int gi = 0; gi < G; ++gi) {
+#pragma unroll
+            for (int mi = 0; mi < MR; ++mi) {
+                int32_t v = acc[gi][mi];
+                v += __shfl_xor_sync(0xffffffffu, v, 1);
+                v += __shfl_xor_sync(0xffffffffu, v, 2);
+                acc[gi][mi] = v;
+            }
         }
         // ... and the eight warps through shared memory
         if (ks > 0 && pos == 0) {
-            int32_t *dst = sRed + ((ks - 1) * kGemvWarpRows + rr) * (MR + 1);
 #pragma unroll
-            for (int mi = 0; mi < MR; ++mi) dst[mi] = acc[mi];
-            dst[MR] = rsum;
+            for (int gi = 0; gi < G; ++gi) {
+                int32_t *dst = sRed + (((ks - 1) * G + gi) * kGemvWarpRows + rr) * (MR + 1);
+#pragma unroll
+                for (int mi = 0; mi < MR; ++mi) dst[mi] = acc[gi][mi];
+                dst[MR] = rsum[gi];
+            }
         }
         __syncthreads();
 
-        if (ks == 0 && pos == 0 && n < args.n) {
+        if (finisher) {
 #pragma unroll
-            for (uint32_t s2 = 1; s2 < S; ++s2) {
-                const int32_t *src = sRed + ((s2 - 1) * kGemvWarpRows + rr) * (MR + 1);
+            for (int gi = 0; gi < G; ++gi) {
+                const uint32_t n = (cur * G + gi) * kGemvWarpRows + rr;
+                if (n < args.n) {
 #pragma unroll
-                for (int mi = 0; mi < MR; ++mi) acc[mi] += src[mi];
-                rsum += src[MR];
-            }
+                    for (uint32_t s2 = 1; s2 < S; ++s2) {
+                        const int32_t *src = sRed + (((s2 - 1) * G + gi) * kGemvWarpRows + rr) * (MR + 1);
 #pragma unroll
-            for (int mi = 0; mi < MR; ++mi) {
-                if ((uint32_t)mi < args.m) {
-                    int32_t a = acc[mi] >> 4;   // operands were 16*q
-                    a -= zp[mi] * rsum;
-                    const float cv = args.C ? TdTraits<TD>::load(args.C, (size_t)mi * args.ldc + n) : 0.0f;
-                    const float v = w4a8_epilogue(a, sa[mi], sb, args.C != nullptr, cv, args.bias != nullptr, bv,
-                                                  args.cmin, args.cmax);
-                    TdTraits<TD>::store(args.D, (size_t)mi * args.ldd + n, v);
+                        for (int mi = 0; mi < MR; ++mi) acc[gi][mi] += src[mi];
+                        rsum[gi] += src[MR];
+                    }
+#pragma unroll
+                    for (int mi = 0; mi < MR; ++mi) {
+                        if ((uint32_t)mi < args.m) {
+                            int32_t a = acc[gi][mi] >> 4;   // operands were 16*q
+                            a -= zp[mi] * rsum[gi];
+                            const float cv = args.C ? TdTraits<TD>::load(args.C, (size_t)mi * args.ldc + n) : 0.0f;
+                            const float v = w4a8_epilogue(a, sa[mi], sb[gi], args.C != nullptr, cv, args.bias != nullptr, bv[gi],
+                                                          args.cmin, args.cmax);
+                            TdTraits<TD>::store(args.D, (size_t)mi * args.ldd + n, v);
+                        }
+                    }
                 }
             }
         }
-        if (next >= groups) break;
-        grp = next;
-        load_column_constants(grp);
+        if (next >= sgroups) break;
+        sg = next;
+        load_column_constants(sg);
         __syncthreads();   // the partial sums in shared memory have been read
     }
 }
@@ -237,15 +280,27 @@ bool pdl_enabled()
     return cached != 0;
 }
 
-template <int MR, Dtype TD>
+// TQT_B200_GEMV_G=1|2 forces the number of column groups per CTA (read once); by default two for launches
+// that fit the GPU in one round at two CTAs per SM (decode-sized N), one otherwise.
+static int gemv_forced_groups()
+{
+    static const int cached = [] {
+        const char *e = std::getenv("TQT_B200_GEMV_G");
+        return e ? std::atoi(e) : 0;
+    }();
+    return cached;
+}
+
+template <int MR, int G, Dtype TD>
 static Result launch_gemv_t(GemvArgs a, cudaStream_t st)
 {
     a.pdl = pdl_enabled() ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
-    // CTA c owns the 8-column groups c, c + grid, ...: one group each while they all fit on the GPU at once
+    // CTA c owns the sets of G 8-column groups c, c + grid, ...: one set each while they all fit on the GPU at once
     const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
-    const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_min_ctas<MR>();
-    cfg.gridDim = dim3(groups < resident ? groups : resident, 1, 1);
+    const uint32_t sgroups = (groups + G - 1) / G;
+    const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_min_ctas<MR, G>();
+    cfg.gridDim = dim3(sgroups < resident ? sgroups : resident, 1, 1);
     cfg.blockDim = dim3(kGemvThreads, 1, 1);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
@@ -254,24 +309,37 @@ static Result launch_gemv_t(GemvArgs a, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a8_kernel<MR, TD>, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a8_kernel<MR, G, TD>, a);
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
     return Result{kOk, 0};
+}
+
+template <int MR, Dtype TD>
+static Result launch_gemv_g(const GemvArgs &a, cudaStream_t st)
+{
+    if constexpr (MR <= 8) {
+        const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
+        const int forced = gemv_forced_groups();
+        const bool two = forced ? forced == 2 : (groups + 1) / 2 <= (uint32_t)sm_count_cached() * 2u;
+        if (two) return launch_gemv_t<MR, 2, TD>(a, st);
+    }
+    return launch_gemv_t<MR, 1, TD>(a, st);
 }
 
 template <Dtype TD>
 static Result launch_gemv_m(const GemvArgs &a, cudaStream_t st)
 {
-    if (a.m <= 1) return launch_gemv_t<1, TD>(a, st);
-    if (a.m <= 2) return launch_gemv_t<2, TD>(a, st);
-    if (a.m <= 4) return launch_gemv_t<4, TD>(a, st);
-    return launch_gemv_t<8, TD>(a, st);
+    if (a.m <= 1) return launch_gemv_g<1, TD>(a, st);
+    if (a.m <= 2) return launch_gemv_g<2, TD>(a, st);
+    if (a.m <= 4) return launch_gemv_g<4, TD>(a, st);
+    if (a.m <= 8) return launch_gemv_g<8, TD>(a, st);
+    return launch_gemv_g<16, TD>(a, st);
 }
 
 Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
 {
     if (g.m == 0 || g.n == 0) return Result{kOk, 0};
-    if (g.m > 8 || g.k == 0 || g.k > 65536 || g.n > 0x3fffff00ull) return Result{kUnsupported, 0};
+    if (g.m > kGemvMaxRows || g.k == 0 || g.k > 65536 || g.n > 0x3fffff00ull) return Result{kUnsupported, 0};
     if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15)) return Result{kUnsupported, 0};
     GemvArgs a{};
     a.m = (uint32_t)g.m;

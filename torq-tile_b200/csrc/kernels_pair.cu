@@ -85,7 +85,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
             ptx::mbar_init(BAR(kTmemFull + e), 1);
             ptx::mbar_init(BAR(kTmemEmpty + e), 16);   // 8 epilogue warps of each CTA
         }
-        *sAbort = 0;
+        sAbort[0] = 0;
+        sAbort[1] = (int)args.wait_shift;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -144,7 +145,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                 const uint32_t s = j % S, ph = (j / S) & 1u;
                 const long long t0 = clock64();
                 while (!ptx::mbar_try_wait(BAR(kFull + s), ph)) {
-                    if (clock64() - t0 > ptx::kWaitLimitCycles) {
+                    if (clock64() - t0 > ptx::wait_limit(sAbort)) {
                         if (args.fault) atomicCAS(args.fault, 0u, (unsigned)kFaultDrainWait);
                         break;
                     }
@@ -447,7 +448,8 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             ptx::mbar_init(BAR(kRsumFull + e), 8);   // 8 converter warps
             ptx::mbar_init(BAR(kRsumEmpty + e), 8);
         }
-        *sAbort = 0;
+        sAbort[0] = 0;
+        sAbort[1] = (int)args.wait_shift;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -479,6 +481,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
         // SM), so the two K steps of a group are issued by two warps: warp 0 step 0, warp 18 step 1.
         const uint32_t ph = warp == 0 ? 0u : 1u;
         uint32_t Gc = 0;   // groups issued so far
+        uint32_t withheld = 0xffffffffu;   // group whose stage this warp left without copies and arrive (test knob)
         bool ok = true;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs) {
             uint32_t tm, tn;
@@ -511,6 +514,10 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                         __syncwarp();
                         continue;
                     }
+                    if ((args.inject & 1u) && Gc == 0 && ph == 0) {   // host-made failure: see UmmaArgs::inject
+                        withheld = 0;
+                        continue;
+                    }
                     // W4A8: every step brings its own 128-k block of nibbles; W4A16: the group's single block rides on step 0
                     const bool nib_now = nib_valid && (!kF16 || h == 0);
                     const uint32_t nib_bytes = kF16 ? 8192u : 8448u;
@@ -535,10 +542,20 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             }
         }
         if (!ok) {
-            // bail-out: give the copies already issued (a few KiB each) a bounded time to land before the
-            // CTA returns its shared memory
-            const long long t0 = clock64();
-            while (clock64() - t0 < 4000000ll) {
+            // bail-out: the copies this warp has issued must have landed before the CTA returns its shared
+            // memory.  Each of the last NG groups owns one stage of this warp: wait (bounded) for its barrier.
+            const uint32_t pending = Gc < NG ? Gc : NG;
+            for (uint32_t i = 0; i < pending; ++i) {
+                const uint32_t G = Gc - 1u - i;
+                if (G == withheld) continue;
+                const uint32_t s = (G % NG) * 2u + ph, phs = (G / NG) & 1u;
+                const long long t0 = clock64();
+                while (!ptx::mbar_try_wait(BAR(kFull + s), phs)) {
+                    if (clock64() - t0 > ptx::wait_limit(sAbort)) {
+                        if (args.fault) atomicCAS(args.fault, 0u, (unsigned)kFaultDrainWait);
+                        break;
+                    }
+                }
             }
         }
     } else if (warp == 1) {

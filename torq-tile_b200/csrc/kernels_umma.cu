@@ -22,6 +22,7 @@
 //
 // Every wait is bounded (ptx::mbar_wait); a wait that runs out records a code in the device fault
 // word, the CTA stops issuing work, drains its copies, frees tensor memory and returns.
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -42,9 +43,15 @@ namespace tqt {
         return _r;                                              \
     }())
 
-static long long *g_timing_buffer = nullptr;
-void set_timing_buffer(void *p) { g_timing_buffer = static_cast<long long *>(p); }
-long long *timing_buffer() { return g_timing_buffer; }
+static std::atomic<unsigned> g_wait_shift{0}, g_inject{0};
+void set_failure_injection(unsigned wait_shift, unsigned flags)
+{
+    g_wait_shift.store(wait_shift > 20 ? 20 : wait_shift);
+    g_inject.store(flags);
+}
+static std::atomic<long long *> g_timing_buffer{nullptr};
+void set_timing_buffer(void *p) { g_timing_buffer.store(static_cast<long long *>(p)); }
+long long *timing_buffer() { return g_timing_buffer.load(std::memory_order_relaxed); }
 
 template <BMode BM>
 struct ModeCfg;
@@ -127,7 +134,8 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             ptx::mbar_init(BAR(kTmemEmpty + e), 4);
             ptx::mbar_init(BAR(kRsumFull + e), 4);
         }
-        *sAbort = 0;
+        sAbort[0] = 0;
+        sAbort[1] = (int)args.wait_shift;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -184,7 +192,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                 const uint32_t s = j % S, ph = (j / S) & 1u;
                 const long long t0 = clock64();
                 while (!ptx::mbar_try_wait(BAR(kFull + s), ph)) {
-                    if (clock64() - t0 > ptx::kWaitLimitCycles) {
+                    if (clock64() - t0 > ptx::wait_limit(sAbort)) {
                         if (args.fault) atomicCAS(args.fault, 0u, (unsigned)kFaultDrainWait);
                         break;
                     }
@@ -570,7 +578,9 @@ static bool fill_common(UmmaArgs &a, const GemmCommon &g, size_t out_elem, size_
     a.n_replicas = (uint32_t)(g.n_replicas > 7 ? 7 : g.n_replicas);
     for (uint32_t i = 0; i < a.n_replicas; ++i) a.replica_delta[i] = g.replica_delta[i];
     a.fault = fault_word_device_ptr();
-    a.dbg = g_timing_buffer;
+    a.dbg = timing_buffer();
+    a.wait_shift = g_wait_shift.load(std::memory_order_relaxed);
+    a.inject = g_inject.load(std::memory_order_relaxed);
     // bulk copies need 16-byte aligned sources; block sizes are multiples of 16
     if ((reinterpret_cast<uintptr_t>(g.A) & 15) || (reinterpret_cast<uintptr_t>(g.B) & 15)) return false;
     return true;
@@ -582,15 +592,6 @@ Result ts_gemm_w4a16(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st);
 
 // TQT_B200_UMMA=single|pair forces one of the two tensor-core kernels (tests); default: CTA pairs
 // once the problem has more than one 128-row tile, the single-CTA kernel below that.
-static int umma_variant()
-{
-    const char *e = std::getenv("TQT_B200_UMMA");
-    if (!e) return 0;
-    if (!std::strcmp(e, "single")) return 1;
-    if (!std::strcmp(e, "pair")) return 2;
-    if (!std::strcmp(e, "ts")) return 3;
-    return 0;
-}
 static bool use_pair(uint32_t m, uint32_t min_m)
 {
     const int v = umma_variant();

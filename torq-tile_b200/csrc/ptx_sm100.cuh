@@ -66,7 +66,10 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 }
 // About one second at B200 clocks.  A wait that exceeds it records `code` in *fault, raises the
 // CTA-wide abort flag and returns false; every other wait in the CTA then returns false promptly.
+// The abort flag is a pair of ints in shared memory: [0] the flag, [1] a right shift applied to the limit
+// (0 in normal use; a test makes a wait run out in about a millisecond with 10).
 constexpr long long kWaitLimitCycles = 2000000000ll;
+__device__ __forceinline__ long long wait_limit(volatile int *abort_flag) { return kWaitLimitCycles >> (abort_flag[1] & 31); }
 
 // Bounded wait.  Every polling thread spins on try_wait (which itself suspends the thread for a
 // hardware-defined interval); sleeping between polls was measured to cost throughput, because the
@@ -82,7 +85,7 @@ __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, vo
         if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
         if ((++spins & 31u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > wait_limit(abort_flag)) {
                 *abort_flag = 1;
                 if (fault) atomicCAS(fault, 0u, code);
                 return false;

@@ -141,10 +141,20 @@ int read_device_fault(void *stream);
 // (nullptr switches it off).  Owned by the caller.
 void set_timing_buffer(void *dev_ptr);
 
+// Test knob of the tensor-core kernels' bounded waits: shift every wait limit right by wait_shift (10: about a
+// millisecond) and, with bit 0 of flags, make the first producer warp of the tensor-memory kernels withhold its
+// first stage, so that a wait runs out and the kernel returns with a fault code.  (0, 0) = normal operation.
+void set_failure_injection(unsigned wait_shift, unsigned flags);
+
 // Diagnostic: launch a kernel with the GEMV's launch shape that only reads `bytes` from src (16-byte aligned).
 Result stream_read(const void *src, size_t bytes, void *sink, void *stream);
 
-// Path override from the environment (TQT_B200_PATH = auto|umma|gemv|simt), for tests.
+// Path / tensor-core kernel overrides (tests): TQT_B200_PATH = auto|umma|gemv|simt and TQT_B200_UMMA =
+// single|pair|ts are read from the environment once; set_path_switches replaces both at run time (nullptr or an
+// unknown word = automatic choice).  umma_variant: 0 automatic, 1 single CTA, 2 CTA pair, 3 single-CTA
+// tensor-memory kernel.
 Path env_path();
+int umma_variant();
+void set_path_switches(const char *path, const char *umma);
 
 }  // namespace tqt

@@ -44,6 +44,10 @@ struct UmmaArgs {
     uint32_t band_m;  // tile order: activation-row tiles are walked in bands of this many (0 = one band)
     unsigned int *fault;
     long long *dbg;  // optional per-CTA role timing (diagnostic), 16 slots per CTA
+    uint32_t wait_shift;  // test knob: every wait limit is shifted right by this (0 = about a second)
+    uint32_t inject;      // test knob, bit 0: the first producer warp withholds the copies and the arrive of its
+                          // very first stage, so that the waits downstream of it run out (host-made failure:
+                          // nothing traps, faults or spins without a limit)
 };
 
 // Tile t of a cm x cn tile grid, walked band by band: inside a band of `band` row tiles the row index

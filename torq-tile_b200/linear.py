@@ -15,6 +15,11 @@ from . import (GemmReqI8, GemmW4A8, GemmW4A16, QaI8DxQsI4CxParams, QaI8QaI8QsI8C
 
 _TORCH_TD = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 FLT_MAX = 3.4028234663852886e38
+BF16_MAX = 3.3895313892515355e38   # largest finite bf16
+F16_MAX = 65504.0
+# "no clamp" per output type: the largest finite value of the type (bf16 has the f32 exponent range,
+# so the f16 maximum would saturate it at +-65536)
+_NO_CLAMP = {"f32": (-FLT_MAX, FLT_MAX), "f16": (-F16_MAX, F16_MAX), "bf16": (-BF16_MAX, BF16_MAX)}
 
 
 class _HostPipelined:
@@ -147,9 +152,7 @@ class W4A8Linear(_HostPipelined):
         self.uk.run_bt_pack(self.n, k, k, k, 0, nib.contiguous(), self.b_packed)
         self.scale_b = scale_b.contiguous()
         self.bias = None if bias is None else bias.to(self.td).contiguous()
-        if clamp is None:
-            clamp = (-FLT_MAX, FLT_MAX) if out_dtype == "f32" else (-65504.0, 65504.0)
-        self.clamp = clamp
+        self.clamp = _NO_CLAMP[out_dtype] if clamp is None else clamp
         self._ws = {}
 
     def workspace(self, m):
@@ -249,9 +252,7 @@ class W4A16Linear(_HostPipelined):
         self.uk.run_bt_pack(self.n, k, k, k, 0, nib.contiguous(), self.b_packed)
         self.scale_b = scale_b.contiguous()   # [n, k/bl] f16, not packed
         self.bias = None if bias is None else bias.to(self.td).contiguous()
-        if clamp is None:
-            clamp = (-FLT_MAX, FLT_MAX) if out_dtype == "f32" else (-65504.0, 65504.0)
-        self.clamp = clamp
+        self.clamp = _NO_CLAMP[out_dtype] if clamp is None else clamp
         self._ws = {}
 
     def workspace(self, m):
