@@ -53,6 +53,8 @@ struct GemvArgs {
     const float *scale_b;
     float cmin, cmax;
     int pdl;
+    int exp_flags;   // experiment switches (TQT_B200_GEMV_EXP, diagnostics only): 1 = no wait for the predecessor,
+                     // 2 = activations requested before the wait (both valid only while the inputs are static)
 };
 
 // 128-bit streaming load: read-only path, do not keep the line in L1.
@@ -65,6 +67,15 @@ __device__ __forceinline__ uint4 ldg_stream(const void *p)
     return v;
 }
 
+// 16-byte asynchronous copy global -> shared (L2 only, not through registers); bytes = 0 writes zeros and reads
+// nothing.  A thread that waits for its own copies (cp_async_wait_all) may read what they wrote without a barrier.
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src, uint32_t bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 constexpr uint32_t kGemvSlices = kGemvThreads / 32;   // warps of a CTA = interleaved K slices
 constexpr uint32_t kGemvChunk = 4;                   // loads in flight per thread
 
@@ -74,14 +85,24 @@ constexpr uint32_t kGemvChunk = 4;                   // loads in flight per thre
 // phases of back-to-back GEMVs do not overlap.  With G = 2 a CTA streams 16 columns (eight 128-bit loads in
 // flight per thread, the activation words shared by both groups), the launch takes two slots per SM, and the
 // next GEMV of the chain is resident and has its weights in flight while this one runs its post-wait tail.
-template <int MR, int G>
-constexpr int gemv_min_ctas() { return G == 2 ? 2 : (MR <= 2 ? 4 : (MR <= 8 ? 3 : 2)); }
+//
+// STAGED: the weight loads in flight are held in shared memory (16-byte cp.async, one private slot per thread and
+// load) instead of registers.  A decode-sized launch then needs about a third of the register file instead of
+// most of it, so the CTAs of the next GEMV of a chain find room beside this one's: its weights stream in while
+// this kernel runs the serial tail that follows its wait for the predecessor.
+template <int MR, int G, bool STAGED>
+constexpr int gemv_min_ctas() { return STAGED ? (MR <= 4 ? 4 : 3) : (G == 2 ? 2 : (MR <= 2 ? 4 : (MR <= 8 ? 3 : 2))); }
 
-template <int MR, int G, Dtype TD>
-__global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a8_kernel(const GemvArgs args)
+template <int MR, int G, bool STAGED, Dtype TD>
+__global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G, STAGED>()) gemv_w4a8_kernel(const GemvArgs args)
 {
     constexpr uint32_t S = kGemvSlices, CH = kGemvChunk;
     __shared__ int32_t sRed[(S - 1) * G * kGemvWarpRows * (MR + 1)];
+    __shared__ uint4 sW[STAGED ? G * CH * kGemvThreads : 1];   // slot (gi, i) of thread t at [(gi * CH + i) * threads + t]
+#ifdef TQT_GEMV_PAD_SMEM
+    __shared__ int32_t sPad[TQT_GEMV_PAD_SMEM / 4];
+    if (args.exp_flags & 512) sPad[threadIdx.x] = 1;
+#endif
     const uint32_t tid = threadIdx.x, ks = tid >> 5, lane = tid & 31u;
     const uint32_t rr = lane >> 2;                                 // row inside the group
     const uint32_t pos = lane & 3u;                                // physical 16-byte segment
@@ -107,18 +128,24 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
             rp[gi] = blk + kI4NibBytes + r_blk * 2u;   // tail of every packed block: the zero-point correction terms
         }
     };
-    uint4 w[G][CH];
+    uint4 w[STAGED ? 1 : G][STAGED ? 1 : CH];
     int32_t rsv[G][CH];
+    const uint32_t sw0 = ptx::smem_u32(sW) + tid * 16u;
     auto load_chunk = [&](uint32_t t0) {   // K blocks t0 .. t0 + CH - 1 of this warp
 #pragma unroll
         for (int gi = 0; gi < G; ++gi) {
 #pragma unroll
             for (uint32_t i = 0; i < CH; ++i) {
                 const bool ok = gok[gi] && t0 + i < T;
-                w[gi][i] = ok ? ldg_stream(wp[gi] + (size_t)(t0 + i) * kWStep) : make_uint4(0, 0, 0, 0);
-                rsv[gi][i] = (ok && pos == 0) ? (int32_t)__ldg(reinterpret_cast<const int16_t *>(rp[gi] + (size_t)(t0 + i) * kWStep)) : 0;
+                if constexpr (STAGED)
+                    cp_async16(sw0 + (uint32_t)(gi * CH + i) * (kGemvThreads * 16u), ok ? wp[gi] + (size_t)(t0 + i) * kWStep : args.B,
+                               ok ? 16u : 0u);
+                else
+                    w[gi][i] = ok ? ldg_stream(wp[gi] + (size_t)(t0 + i) * kWStep) : make_uint4(0, 0, 0, 0);
+                rsv[gi][i] = (ok && pos == 0 && !(args.exp_flags & 4)) ? (int32_t)__ldg(reinterpret_cast<const int16_t *>(rp[gi] + (size_t)(t0 + i) * kWStep)) : 0;
             }
         }
+        if constexpr (STAGED) cp_async_commit();
     };
     uint32_t sg = blockIdx.x;
     set_group(sg);
@@ -140,7 +167,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
     };
     load_column_constants(sg);
     // everything else may have been produced by the preceding kernel
-    if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (args.pdl && !(args.exp_flags & 1)) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     float sa[MR];
     int32_t zp[MR];
@@ -166,6 +193,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
         }
 
         for (uint32_t t0 = 0; t0 < T; t0 += CH) {
+            if constexpr (STAGED) cp_async_wait_all();   // this thread's own copies: no barrier needed to read them
 #pragma unroll
             for (int mi = 0; mi < MR; ++mi) {
                 if (MR == 1 || (uint32_t)mi < args.m) {
@@ -174,11 +202,11 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
 #pragma unroll
                     for (uint32_t i = 0; i < CH; ++i) {
                         const uint8_t *act = ap + (size_t)(t0 + i) * kAStep;
-                        const bool ok = t0 + i < T;
+                        const bool ok = t0 + i < T && !(args.exp_flags & 8);
                         av[i][0] = ok ? __ldg(reinterpret_cast<const uint4 *>(act + sw128_byte((uint32_t)mi, seg * 32u)))
-                                      : make_uint4(0, 0, 0, 0);
+                                      : make_uint4(1, 2, 3, 4);
                         av[i][1] = ok ? __ldg(reinterpret_cast<const uint4 *>(act + sw128_byte((uint32_t)mi, seg * 32u + 16u)))
-                                      : make_uint4(0, 0, 0, 0);
+                                      : make_uint4(5, 6, 7, 8);
                     }
 #pragma unroll
                     for (uint32_t i = 0; i < CH; ++i) {
@@ -186,7 +214,10 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
                         const uint32_t ah[4] = {av[i][1].x, av[i][1].y, av[i][1].z, av[i][1].w};
 #pragma unroll
                         for (int gi = 0; gi < G; ++gi) {
-                            const uint32_t ws[4] = {w[gi][i].x, w[gi][i].y, w[gi][i].z, w[gi][i].w};
+                            uint4 wv;
+                            if constexpr (STAGED) wv = sW[(gi * CH + i) * kGemvThreads + tid];
+                            else wv = w[gi][i];
+                            const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const uint32_t lo = (ws[j] << 4) & 0xF0F0F0F0u;   // 16*q for k = 32*seg + 4j .. +3
@@ -224,6 +255,12 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 acc[gi][mi] = v;
             }
+        }
+        if (args.exp_flags & 16) {   // experiment: no cross-warp combine, no epilogue (keeps the loads alive)
+            if (acc[0][0] == 0x7f123456) static_cast<int *>(args.D)[tid] = rsum[0];
+            if (next >= sgroups) break;
+            sg = next;
+            continue;
         }
         // ... and the eight warps through shared memory
         if (ks > 0 && pos == 0) {
@@ -270,6 +307,241 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
     }
 }
 
+// ======================================================================================================
+// GEMV for 1 <= m <= 16 on mma.sync (m16n8k32, s8 x s8 -> s32), weights streamed through registers.
+// The tensor cores here are a convenience, not a throughput need: the 16-row A fragment is exactly a decode
+// batch, so one kernel serves every m <= 16 at nearly the cost of m = 1, and the activations are fetched once
+// per CTA (staged in shared memory after the wait for the predecessor) instead of once per lane and row.
+//
+// A CTA owns a set of 8 G consecutive output columns (G = 2 or 4 groups of 8); warp w takes K blocks w, w+8, ...
+// Lane (g, t) = (lane / 4, lane % 4) streams, per group and K block, the 16 bytes of weight row g that hold
+// logical segment t (physical position t ^ ((g >> 1) & 3): a warp-wide load still covers 512 contiguous
+// bytes), and supplies, for MMA step j, b0 = 16 q[col g][32 t + 4 j ..] and b1 = 16 q[col g][32 t + 16 + 4 j ..]
+// (the two masks of word j).  The A fragment takes words j of activation chunks 2t / 2t+1 of rows g / g+8: any
+// consistent permutation of k is a valid contraction order, and integer sums are exact.  The column sums of the
+// weights (the zero-point correction) are accumulated from the same words with dp4a against ones, so the row-sum
+// tails of the packed blocks are not read.  The eight warps are combined through shared
+// memory; warp 0 runs the epilogue (reference: src/gemm/gemm_i8_i4/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp/
+// ..._4x1vl_rvv.cpp:118-177).  No mbarrier, no scratch memory.
+//
+// All weight loads of a CTA's first set are requested before griddepcontrol.wait.  With G = 4 a decode-sized
+// launch (N = 4096: 128 CTAs of 256 threads) takes under half of the register file, so the next GEMV of a chain
+// is resident with its weights in flight while this one runs its post-wait tail.
+// ======================================================================================================
+constexpr uint32_t kGvRedInts = 5u * 32u;   // per warp and group: [acc0..3, column sum][lane]
+
+__device__ __forceinline__ void mma_s8_16832(int32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                             uint32_t b1)
+{
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int G>
+constexpr int gemv_mma_min_ctas() { return 2; }
+
+// Dynamic shared memory: [m rows][K blocks][128 B] activations (as they lie in the packed blocks) | [7 warps][G][reduce].
+// R16: the launch has more than 8 activation rows (fragment rows g + 8 exist); their fragments are then fetched
+// two K blocks at a time to stay inside the register budget.
+template <int G, bool R16, Dtype TD>
+__global__ void __launch_bounds__(kGemvThreads, gemv_mma_min_ctas<G>()) gemv_mma_kernel(const GemvArgs args)
+{
+    constexpr uint32_t S = kGemvSlices, CH = kGemvChunk;
+    __shared__ int32_t sRed[(S - 1) * G * kGvRedInts];
+    const uint32_t tid = threadIdx.x, ks = tid >> 5, lane = tid & 31u;
+    const uint32_t g = lane >> 2, t4 = lane & 3u;
+    const uint32_t KB = (args.k + 127) / 128;
+    const uint32_t T = KB > ks ? (KB - ks + S - 1) / S : 0;        // K blocks of this warp: ks, ks+S, ...
+    const uint32_t groups = (args.n + kGemvWarpRows - 1) / kGemvWarpRows;
+    const uint32_t sets = (groups + G - 1) / G;
+
+    if (args.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    constexpr size_t kWStep = (size_t)S * kI4CxBlockBytes;
+    const uint32_t wpos = (t4 ^ ((g >> 1) & 3u)) * 16u;   // physical position of logical segment t4 in weight row g
+    const uint8_t *wp[G];
+    bool gok[G];
+    auto set_group = [&](uint32_t sg) {
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            const uint32_t grp = sg * G + gi;
+            gok[gi] = grp < groups;
+            const uint32_t row0 = (gok[gi] ? grp : 0u) * kGemvWarpRows, tile = row0 >> 7, r_blk = (row0 & 127u) + g;
+            wp[gi] = args.B + ((size_t)tile * args.b_kblocks_total + ks) * kI4CxBlockBytes + r_blk * 64u + wpos;
+        }
+    };
+    uint4 w[G][CH];
+    auto load_chunk = [&](uint32_t t0) {   // K blocks t0 .. t0 + CH - 1 of this warp
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+#pragma unroll
+            for (uint32_t i = 0; i < CH; ++i) {
+                const bool ok = gok[gi] && t0 + i < T;
+                w[gi][i] = ok ? ldg_stream(wp[gi] + (size_t)(t0 + i) * kWStep) : make_uint4(0, 0, 0, 0);
+            }
+        }
+    };
+    uint32_t sg = blockIdx.x;
+    set_group(sg);
+    load_chunk(0);
+    // per-column constants (warp 0 only): requested together with the activations, one round trip for all
+    float sb[G][2], bv[G][2];
+    auto load_column_constants = [&](uint32_t sg_) {
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                const uint32_t n = (sg_ * G + gi) * kGemvWarpRows + 2u * t4 + c;
+                sb[gi][c] = 0.0f;
+                bv[gi][c] = 0.0f;
+                if (ks == 0 && n < args.n) {
+                    sb[gi][c] = args.scale_b[n];
+                    bv[gi][c] = args.bias ? TdTraits<TD>::load(args.bias, n) : 0.0f;
+                }
+            }
+        }
+    };
+    // everything else may have been produced by the preceding kernel
+    if (args.pdl && !(args.exp_flags & 1)) asm volatile("griddepcontrol.wait;" ::: "memory");
+    load_column_constants(sg);
+
+    float sa[2] = {0.0f, 0.0f};
+    int32_t zp[2] = {0, 0};
+    if (ks == 0) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t row = g + 8u * h;
+            if (row < args.m) {
+                sa[h] = args.scale_a[row];
+                zp[h] = args.zp_a[row];
+            }
+        }
+    }
+    const bool row_lo = g < args.m, row_hi = R16 && g + 8u < args.m;   // this lane's fragment rows exist
+    const uint32_t a_lo_off = g * 128u + (((2u * t4) ^ g) << 4), a_hi_off = g * 128u + (((2u * t4 + 1u) ^ g) << 4);
+
+    while (true) {
+        int32_t acc[G][4], rs[G];   // rs: 16 * sum of q over this lane's words of weight row g
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+            rs[gi] = 0;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[gi][e] = 0;
+        }
+        for (uint32_t t0 = 0; t0 < T; t0 += CH) {
+            // activation fragments, straight from the packed blocks (L2): logical chunks 2 t4 and 2 t4 + 1 of rows g
+            // and g + 8 ((g + 8) & 7 = g: same swizzle); a batch is requested whole before its first use
+            constexpr uint32_t BA = R16 ? 2u : CH;   // K blocks per batch of fragments
+#pragma unroll
+            for (uint32_t i0 = 0; i0 < CH; i0 += BA) {
+                uint4 fa[BA][2], fb[R16 ? BA : 1][2];
+#pragma unroll
+                for (uint32_t u = 0; u < BA; ++u) {
+                    const uint8_t *ab = args.A + (size_t)(ks + (t0 + i0 + u) * S) * kI8BlockBytes;
+                    const bool in = t0 + i0 + u < T;
+                    fa[u][0] = (in && row_lo) ? __ldg(reinterpret_cast<const uint4 *>(ab + a_lo_off)) : make_uint4(0, 0, 0, 0);
+                    fa[u][1] = (in && row_lo) ? __ldg(reinterpret_cast<const uint4 *>(ab + a_hi_off)) : make_uint4(0, 0, 0, 0);
+                    if constexpr (R16) {
+                        fb[u][0] = (in && row_hi) ? __ldg(reinterpret_cast<const uint4 *>(ab + 1024u + a_lo_off)) : make_uint4(0, 0, 0, 0);
+                        fb[u][1] = (in && row_hi) ? __ldg(reinterpret_cast<const uint4 *>(ab + 1024u + a_hi_off)) : make_uint4(0, 0, 0, 0);
+                    }
+                }
+#pragma unroll
+                for (uint32_t u = 0; u < BA; ++u) {
+                    const uint32_t i = i0 + u;
+                    const uint32_t a0[4] = {fa[u][0].x, fa[u][0].y, fa[u][0].z, fa[u][0].w};
+                    const uint32_t a2[4] = {fa[u][1].x, fa[u][1].y, fa[u][1].z, fa[u][1].w};
+                    uint32_t a1[4] = {0u, 0u, 0u, 0u}, a3[4] = {0u, 0u, 0u, 0u};
+                    if constexpr (R16) {
+                        a1[0] = fb[u][0].x; a1[1] = fb[u][0].y; a1[2] = fb[u][0].z; a1[3] = fb[u][0].w;
+                        a3[0] = fb[u][1].x; a3[1] = fb[u][1].y; a3[2] = fb[u][1].z; a3[3] = fb[u][1].w;
+                    }
+#pragma unroll
+                    for (int gi = 0; gi < G; ++gi) {
+                        const uint32_t ws[4] = {w[gi][i].x, w[gi][i].y, w[gi][i].z, w[gi][i].w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const uint32_t b0 = (ws[j] << 4) & 0xF0F0F0F0u;   // 16*q, k = 32 t4 + 4 j .. + 3
+                            const uint32_t b1 = ws[j] & 0xF0F0F0F0u;          // 16*q, k = 32 t4 + 16 + 4 j .. + 3
+                            mma_s8_16832(acc[gi], a0[j], a1[j], a2[j], a3[j], b0, b1);
+                            rs[gi] = __dp4a((int)b0, 0x01010101, rs[gi]);
+                            rs[gi] = __dp4a((int)b1, 0x01010101, rs[gi]);
+                        }
+                    }
+                }
+            }
+            if (t0 + CH < T) load_chunk(t0 + CH);
+        }
+
+        // request the next set's first chunk before combining this one: the registers are free
+        const uint32_t cur = sg, next = sg + gridDim.x;
+        if (next < sets) {
+            set_group(next);
+            load_chunk(0);
+        }
+
+        // the four lanes of a weight row hold its four segments: after this every lane (g, *) has the sum of row g
+#pragma unroll
+        for (int gi = 0; gi < G; ++gi) {
+
+            rs[gi] += __shfl_xor_sync(0xffffffffu, rs[gi], 1);
+            rs[gi] += __shfl_xor_sync(0xffffffffu, rs[gi], 2);
+        }
+        // combine the eight warps through shared memory
+        if (ks > 0) {
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+                int32_t *dst = sRed + ((ks - 1) * G + gi) * kGvRedInts + lane;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) dst[e * 32] = acc[gi][e];
+                dst[4 * 32] = rs[gi];
+            }
+        }
+        if (args.exp_flags & 128) {   // experiment: no combine, no epilogue
+            if (acc[0][0] == 0x7f123456) static_cast<int *>(args.D)[tid] = rs[0];
+            if (next >= sets) break;
+            sg = next;
+            continue;
+        }
+        __syncthreads();
+        if (ks == 0) {
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+#pragma unroll
+                for (uint32_t s2 = 1; s2 < S; ++s2) {
+                    const int32_t *src = sRed + ((s2 - 1) * G + gi) * kGvRedInts + lane;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[gi][e] += src[e * 32];
+                    rs[gi] += src[4 * 32];
+                }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    // this lane's accumulator columns are 2 t4 + c; the sum of weight row r sits in lanes 4 r .. 4 r + 3
+                    const int32_t rsum = __shfl_sync(0xffffffffu, rs[gi], (int)((2u * t4 + c) * 4u)) >> 4;
+                    const uint32_t n = (cur * G + gi) * kGemvWarpRows + 2u * t4 + c;
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t row = g + 8u * h;
+                        if (row < args.m && n < args.n) {
+                            int32_t a = acc[gi][2 * h + c] >> 4;   // operands were 16*q
+                            a -= zp[h] * rsum;
+                            const float cv = args.C ? TdTraits<TD>::load(args.C, (size_t)row * args.ldc + n) : 0.0f;
+                            const float v = w4a8_epilogue(a, sa[h], sb[gi][c], args.C != nullptr, cv, args.bias != nullptr,
+                                                          bv[gi][c], args.cmin, args.cmax);
+                            TdTraits<TD>::store(args.D, (size_t)row * args.ldd + n, v);
+                        }
+                    }
+                }
+            }
+        }
+        if (next >= sets) break;
+        sg = next;
+        load_column_constants(sg);
+        __syncthreads();   // the partial sums in shared memory have been read
+    }
+}
+
 bool pdl_enabled()
 {
     static int cached = -1;
@@ -291,15 +563,30 @@ static int gemv_forced_groups()
     return cached;
 }
 
-template <int MR, int G, Dtype TD>
+// TQT_B200_GEMV_STAGE=0|1 forces register-held or shared-memory-held weight loads (read once).
+static int gemv_forced_stage()
+{
+    static const int cached = [] {
+        const char *e = std::getenv("TQT_B200_GEMV_STAGE");
+        return e ? std::atoi(e) : -1;
+    }();
+    return cached;
+}
+
+template <int MR, int G, bool STAGED, Dtype TD>
 static Result launch_gemv_t(GemvArgs a, cudaStream_t st)
 {
     a.pdl = pdl_enabled() ? 1 : 0;
+    static const int exp_flags = [] {
+        const char *e = std::getenv("TQT_B200_GEMV_EXP");
+        return e ? std::atoi(e) : 0;
+    }();
+    a.exp_flags = exp_flags;
     cudaLaunchConfig_t cfg = {};
     // CTA c owns the sets of G 8-column groups c, c + grid, ...: one set each while they all fit on the GPU at once
     const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
     const uint32_t sgroups = (groups + G - 1) / G;
-    const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_min_ctas<MR, G>();
+    const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_min_ctas<MR, G, STAGED>();
     cfg.gridDim = dim3(sgroups < resident ? sgroups : resident, 1, 1);
     cfg.blockDim = dim3(kGemvThreads, 1, 1);
     cfg.dynamicSmemBytes = 0;
@@ -309,7 +596,7 @@ static Result launch_gemv_t(GemvArgs a, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a8_kernel<MR, G, TD>, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a8_kernel<MR, G, STAGED, TD>, a);
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
     return Result{kOk, 0};
 }
@@ -319,16 +606,66 @@ static Result launch_gemv_g(const GemvArgs &a, cudaStream_t st)
 {
     if constexpr (MR <= 8) {
         const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
-        const int forced = gemv_forced_groups();
+        const int forced = gemv_forced_groups(), stage = gemv_forced_stage();
         const bool two = forced ? forced == 2 : (groups + 1) / 2 <= (uint32_t)sm_count_cached() * 2u;
-        if (two) return launch_gemv_t<MR, 2, TD>(a, st);
+        if (two) {
+            if (stage == 1) return launch_gemv_t<MR, 2, true, TD>(a, st);
+            return launch_gemv_t<MR, 2, false, TD>(a, st);
+        }
     }
-    return launch_gemv_t<MR, 1, TD>(a, st);
+    return launch_gemv_t<MR, 1, false, TD>(a, st);
+}
+
+// TQT_B200_GEMV_KERNEL=regs|mma forces the register-held dp4a kernel or the shared-memory mma.sync kernel (read once).
+static int gemv_forced_kernel()
+{
+    static const int cached = [] {
+        const char *e = std::getenv("TQT_B200_GEMV_KERNEL");
+        if (!e) return 0;
+        return e[0] == 'r' ? 1 : (e[0] == 'm' ? 2 : 0);
+    }();
+    return cached;
+}
+
+template <int G, bool R16, Dtype TD>
+static Result launch_gemv_mma(GemvArgs a, cudaStream_t st)
+{
+    a.pdl = pdl_enabled() ? 1 : 0;
+    static const int exp_flags = [] {
+        const char *e = std::getenv("TQT_B200_GEMV_EXP");
+        return e ? std::atoi(e) : 0;
+    }();
+    a.exp_flags = exp_flags;
+    const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows, sets = (groups + G - 1) / G;
+    const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_mma_min_ctas<G>();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sets < resident ? sets : resident, 1, 1);
+    cfg.blockDim = dim3(kGemvThreads, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_mma_kernel<G, R16, TD>, a);
+    if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
+    return Result{kOk, 0};
 }
 
 template <Dtype TD>
 static Result launch_gemv_m(const GemvArgs &a, cudaStream_t st)
 {
+    const int forced = gemv_forced_kernel();
+    if (forced == 2 || (forced == 0 && a.m > 1)) {
+        // four column groups per CTA while the launch still fills the GPU (two CTAs per SM), two otherwise
+        const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
+        const int fg = gemv_forced_groups();
+        (void)groups;
+        const bool one = fg == 1;
+        if (a.m > 8) return one ? launch_gemv_mma<1, true, TD>(a, st) : launch_gemv_mma<2, true, TD>(a, st);
+        return one ? launch_gemv_mma<1, false, TD>(a, st) : launch_gemv_mma<2, false, TD>(a, st);
+    }
     if (a.m <= 1) return launch_gemv_g<1, TD>(a, st);
     if (a.m <= 2) return launch_gemv_g<2, TD>(a, st);
     if (a.m <= 4) return launch_gemv_g<4, TD>(a, st);
