@@ -88,13 +88,55 @@ struct tqt_qai8dxp_qsi8cxp_params {
     void tqt_run_bt_pack_##TYPE##_128x128_sm100a(size_t n, size_t k, size_t ldb, size_t ldb_packed, size_t k_idx,     \
                                                  const void *B, void *B_packed);
 
+/* The function-pointer table of a kernel type, member for member as the reference's <type>_interface.h
+ * (src/gemm/<family>/<type>/tqt_<type>_interface.h): a caller fills it with this variant's symbols exactly as it
+ * does with the RVV variant's (examples/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp_rvv/..._rvv.cpp:28-41). */
+#define TQT_B200_DECLARE_UNPACKED_UKERNEL(TYPE, CLAMPT, PARAMS)                                                        \
+    struct tqt_##TYPE##_ukernel {                                                                                      \
+        size_t (*get_m_step)(void);                                                                                    \
+        size_t (*get_n_step)(void);                                                                                    \
+        size_t (*get_a_offset)(size_t m_idx, size_t k_idx, size_t lda);                                                \
+        size_t (*get_b_offset)(size_t n_idx, size_t k_idx, size_t ldb);                                                \
+        size_t (*get_c_offset)(size_t m_idx, size_t n_idx, size_t ldc);                                                \
+        size_t (*get_bias_offset)(size_t idx);                                                                         \
+        size_t (*get_d_offset)(size_t m_idx, size_t n_idx, size_t ldd);                                                \
+        size_t (*get_d_size)(size_t m, size_t n);                                                                      \
+        void (*run_gemm)(size_t m, size_t n, size_t k, const void *A, size_t lda, size_t k_idx_a, const void *B,       \
+                         size_t ldb, size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias, \
+                         CLAMPT clamp_min, CLAMPT clamp_max, const struct PARAMS *params);                             \
+    };
+
+#define TQT_B200_DECLARE_PACKED_I8_UKERNEL(TYPE, CLAMPT, PARAMS)                                                       \
+    struct tqt_##TYPE##_ukernel {                                                                                      \
+        size_t (*get_m_step)(void);                                                                                    \
+        size_t (*get_n_step)(void);                                                                                    \
+        size_t (*get_a_packed_offset)(size_t m_idx, size_t k_idx, size_t lda, size_t actual_m);                        \
+        size_t (*get_b_packed_offset)(size_t n_idx, size_t k_idx, size_t ldb, size_t actual_n);                        \
+        size_t (*get_c_offset)(size_t m_idx, size_t n_idx, size_t ldc);                                                \
+        size_t (*get_bias_offset)(size_t idx);                                                                         \
+        size_t (*get_d_offset)(size_t m_idx, size_t n_idx, size_t ldd);                                                \
+        size_t (*get_d_size)(size_t m, size_t n);                                                                      \
+        size_t (*get_a_packed_size)(size_t m, size_t k);                                                               \
+        size_t (*get_b_packed_size)(size_t n, size_t k);                                                               \
+        void (*run_a_pack)(size_t m, size_t k, size_t lda, size_t lda_packed, size_t k_idx, const void *A,             \
+                           void *A_packed);                                                                            \
+        void (*run_b_pack)(size_t n, size_t k, size_t ldb, size_t ldb_packed, size_t k_idx, const void *B,             \
+                           void *B_packed);                                                                            \
+        void (*run_bt_pack)(size_t n, size_t k, size_t ldb, size_t ldb_packed, size_t k_idx, const void *B,            \
+                            void *B_packed);                                                                           \
+        void (*run_gemm)(size_t m, size_t n, size_t k, const void *A_packed, size_t lda, size_t k_idx_a,       \
+                         const void *B_packed, size_t ldb, size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias, \
+                         CLAMPT clamp_min, CLAMPT clamp_max, const struct PARAMS *params);                             \
+    };
+
 /* ---- W4A8 on unpacked operands ----------------------------------------------------------------------- */
 #define TQT_B200_DECLARE_W4A8_UNPACKED(TDNAME, TDTYPE)                                                                \
     TQT_B200_DECLARE_UNPACKED_HELPERS(gemm_1xnbias_clamp_##TDNAME##_qai8dx_qsi4cxt)                                   \
     void tqt_run_gemm_1xnbias_clamp_##TDNAME##_qai8dx_qsi4cxt_128x128_sm100a(                                         \
         size_t m, size_t n, size_t k, const void *A, size_t lda, size_t k_idx_a, const void *B, size_t ldb,           \
         size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias, TDTYPE clamp_min,           \
-        TDTYPE clamp_max, const struct tqt_qai8dx_qsi4cx_params *params);
+        TDTYPE clamp_max, const struct tqt_qai8dx_qsi4cx_params *params);                                             \
+    TQT_B200_DECLARE_UNPACKED_UKERNEL(gemm_1xnbias_clamp_##TDNAME##_qai8dx_qsi4cxt, TDTYPE, tqt_qai8dx_qsi4cx_params)
 
 TQT_B200_DECLARE_W4A8_UNPACKED(f32, float)
 #if !defined(TQT_B200_NO_HALF_TYPES)
@@ -108,6 +150,7 @@ void tqt_run_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxt_128x128_sm100a(
     size_t m, size_t n, size_t k, const void *A, size_t lda, size_t k_idx_a, const void *B, size_t ldb,
     size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias, int8_t clamp_min,
     int8_t clamp_max, const struct tqt_qai8_qai8_qsi8cx_params *params);
+TQT_B200_DECLARE_UNPACKED_UKERNEL(gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxt, int8_t, tqt_qai8_qai8_qsi8cx_params)
 
 size_t tqt_get_m_step_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp_128x128_sm100a(void);
 size_t tqt_get_n_step_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp_128x128_sm100a(void);
@@ -134,6 +177,24 @@ void tqt_run_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp_128x128_sm100a(
     size_t m, size_t n, size_t k, const void *A, size_t lda, size_t k_idx_a, const void *B_packed, size_t ldb,
     size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias, int8_t clamp_min,
     int8_t clamp_max, const struct tqt_qai8_qai8_qsi8cx_params *params);
+/* A in its original layout, B packed (src/gemm/gemm_i8_i8/gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp/
+ * tqt_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp_interface.h:52-67). */
+struct tqt_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp_ukernel {
+    size_t (*get_m_step)(void);
+    size_t (*get_n_step)(void);
+    size_t (*get_a_offset)(size_t m_idx, size_t k_idx, size_t lda);
+    size_t (*get_b_packed_offset)(size_t n_idx, size_t k_idx, size_t ldb, size_t actual_n);
+    size_t (*get_c_offset)(size_t m_idx, size_t n_idx, size_t ldc);
+    size_t (*get_bias_offset)(size_t n_idx);
+    size_t (*get_d_offset)(size_t m_idx, size_t n_idx, size_t ldd);
+    size_t (*get_d_size)(size_t m, size_t n);
+    size_t (*get_b_packed_size)(size_t n, size_t k);
+    void (*run_b_pack)(size_t n, size_t k, size_t ldb, size_t ldb_packed, size_t k_idx, const void *B, void *B_packed);
+    void (*run_bt_pack)(size_t n, size_t k, size_t ldb, size_t ldb_packed, size_t k_idx, const void *B, void *B_packed);
+    void (*run_gemm)(size_t m, size_t n, size_t k, const void *A, size_t lda, size_t k_idx_a, const void *B_packed,
+                     size_t ldb, size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias,
+                     int8_t clamp_min, int8_t clamp_max, const struct tqt_qai8_qai8_qsi8cx_params *params);
+};
 
 /* ---- static W8A8 requantisation, Mx1 bias, per-row scale of A ------------------------------------------ */
 TQT_B200_DECLARE_UNPACKED_HELPERS(gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8)
@@ -141,12 +202,14 @@ void tqt_run_gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8_128x128_sm100a(
     size_t m, size_t n, size_t k, const void *A, size_t lda, size_t k_idx_a, const void *B, size_t ldb,
     size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias, int8_t clamp_min,
     int8_t clamp_max, const struct tqt_qai8_qsi8dx_qai8_params *params);
+TQT_B200_DECLARE_UNPACKED_UKERNEL(gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8, int8_t, tqt_qai8_qsi8dx_qai8_params)
 
 TQT_B200_DECLARE_PACKED_I8_HELPERS(gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p)
 void tqt_run_gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p_128x128_sm100a(
     size_t m, size_t n, size_t k, const void *A_packed, size_t lda, size_t k_idx_a, const void *B_packed,
     size_t ldb, size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias,
     int8_t clamp_min, int8_t clamp_max, const struct tqt_qai8_qsi8dx_qai8_params *params);
+TQT_B200_DECLARE_PACKED_I8_UKERNEL(gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p, int8_t, tqt_qai8_qsi8dx_qai8_params)
 
 /* ---- dynamic-activation W8A8 with float output (qai8dx x qsi8cx) --------------------------------------- */
 #define TQT_B200_DECLARE_DXCX(TDNAME, TDTYPE)                                                                         \
@@ -155,11 +218,13 @@ void tqt_run_gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p_128x128_sm100a(
         size_t m, size_t n, size_t k, const void *A, size_t lda, size_t k_idx_a, const void *B, size_t ldb,           \
         size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias, TDTYPE clamp_min,           \
         TDTYPE clamp_max, const struct tqt_qai8dxp_qsi8cxp_params *params);                                           \
+    TQT_B200_DECLARE_UNPACKED_UKERNEL(gemm_1xnbias_clamp_##TDNAME##_qai8dx_qsi8cxt, TDTYPE, tqt_qai8dxp_qsi8cxp_params) \
     TQT_B200_DECLARE_PACKED_I8_HELPERS(gemm_1xnbias_clamp_##TDNAME##_qai8dxp_qsi8cxp)                                 \
     void tqt_run_gemm_1xnbias_clamp_##TDNAME##_qai8dxp_qsi8cxp_128x128_sm100a(                                        \
         size_t m, size_t n, size_t k, const void *A_packed, size_t lda, size_t k_idx_a, const void *B_packed,         \
         size_t ldb, size_t k_idx_b, const void *C, size_t ldc, void *D, size_t ldd, const void *bias,                 \
-        TDTYPE clamp_min, TDTYPE clamp_max, const struct tqt_qai8dxp_qsi8cxp_params *params);
+        TDTYPE clamp_min, TDTYPE clamp_max, const struct tqt_qai8dxp_qsi8cxp_params *params);                         \
+    TQT_B200_DECLARE_PACKED_I8_UKERNEL(gemm_1xnbias_clamp_##TDNAME##_qai8dxp_qsi8cxp, TDTYPE, tqt_qai8dxp_qsi8cxp_params)
 
 TQT_B200_DECLARE_DXCX(f32, float)
 #if !defined(TQT_B200_NO_HALF_TYPES)
@@ -186,7 +251,21 @@ TQT_B200_DECLARE_DXCX(f16, float16_t)
     void tqt_run_gemm_1xnbias_clamp_##TDNAME##_f16_qsi4c2t_128x128_sm100a(                                            \
         size_t m, size_t n, size_t k, size_t bl, const void *A, size_t lda, size_t k_idx_a, const void *B,            \
         size_t ldb, size_t k_idx_b, const void *scale_b, size_t ldsb, const void *C, size_t ldc, void *D,             \
-        size_t ldd, const void *bias, TDTYPE clamp_min, TDTYPE clamp_max);
+        size_t ldd, const void *bias, TDTYPE clamp_min, TDTYPE clamp_max);                                            \
+    struct tqt_gemm_1xnbias_clamp_##TDNAME##_f16_qsi4c2t_ukernel {                                                    \
+        size_t (*get_m_step)(void);                                                                                   \
+        size_t (*get_n_step)(void);                                                                                   \
+        size_t (*get_a_offset)(size_t m_idx, size_t k_idx, size_t lda, size_t bl);                                    \
+        size_t (*get_b_offset)(size_t n_idx, size_t k_idx, size_t ldb, size_t bl);                                    \
+        size_t (*get_scale_b_offset)(size_t n_idx, size_t b_idx, size_t ldsb);                                        \
+        size_t (*get_c_offset)(size_t m_idx, size_t n_idx, size_t ldc);                                               \
+        size_t (*get_bias_offset)(size_t n_idx);                                                                      \
+        size_t (*get_d_offset)(size_t m_idx, size_t n_idx, size_t ldd);                                               \
+        size_t (*get_d_size)(size_t m, size_t n);                                                                     \
+        void (*run_gemm)(size_t m, size_t n, size_t k, size_t bl, const void *A, size_t lda, size_t k_idx_a,          \
+                         const void *B, size_t ldb, size_t k_idx_b, const void *scale_b, size_t ldsb, const void *C,  \
+                         size_t ldc, void *D, size_t ldd, const void *bias, TDTYPE clamp_min, TDTYPE clamp_max);      \
+    };
 
 TQT_B200_DECLARE_W4A16_UNPACKED(f32, float)
 #if !defined(TQT_B200_NO_HALF_TYPES)

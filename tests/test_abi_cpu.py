@@ -223,3 +223,46 @@ int main(void) {
     assert out.returncode == 0, out.stderr
     # 2 x 2 qsi4cx blocks of 8448 B; one int8 block with its row sums; nibble offset n_idx * (ldb / 2) + k_idx / 2
     assert out.stdout.split() == ["128", str(4 * 8448), str(16384 + 256), str(128 * 256 + 32)]
+
+
+def test_sibling_ukernel_tables_fill_and_link(pkg, tmp_path):
+    """Every sibling kernel type has a struct tqt_<type>_ukernel with the members of the reference's
+    <type>_interface.h; a C caller fills the tables with this variant's symbols (positionally for one of them,
+    which checks member order and signatures at compile time) and links.  Also accepted by a C++17 compiler."""
+    import subprocess
+    libdir = os.path.join(ROOT, "torq-tile_b200")
+    src = tmp_path / "tables.c"
+    src.write_text(r'''
+#include "tqt_b200_gemm_siblings.h"
+int main(void) {
+    struct tqt_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_ukernel a = {
+        tqt_get_m_step_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a, tqt_get_n_step_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a,
+        tqt_get_a_offset_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a, tqt_get_b_offset_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a,
+        tqt_get_c_offset_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a, tqt_get_bias_offset_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a,
+        tqt_get_d_offset_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a, tqt_get_d_size_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a,
+        tqt_run_gemm_1xnbias_clamp_f32_qai8dx_qsi4cxt_128x128_sm100a};
+    struct tqt_gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p_ukernel b;
+    b.run_gemm = tqt_run_gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p_128x128_sm100a;
+    b.run_bt_pack = tqt_run_bt_pack_gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p_128x128_sm100a;
+    struct tqt_gemm_1xnbias_clamp_f16_qai8dxp_qsi8cxp_ukernel c;
+    c.run_gemm = tqt_run_gemm_1xnbias_clamp_f16_qai8dxp_qsi8cxp_128x128_sm100a;
+    struct tqt_gemm_1xnbias_clamp_f16_f16_qsi4c2t_ukernel d;
+    d.run_gemm = tqt_run_gemm_1xnbias_clamp_f16_f16_qsi4c2t_128x128_sm100a;
+    struct tqt_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp_ukernel e;
+    e.run_gemm = tqt_run_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp_128x128_sm100a;
+    struct tqt_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxt_ukernel f;
+    f.run_gemm = tqt_run_gemm_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxt_128x128_sm100a;
+    struct tqt_gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8_ukernel g;
+    g.run_gemm = tqt_run_gemm_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8_128x128_sm100a;
+    return (int)a.get_m_step() + (b.run_gemm && c.run_gemm && d.run_gemm && e.run_gemm && f.run_gemm && g.run_gemm && b.run_bt_pack);
+}
+''')
+    exe = tmp_path / "tables"
+    r = subprocess.run(["/usr/bin/gcc", "-std=c11", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"), str(src),
+                        "-L", libdir, "-ltorq_tile_b200", f"-Wl,-rpath,{libdir}", "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 129          # m_step 128 + all table members set
+    r = subprocess.run(["/usr/bin/g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-I",
+                        os.path.join(ROOT, "include"), "-x", "c++", str(src)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr

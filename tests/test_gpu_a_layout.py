@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from oracle.tqo import TD_BF16, TD_F16, TD_F32
-from tqt_testlib import DEV, bits16, from_bits16, pkg, sync_and_check, to_dev
+from tqt_testlib import DEV, bits16, f32_to_bf16_bits, from_bits16, pkg, sync_and_check, to_dev
 
 pytestmark = pytest.mark.gpu
 
@@ -202,3 +202,32 @@ def test_quantiser_rows_in_registers_exact_division(oracle, m, k, ta):
     sync_and_check()
     assert np.array_equal(back.cpu().numpy(), q_o)
     assert np.array_equal(s2.cpu().numpy().view(np.uint32), s_o.view(np.uint32))
+
+
+def test_quantiser_rows_with_extreme_scales(oracle):
+    """bf16 rows whose range is far outside the normal f32 reciprocal range (scale below 2^-126, or a huge
+    scale): the warp-per-row kernel's corrected reciprocal cannot be used there (1 / s overflows or goes
+    subnormal), so such rows divide; every byte must equal the reference's nearbyint(x / scale) + zero point."""
+    p = pkg()
+    p.use_current_torch_stream()
+    rng = np.random.default_rng(31)
+    m, k = 64, 256
+    A = rng.normal(0, 1, (m, k)).astype(np.float32)
+    A[0] *= np.float32(1e-38)
+    A[1] *= np.float32(3e-39)
+    A[2] *= np.float32(1e-36)
+    A[3] *= np.float32(1e37)
+    A[4] *= np.float32(3e38) / np.abs(A[4]).max()
+    A[5] *= np.float32(1e-33)
+    A[6] = np.abs(A[6]) * np.float32(2e-39)
+    bits = f32_to_bf16_bits(A)
+    a_dev = from_bits16(bits, torch.bfloat16)
+    q_o, s_o, z_o = oracle.quantize_a_per_row_asym(bits, TD_BF16)
+    q = torch.full((m, k), 77, dtype=torch.int8, device=DEV)
+    s = torch.zeros(m, dtype=torch.float32, device=DEV)
+    z = torch.zeros(m, dtype=torch.int32, device=DEV)
+    p.quant_qai8dx(a_dev, q, s, z)
+    sync_and_check()
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), s_o.view(np.uint32))
+    assert np.array_equal(z.cpu().numpy(), z_o)
+    assert np.array_equal(q.cpu().numpy(), q_o)

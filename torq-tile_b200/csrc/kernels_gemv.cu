@@ -636,6 +636,17 @@ static Result launch_gemv_mma(GemvArgs a, cudaStream_t st)
         return e ? std::atoi(e) : 0;
     }();
     a.exp_flags = exp_flags;
+    static const int carve = [] {
+        const char *e = std::getenv("TQT_B200_GEMV_CARVEOUT");
+        return e ? std::atoi(e) : -1;
+    }();
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (carve >= 0 && dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaFuncSetAttribute(gemv_mma_kernel<G, R16, TD>, cudaFuncAttributePreferredSharedMemoryCarveout, carve);
+        attr_set[dev] = true;
+    }
     const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows, sets = (groups + G - 1) / G;
     const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_mma_min_ctas<G>();
     cudaLaunchConfig_t cfg = {};

@@ -182,55 +182,95 @@ Result launch_unpack_rows(void *stream, size_t rows, size_t k, size_t ld_packed,
 }
 
 // ---- int4 blocks -----------------------------------------------------------------------------------
-// One CTA of 128 threads per (row-tile, k-block); thread r owns row r of the block: it reads the 64
-// source bytes of its row, re-orders the nibbles and (qsi4cx) adds up the row's partial sum.
+// One CTA of 128 threads per (row-tile, k-block).  The 128 x 64-byte source tile is read with row-contiguous
+// 128-bit loads (four threads per row: every 32-byte sector is fetched whole, once) into shared memory, at a
+// swizzled position so that the per-row reads that follow are conflict-free; thread r then owns row r of the
+// block: it re-orders the nibbles of its 64 bytes, (qsi4cx) adds up the row's partial sum, and writes its four
+// 16-byte segments, which makes the CTA's output one contiguous 8 KiB (+ 256 B of sums) stream.  Sources whose
+// rows are not 16-byte aligned, and the ragged right / bottom edges, take byte loads.
 template <bool C2>
-__global__ void pack_i4_kernel(size_t n, size_t k, size_t ld_src_bytes, size_t kblocks_total,
-                               const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, size_t kblocks)
+__global__ void __launch_bounds__(128) pack_i4_kernel(size_t n, size_t k, size_t ld_src_bytes, size_t kblocks_total,
+                                                      const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, size_t kblocks,
+                                                      int aligned)
 {
     constexpr size_t BLOCK_BYTES = C2 ? kI4C2BlockBytes : kI4CxBlockBytes;
+    __shared__ uint4 sTile[128 * 4];
     const size_t blk = blockIdx.x;
     const size_t kb = blk % kblocks, tile = blk / kblocks;
     const uint32_t r = threadIdx.x;
-    const size_t row = tile * 128 + r;
     uint8_t *base = dst + (tile * kblocks_total + kb) * BLOCK_BYTES;
-
-    // gather the 128 signed values of this row / k-block (0 for padding)
-    uint8_t raw[64];
     const size_t kbyte0 = kb * 64;
     const size_t kbytes = k / 2;
+
+    // stage: chunk c = (row c / 4, 16-byte segment c % 4); consecutive threads take consecutive chunks
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-        const size_t kbyte = kbyte0 + i;
-        raw[i] = (row < n && kbyte < kbytes) ? src[row * ld_src_bytes + kbyte] : (uint8_t)0x88;  // nib 8 == value 0
-    }
-    uint32_t out[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i) out[i] = 0;
-    int psum = 0;
-#pragma unroll
-    for (uint32_t kk = 0; kk < 128; ++kk) {
-        const uint32_t nib = (raw[kk >> 1] >> ((kk & 1) * 4)) & 0xFu;  // stored value = q + 8
-        psum += (int)nib - 8;
-        uint32_t hi;
-        // position inside this thread's 64-byte row, without the per-row segment swizzle
-        uint32_t byte;
-        uint32_t val;
-        if (C2) {
-            byte = i4c2_byte(0, kk, &hi);  // row 0: swizzle term is zero
-            val = nib;                     // unsigned, as stored
-        } else {
-            byte = i4cx_byte(0, kk, &hi);
-            val = nib ^ 8u;                // two's complement nibble of q
+    for (uint32_t u = 0; u < 4; ++u) {
+        const uint32_t c = r + u * 128u, lr = c >> 2, seg = c & 3u;
+        const size_t row = tile * 128 + lr, kbyte = kbyte0 + seg * 16u;
+        uint4 v = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);   // nibble 8 == value 0 (padding)
+        if (row < n && kbyte < kbytes) {
+            const uint8_t *p = src + row * ld_src_bytes + kbyte;
+            if (aligned && kbyte + 16 <= kbytes) {
+                v = __ldg(reinterpret_cast<const uint4 *>(p));
+            } else {
+                uint32_t w[4] = {0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u};
+                for (uint32_t b = 0; b < 16 && kbyte + b < kbytes; ++b)
+                    w[b >> 2] = (w[b >> 2] & ~(0xFFu << ((b & 3u) * 8u))) | ((uint32_t)p[b] << ((b & 3u) * 8u));
+                v = make_uint4(w[0], w[1], w[2], w[3]);
+            }
         }
-        out[byte >> 2] |= val << (((byte & 3u) * 8u) + hi * 4u);
+        sTile[lr * 4u + (seg ^ ((lr >> 1) & 3u))] = v;
+    }
+    __syncthreads();
+
+    // this thread's row: 64 source bytes = 128 stored nibbles (value q + 8), k ascending
+    uint32_t raw[16];
+#pragma unroll
+    for (uint32_t sg = 0; sg < 4; ++sg) {
+        const uint4 v = sTile[r * 4u + (sg ^ ((r >> 1) & 3u))];
+        raw[sg * 4 + 0] = v.x;
+        raw[sg * 4 + 1] = v.y;
+        raw[sg * 4 + 2] = v.z;
+        raw[sg * 4 + 3] = v.w;
+    }
+    // Re-order whole words.  Source word w of a 32-k segment holds the stored nibbles (value q + 8) of k = 8 w ..
+    // 8 w + 7, nibble i at bits 4 i.
+    //   qsi4cx: output word j, byte b = q[4 j + b] | q[16 + 4 j + b] << 4 in two's complement: the four nibbles of
+    //           a 16-bit half of a source word are spread over the low nibbles of four bytes.
+    //   qsi4c2: output word j holds k = 8 j .. 8 j + 7 as (k0, k2, k4, k6, k1, k3, k5, k7), unsigned as stored: the
+    //           even nibbles of source word j compressed into the low half, the odd ones into the high half.
+    uint32_t out[16];
+    int psum = -8 * 128;
+    auto spread = [](uint32_t h) {   // nibbles n0..n3 of a 16-bit value -> bytes 0x0n3 0x0n2 0x0n1 0x0n0
+        const uint32_t t = (h | (h << 8)) & 0x00FF00FFu;
+        return (t | (t << 4)) & 0x0F0F0F0Fu;
+    };
+    auto even_nibbles = [](uint32_t w) {   // nibbles 0, 2, 4, 6 -> the low 16 bits
+        uint32_t x = w & 0x0F0F0F0Fu;
+        x = (x | (x >> 4)) & 0x00FF00FFu;
+        return (x | (x >> 8)) & 0x0000FFFFu;
+    };
+#pragma unroll
+    for (uint32_t sg = 0; sg < 4; ++sg) {
+        const uint32_t *w = raw + sg * 4;
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            psum += __dp4a((int)((w[j] & 0x0F0F0F0Fu) + ((w[j] >> 4) & 0x0F0F0F0Fu)), 0x01010101, 0);
+            if (C2) {
+                out[sg * 4 + j] = even_nibbles(w[j]) | (even_nibbles(w[j] >> 4) << 16);
+            } else {
+                const uint32_t lo = (w[j >> 1] >> (16u * (j & 1u))) & 0xFFFFu;        // k = 4 j .. 4 j + 3
+                const uint32_t hi = (w[2 + (j >> 1)] >> (16u * (j & 1u))) & 0xFFFFu;  // k = 16 + 4 j .. + 3
+                out[sg * 4 + j] = (spread(lo) | (spread(hi) << 4)) ^ 0x88888888u;
+            }
+        }
     }
     // write the four 16-byte segments at their swizzled positions
 #pragma unroll
-    for (uint32_t s = 0; s < 4; ++s) {
-        const uint32_t pos = s ^ ((r >> 1) & 3u);
+    for (uint32_t sg = 0; sg < 4; ++sg) {
+        const uint32_t pos = sg ^ ((r >> 1) & 3u);
         *reinterpret_cast<uint4 *>(base + r * 64u + pos * 16u) =
-            make_uint4(out[s * 4 + 0], out[s * 4 + 1], out[s * 4 + 2], out[s * 4 + 3]);
+            make_uint4(out[sg * 4 + 0], out[sg * 4 + 1], out[sg * 4 + 2], out[sg * 4 + 3]);
     }
     if (!C2) reinterpret_cast<int16_t *>(base + kI4NibBytes)[r] = (int16_t)psum;
 }
@@ -267,12 +307,14 @@ Result launch_pack_i4(void *stream, size_t n, size_t k, size_t ld_src_bytes, siz
     const size_t blocks = ceil_div(n, 128) * kblocks;
     if (blocks > 0x7fffffffull) return Result{kUnsupported, 0};
     cudaStream_t st = (cudaStream_t)stream;
+    // 128-bit source loads need 16-byte aligned rows (k blocks start at multiples of 64 bytes)
+    const int aligned = ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (ld_src_bytes & 15) == 0) ? 1 : 0;
     if (c2)
         pack_i4_kernel<true><<<(unsigned)blocks, 128, 0, st>>>(n, k, ld_src_bytes, kblocks_total, (const uint8_t *)src,
-                                                             (uint8_t *)dst, kblocks);
+                                                             (uint8_t *)dst, kblocks, aligned);
     else
         pack_i4_kernel<false><<<(unsigned)blocks, 128, 0, st>>>(n, k, ld_src_bytes, kblocks_total, (const uint8_t *)src,
-                                                              (uint8_t *)dst, kblocks);
+                                                              (uint8_t *)dst, kblocks, aligned);
     return check_launch();
 }
 
@@ -537,6 +579,10 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
         zp_a[row] = zp;
     }
     const float y = s != 0.0f ? __frcp_rn(s) : 0.0f;
+    // The reciprocal route needs 1/s and the intermediate products to stay normal: rows whose scale is extreme
+    // (a bf16 row has the f32 exponent range; below about 2.9e-39 the reciprocal overflows) divide instead.
+    // Uniform per row, so per warp.
+    const bool plain_div = !(s > 7.8886091e-31f && s < 1.2676506e30f);   // outside [2^-100, 2^100]
     const size_t tile = row >> 7;
     const uint32_t r = (uint32_t)(row & 127);
     const uint32_t out_chunks = PACKED ? (uint32_t)((k + 127) / 128) * 8u : nchunks;   // packed rows are zero-padded to the block width
@@ -556,9 +602,14 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
                     widen(w[j], x2[0], x2[1]);
 #pragma unroll
                     for (uint32_t e2 = 0; e2 < 2; ++e2) {
-                        const float q0 = __fmul_rn(x2[e2], y);
-                        const float err = __fmaf_rn(-q0, s, x2[e2]);
-                        const float q = __fmaf_rn(err, y, q0);
+                        float q;
+                        if (plain_div) {
+                            q = __fdiv_rn(x2[e2], s);
+                        } else {
+                            const float q0 = __fmul_rn(x2[e2], y);
+                            const float err = __fmaf_rn(-q0, s, x2[e2]);
+                            q = __fmaf_rn(err, y, q0);
+                        }
                         v[j * 2 + e2] = __float2int_rn(q) + zp;
                     }
                 }

@@ -172,8 +172,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
             const uint32_t d_tmem = tmem_base + acc * 256u;
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, true)) ||
-                    !TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kPeerFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, true))) {
+                if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull)) ||
+                    !TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kPeerFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull))) {
                     ok = false;
                     break;
                 }
@@ -197,7 +197,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs) {
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, true))) {
+                if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull))) {
                     ok = false;
                     break;
                 }
@@ -394,6 +394,11 @@ struct TsCfg {
     static constexpr uint32_t kSmem = kUsed > 120u * 1024u ? kUsed : 120u * 1024u;
 };
 
+// Waits: every mbarrier a thread waits on lives in its own CTA's shared memory, also those that the peer CTA
+// arrives on (relaxed remote arrives) or that a multicast tcgen05.commit completes, so the waits use the
+// CTA-scope try_wait: the cluster-scope acquire form costs about 200 cycles per call even on a completed phase,
+// which the MMA issuer paid twice per group of eight MMAs.  What the barriers order is tensor-memory traffic, and
+// that is fenced by tcgen05.wait::st / tcgen05.fence on both sides, not by the barrier's memory scope.
 // A K step is 128 int8 (W4A8) or 64 f16 (W4A16): 128 bytes per activation row and 32 tensor-memory
 // columns per weight row either way.  Steps are handled in groups of two: one tcgen05.commit per group
 // releases two shared-memory stages and two tensor-memory operand stages (a commit after MMAs that
@@ -441,7 +446,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; ++s) ptx::mbar_init(BAR(kFull + s), 1);
         for (uint32_t g = 0; g < NG; ++g) ptx::mbar_init(BAR(kGroupDone + g), 1);
-        for (uint32_t s = 0; s < T; ++s) ptx::mbar_init(BAR(kConvFull + s), PAIR ? 8 : 4);   // 4 converter warps per CTA
+        for (uint32_t s = 0; s < 2; ++s) ptx::mbar_init(BAR(kConvFull + s), PAIR ? 16 : 8);   // per group slot: 8 converter warps per CTA
         for (uint32_t e = 0; e < 2; ++e) {
             ptx::mbar_init(BAR(kTmemFull + e), 1);
             ptx::mbar_init(BAR(kTmemEmpty + e), PAIR ? 16 : 8);
@@ -472,6 +477,14 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
     if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     long long wcyc[3] = {0, 0, 0};
     const long long t_role0 = args.dbg ? clock64() : 0;
+    // how long a waiting thread may stay suspended in hardware before it polls again: the waits on the critical
+    // loop (issuer <-> converters) poll often, the others sleep long
+    // diagnostic: with inject bit 6 the timing buffer of pair 0's leader CTA receives a per-step timeline instead
+    // (2048 int64: [0,512) issuer, [512,1024) converter warp 10, [1024,1536) converter warp 14, [1536,2048) epilogue warp 2)
+    long long *trace = (args.dbg && (args.inject & 64u) && blockIdx.x == 0) ? args.dbg : nullptr;
+    long long *trace_peer = (args.dbg && (args.inject & 64u) && blockIdx.x == 1) ? args.dbg + 1536 : nullptr;   // peer CTA: converter warp 12
+    const uint32_t hint_mma = (args.inject & 16u) ? 0u : ptx::kTryWaitSuspendNs;
+    const uint32_t hint_conv = (args.inject & 32u) ? 0u : ptx::kTryWaitSuspendNs;
     bool conv_failed = false;   // a converter warp whose waits ran out does not help with the epilogue
 
     if (warp == 0 || warp == 18) {
@@ -499,7 +512,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             const uint32_t act_tx = (v1 ? rows1 * 128u : 0u) + (v2 ? rows2 * 128u : 0u);
             for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc) {
                 const uint32_t gs = Gc % NG;
-                if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kGroupDone + gs), ((Gc / NG) & 1u) ^ 1u, sAbort, args.fault,
+                if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kGroupDone + gs), ((Gc / NG) & 1u) ^ 1u, sAbort, args.fault,
                                                           kFaultProducerWait))) {
                     ok = false;
                     break;
@@ -559,64 +572,68 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             }
         }
     } else if (warp == 1) {
-        // ===================== MMA issuer (leader CTA only; the peer's warp 1 idles) =====================
-        if (rank == 0) {
+        // ===================== MMA issuer (one thread of the leader CTA; the rest of the warp idles) ==========
+        // The issuing thread is the bottleneck of the mainloop, not the tensor pipe: a group of eight MMAs occupies
+        // the pipe for ~820 cycles (M256 x N192 x K32: 102.5 each), and the thread has to wait, fence, issue and
+        // commit inside that time.  Measured on this loop: each wait-plus-fence costs ~200-300 cycles even on a
+        // barrier that completed long ago, four MMA issues ~320, a commit ~160.  So the loop does one wait per
+        // GROUP (both steps' converters arrive on one barrier), issues the eight MMAs back to back from
+        // precomputed descriptors, and nothing else; one thread runs it, so no warp-wide reconvergence either.
+        if (rank == 0 && lane == 0) {
             const uint32_t idesc = kF16 ? ptx::make_idesc(1u, 0u, 0u, PAIR ? 256 : 128, mt)
                                         : ptx::make_idesc(2u, 1u, 1u, PAIR ? 256 : 128, mt);
+            const uint64_t desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sAct));
+            const uint32_t desc0_lo = (uint32_t)desc0, desc0_hi = (uint32_t)(desc0 >> 32);
+            constexpr uint32_t kDescStage = kActBytes >> 4;   // descriptor address field counts 16-byte units
             uint32_t Gc = 0, ti = 0;
             bool ok = true;
             for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
                 const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
-                if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
+                if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
                     ok = false;
                     break;
                 }
-                ptx::tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * mt;
-                for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc) {
-                    const uint32_t gs = Gc % NG;
-                    for (uint32_t h = 0; h < 2; ++h) {
-                        const uint32_t s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
-                        const bool step_valid = g * 2 + h < ksteps;
-                        // all converter warps have written their rows of operand stage ts (which also means the
-                        // activation rows of shared-memory stage s have landed, in both CTAs of a pair)
-                        if (!TQT_PTIMED(1, ptx::mbar_wait_cluster(BAR(kConvFull + ts), (Gc >> 1) & 1u, sAbort, args.fault,
-                                                                  kFaultMmaWaitFull, true))) {
-                            ok = false;
-                            break;
-                        }
-                        ptx::tc_fence_after();
-                        if (lane == 0 && step_valid) {
-                            const uint64_t b_desc = ptx::make_desc_k_sw128(ptx::smem_u32(sAct + s * kActBytes));
-#pragma unroll
-                            for (uint32_t j = 0; j < 4; ++j) {
-                                const uint32_t accum = (g | h | j) ? 1u : 0u;
-                                const uint32_t a_t = tmem_a + ts * 32u + j * 8u;
-                                if constexpr (kF16) {
-                                    if constexpr (PAIR) ptx::mma_f16_ts_pair(d_tmem, a_t, b_desc + 2 * j, idesc, accum);
-                                    else ptx::mma_f16_ts(d_tmem, a_t, b_desc + 2 * j, idesc, accum);
-                                } else {
-                                    if constexpr (PAIR) ptx::mma_i8_ts_pair(d_tmem, a_t, b_desc + 2 * j, idesc, accum);
-                                    else ptx::mma_i8_ts(d_tmem, a_t, b_desc + 2 * j, idesc, accum);
-                                }
-                            }
-                        }
-                        __syncwarp();
+                for (uint32_t g = 0; g < ngroups; ++g, ++Gc) {
+                    const uint32_t gs = Gc % NG, slot = Gc & 1u;
+                    const bool tr = trace && Gc < 64u;   // diagnostic trace: first 64 groups of pair 0
+                    if (tr) trace[Gc * 8 + 0] = clock64();
+                    // all converter warps of both steps have written operand stages 2 slot, 2 slot + 1 (which also
+                    // means the activation rows of the two shared-memory stages have landed, in both CTAs of a pair)
+                    if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kConvFull + slot), (Gc >> 1) & 1u, sAbort, args.fault, kFaultMmaWaitFull,
+                                                      hint_mma))) {
+                        ok = false;
+                        break;
                     }
-                    if (!ok) break;
-                    if (lane == 0) {
-                        if constexpr (PAIR) {
-                            ptx::tc_commit_pair(BAR(kGroupDone + gs), 3);
-                            if (g == ngroups - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
-                        } else {
-                            ptx::tc_commit(BAR(kGroupDone + gs));
-                            if (g == ngroups - 1) ptx::tc_commit(BAR(kTmemFull + acc));
-                        }
+                    if (tr) {
+                        trace[Gc * 8 + 4] = clock64();
+                        ptx::mbar_wait(BAR(kConvFull + slot), (Gc >> 1) & 1u, sAbort, args.fault, kFaultMmaWaitFull, hint_mma);   // a completed phase: the floor
+                        trace[Gc * 8 + 5] = clock64();
                     }
-                    __syncwarp();
+                    ptx::tc_fence_after();
+                    if (tr) trace[Gc * 8 + 1] = clock64();
+                    const uint32_t two = (ksteps - g * 2u) >= 2u ? 1u : 0u;
+                    const uint32_t dlo = desc0_lo + gs * 2u * kDescStage, a_t = tmem_a + slot * 64u;
+                    if constexpr (kF16) {
+                        if constexpr (PAIR) ptx::mma_f16_ts_pair_group8(d_tmem, a_t, dlo, desc0_hi, kDescStage, idesc, g, two);
+                        else ptx::mma_f16_ts_group8(d_tmem, a_t, dlo, desc0_hi, kDescStage, idesc, g, two);
+                    } else {
+                        if constexpr (PAIR) ptx::mma_i8_ts_pair_group8(d_tmem, a_t, dlo, desc0_hi, kDescStage, idesc, g, two);
+                        else ptx::mma_i8_ts_group8(d_tmem, a_t, dlo, desc0_hi, kDescStage, idesc, g, two);
+                    }
+                    if (tr) trace[Gc * 8 + 2] = clock64();
+                    if constexpr (PAIR) {
+                        ptx::tc_commit_pair(BAR(kGroupDone + gs), 3);
+                        if (g == ngroups - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
+                    } else {
+                        ptx::tc_commit(BAR(kGroupDone + gs));
+                        if (g == ngroups - 1) ptx::tc_commit(BAR(kTmemFull + acc));
+                    }
+                    if (tr) trace[Gc * 8 + 3] = clock64();
                 }
             }
         }
+        __syncwarp();
     } else if (warp >= 10) {
         // ===================== converters (warps 10..17): int4 -> MMA operand type, into tensor memory ========
         // Two warps per tensor-memory lane quadrant: set 0 (warps 10..13) takes step 0 of every group, set 1
@@ -627,21 +644,21 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
         const uint32_t quad = warp & 3u, cset = (warp - 10u) >> 2;
         const uint32_t row = quad * 32u + lane;
         const uint32_t swz_in = (row >> 1) & 3u;
-        const uint32_t conv_full_leader = PAIR ? ptx::mapa(BAR(kConvFull), 0) : 0u;   // + 8 * ts
+        const uint32_t conv_full_leader = PAIR ? ptx::mapa(BAR(kConvFull), 0) : 0u;   // + 8 * group slot
         const bool word_scale = kF16 && (args.bl & 7u) == 0u;   // W4A16: one scale per 8-k word (bl a multiple of 8)
         const int bl_shift = (kF16 && args.bl && (args.bl & (args.bl - 1u)) == 0u) ? (int)__ffs((int)args.bl) - 1 : -1;
         // the last window of a row may read up to 7 entries past the row's k / bl scales: only when that stays
         // inside the row stride (ldsb a multiple of 8 covers it) and the base is 16-byte aligned
         const bool sc_vec = kF16 && bl_shift >= 3 && (args.ldsb & 7u) == 0u && (reinterpret_cast<uintptr_t>(args.scale_blk) & 15u) == 0u;
-        auto announce = [&](uint32_t ts) {
+        auto announce = [&](uint32_t ts) {   // ts = operand stage; its group slot's barrier counts both steps
             ptx::tmem_wait_st();
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) {
                 if (rank == 0)
-                    ptx::mbar_arrive(BAR(kConvFull + ts));
+                    ptx::mbar_arrive(BAR(kConvFull + (ts >> 1)));
                 else
-                    ptx::mbar_arrive_cluster(conv_full_leader + ts * 8u);
+                    ptx::mbar_arrive_cluster(conv_full_leader + (ts >> 1) * 8u);
             }
         };
         uint32_t Gc = 0, ti = 0;
@@ -692,6 +709,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 const uint32_t h = cset, gs = Gc % NG, s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
                 const uint32_t phs = (Gc / NG) & 1u;
                 const bool step_valid = g * 2 + h < ksteps;
+                long long *ctr = (trace && lane == 0 && quad == 2 && Gc < 64u) ? trace + 512 + cset * 512 + Gc * 4 : nullptr;
+                if (trace_peer && lane == 0 && quad == 2 && cset == 0 && Gc < 64u) ctr = trace_peer + Gc * 4;
+                if (ctr) ctr[0] = clock64();
                 // W4A16: the block scales of a step (one per 8-k word) do not depend on the barriers; they were
                 // requested during the previous step of this warp (or are requested here, for a tile's first step)
                 __half sc8[8];
@@ -711,7 +731,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                     // before is done: otherwise two announcements could fall into one phase of the barrier
                     if (Gc >= 2u) {
                         const uint32_t Gp = Gc - 2u;
-                        if (!TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
+                        if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
                                                                   kFaultConverterWait))) {
                             ok = false;
                             break;
@@ -720,9 +740,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                     __syncwarp();
                     if (lane == 0) {
                         if (rank == 0)
-                            ptx::mbar_arrive(BAR(kConvFull + ts));
+                            ptx::mbar_arrive(BAR(kConvFull + (ts >> 1)));
                         else
-                            ptx::mbar_arrive_cluster(conv_full_leader + ts * 8u);
+                            ptx::mbar_arrive_cluster(conv_full_leader + (ts >> 1) * 8u);
                     }
                     continue;
                 }
@@ -788,18 +808,21 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                         }
                     }
                 }
+                if (ctr) ctr[1] = clock64();
                 // the MMAs of the group two groups back read this tensor-memory stage: they must be done
                 if (Gc >= 2u) {
                     const uint32_t Gp = Gc - 2u;
-                    if (!TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
-                                                              kFaultConverterWait))) {
+                    if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
+                                                              kFaultConverterWait, hint_conv))) {
                         ok = false;
                         break;
                     }
                 }
                 __syncwarp();
+                if (ctr) ctr[2] = clock64();
                 ptx::tmem_st_32x32b_x32(tmem_a + ts * 32u + ((quad * 32u) << 16), regs);
                 announce(ts);
+                if (ctr) ctr[3] = clock64();
             }
             if (!ok) break;
             if constexpr (!kF16) {
@@ -846,8 +869,8 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             float sb = 0.0f;
             if constexpr (!kF16) sb = n_ok ? args.scale_b[n] : 0.0f;
             const float bv = (n_ok && args.bias) ? TdTraits<TD>::load(args.bias, n) : 0.0f;
-            if (!(helper ? ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)
-                         : TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)))) {
+            if (!(helper ? ptx::mbar_wait(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)
+                         : TQT_PTIMED(0, ptx::mbar_wait(BAR(kTmemFull + acc), pha, sAbort, args.fault, kFaultEpilogueWait)))) {
                 ok = false;
                 break;
             }
@@ -875,26 +898,33 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                     sa_l = lane < nvalid ? __ldg(args.scale_a + m0 + c0 + lane) : 0.0f;
                     zp_l = lane < nvalid ? __ldg(args.zp_a + m0 + c0 + lane) : 0;
                 }
-                uint32_t r[32];
                 __syncwarp();
-                const long long tl0 = args.dbg ? clock64() : 0;
-                ptx::tmem_ld_32x32b_x32(t_addr + c0, r);
-                ptx::tmem_wait_ld();
-                if (args.dbg) wcyc[2] += clock64() - tl0;
                 OutT *dcol = static_cast<OutT *>(args.D) + (size_t)(m0 + c0) * args.ldd + n;
-                {
+                // Eight columns at a time in a rolled loop: the strip's code is a quarter of the fully unrolled
+                // form.  The kernel's warps share one instruction cache, and the MMA issuer, whose instruction
+                // stream is the bottleneck of the mainloop, slowed down whenever the epilogue's code grew.
+                // timing experiment (output incomplete): the warps of the lane quadrants named by inject bits 8..11 skip their work
+                if ((args.inject >> 8) & (1u << quad) & 0xFu) continue;
+#pragma unroll 1
+                for (uint32_t q8 = 0; q8 < 32u && q8 < nvalid; q8 += 8u) {
+                    uint32_t r[8];
+                    const long long tl0 = args.dbg ? clock64() : 0;
+                    ptx::tmem_ld_32x32b_x8(t_addr + c0 + q8, r);
+                    ptx::tmem_wait_ld();
+                    if (args.dbg) wcyc[2] += clock64() - tl0;
                     constexpr bool kRepl = replicate;
 #pragma unroll
-                    for (uint32_t j = 0; j < 32; ++j) {
+                    for (uint32_t jj = 0; jj < 8; ++jj) {
+                        const uint32_t j = q8 + jj;
                         float v;
                         if constexpr (!kF16) {
                             const float sa = __shfl_sync(0xffffffffu, sa_l, j);
                             const int32_t zp = __shfl_sync(0xffffffffu, zp_l, j);
                             // operands were 16*q: the accumulator is an exact multiple of 16
-                            const int32_t a = (((int32_t)r[j]) >> 4) - zp * rs;
+                            const int32_t a = (((int32_t)r[jj]) >> 4) - zp * rs;
                             v = __fmul_rn(__fmul_rn(__int2float_rn(a), sa), sb);
                         } else {
-                            v = __uint_as_float(r[j]);
+                            v = __uint_as_float(r[jj]);
                         }
                         // branch-free per element: selects and a predicated load / store instead of three branches
                         const bool live = n_ok && j < nvalid;
@@ -927,7 +957,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
         }
     }
 
-    if (args.dbg && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 10)) {
+    if (args.dbg && !(args.inject & 64u) && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 10)) {
         long long *d = args.dbg + (size_t)blockIdx.x * 16 + (warp == 0 ? 0 : warp == 1 ? 4 : warp == 2 ? 8 : 12);
         d[0] = wcyc[0];
         d[1] = wcyc[1];

@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
             const uint32_t d_tmem = tmem_base + acc * 256u;
             for (uint32_t kb = 0; kb < KB && ok; ++kb, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!TQT_TIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, true))) {
+                if (!TQT_TIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull))) {
                     ok = false;
                     break;
                 }
@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
                     if (kConv) {
                         e = xit % 2u;
                         const uint32_t phe = (xit / 2u) & 1u;
-                        if (!TQT_TIMED(2, ptx::mbar_wait(BAR(kConvFull + e), phe, sAbort, args.fault, kFaultMmaWaitFull, true))) {
+                        if (!TQT_TIMED(2, ptx::mbar_wait(BAR(kConvFull + e), phe, sAbort, args.fault, kFaultMmaWaitFull))) {
                             ok = false;
                             break;
                         }

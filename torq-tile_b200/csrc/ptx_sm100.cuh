@@ -35,7 +35,7 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 // passed, so that waiting warps do not compete for issue slots with the warps that do the work.
 constexpr uint32_t kTryWaitSuspendNs = 20000;
 
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity, uint32_t hint_ns = kTryWaitSuspendNs)
 {
     uint32_t ok;
     asm volatile(
@@ -45,12 +45,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(kTryWaitSuspendNs)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
 
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity)
+// Non-blocking test of a phase: cheaper than try_wait, which may suspend the thread.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity, uint32_t hint_ns = kTryWaitSuspendNs)
 {
     uint32_t ok;
     asm volatile(
@@ -60,7 +76,7 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(kTryWaitSuspendNs)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
         : "memory");
     return ok != 0;
 }
@@ -71,18 +87,22 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 constexpr long long kWaitLimitCycles = 2000000000ll;
 __device__ __forceinline__ long long wait_limit(volatile int *abort_flag) { return kWaitLimitCycles >> (abort_flag[1] & 31); }
 
-// Bounded wait.  Every polling thread spins on try_wait (which itself suspends the thread for a
-// hardware-defined interval); sleeping between polls was measured to cost throughput, because the
-// pipelines are latency-sensitive.  `spin` is accepted for call-site documentation only.
+// Bounded wait.  Every polling thread spins on try_wait, which itself suspends the thread in hardware for up to
+// hint_ns nanoseconds (sleeping between polls in software was measured to cost throughput, because the pipelines
+// are latency-sensitive).
 template <bool CLUSTER>
 __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                               unsigned int *fault, unsigned int code, bool /*spin*/)
+                                               unsigned int *fault, unsigned int code, uint32_t hint_ns)
 {
-    if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+    if (!CLUSTER && hint_ns == 0u) {
+        if (mbar_test_wait(bar, parity)) return true;   // the common case on the critical loops: already complete
+    } else if (CLUSTER ? mbar_try_wait_cluster(bar, parity, hint_ns) : mbar_try_wait(bar, parity, hint_ns)) {
+        return true;
+    }
     const long long t0 = clock64();
     unsigned int spins = 0;
     for (;;) {
-        if (CLUSTER ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        if (CLUSTER ? mbar_try_wait_cluster(bar, parity, hint_ns) : mbar_try_wait(bar, parity, hint_ns)) return true;
         if ((++spins & 31u) == 0u) {
             if (*abort_flag) return false;
             if (clock64() - t0 > wait_limit(abort_flag)) {
@@ -95,9 +115,9 @@ __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, vo
 }
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          unsigned int *fault, unsigned int code, bool spin = false)
+                                          unsigned int *fault, unsigned int code, uint32_t hint_ns = kTryWaitSuspendNs)
 {
-    return mbar_wait_impl<false>(bar, parity, abort_flag, fault, code, spin);
+    return mbar_wait_impl<false>(bar, parity, abort_flag, fault, code, hint_ns);
 }
 
 // ---- async proxy ------------------------------------------------------------------------------------
@@ -165,6 +185,15 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+
+// 32 lanes x 8 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 
 // ---- tcgen05.mma -------------------------------------------------------------------------------------
@@ -268,9 +297,9 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
 }
 // bounded wait with cluster-scope acquire (the arrivals may come from the peer CTA)
 __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                                  unsigned int *fault, unsigned int code, bool spin = false)
+                                                  unsigned int *fault, unsigned int code, uint32_t hint_ns = kTryWaitSuspendNs)
 {
-    return mbar_wait_impl<true>(bar, parity, abort_flag, fault, code, spin);
+    return mbar_wait_impl<true>(bar, parity, abort_flag, fault, code, hint_ns);
 }
 // Hardware cluster barrier: every thread of both CTAs arrives; cannot be bounded, so it is only
 // used where all paths provably reach it (kernel prologue and teardown).
@@ -343,6 +372,51 @@ __device__ __forceinline__ void mma_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem
         : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+
+// A group of eight TS MMAs (two K steps of four K slices) in one instruction block, to keep the issuing
+// thread's instruction count per MMA at its minimum (the thread is the bottleneck of the mainloop).  MMA q = 4 h + j
+// takes its M-side operand at a_tmem + 8 q, its N-side descriptor at desc + h * stage16 + 2 j (only the low word of
+// the descriptor changes: the address field counts 16-byte units), accumulates unless it is the very first of a tile
+// (accum_first = 0).  two_steps = 0 issues the first four only.
+#define TQT_MMA_TS_GROUP8(NAME, KINDSTR)                                                                                  \
+    __device__ __forceinline__ void NAME(uint32_t d_tmem, uint32_t a_tmem, uint32_t desc_lo, uint32_t desc_hi,            \
+                                         uint32_t stage16, uint32_t idesc, uint32_t accum_first, uint32_t two_steps)     \
+    {                                                                                                                     \
+        asm volatile(                                                                                                     \
+            "{\n\t"                                                                                                       \
+            ".reg .pred p, pt, q;\n\t"                                                                                    \
+            ".reg .b32 lo, at, lo1;\n\t"                                                                                  \
+            ".reg .b64 d;\n\t"                                                                                            \
+            "setp.ne.b32 p, %6, 0;\n\t"                                                                                   \
+            "setp.eq.b32 pt, 0, 0;\n\t"                                                                                   \
+            "setp.ne.b32 q, %7, 0;\n\t"                                                                                   \
+            "mov.b64 d, {%2, %3};\n\t"                                                                                    \
+            "tcgen05.mma." KINDSTR " [%0], [%1], d, %5, p;\n\t"                                                           \
+            "add.u32 lo, %2, 2;\n\t add.u32 at, %1, 8;\n\t mov.b64 d, {lo, %3};\n\t"                                      \
+            "tcgen05.mma." KINDSTR " [%0], [at], d, %5, pt;\n\t"                                                          \
+            "add.u32 lo, %2, 4;\n\t add.u32 at, %1, 16;\n\t mov.b64 d, {lo, %3};\n\t"                                     \
+            "tcgen05.mma." KINDSTR " [%0], [at], d, %5, pt;\n\t"                                                          \
+            "add.u32 lo, %2, 6;\n\t add.u32 at, %1, 24;\n\t mov.b64 d, {lo, %3};\n\t"                                     \
+            "tcgen05.mma." KINDSTR " [%0], [at], d, %5, pt;\n\t"                                                          \
+            "add.u32 lo1, %2, %4;\n\t add.u32 at, %1, 32;\n\t mov.b64 d, {lo1, %3};\n\t"                                  \
+            "@q tcgen05.mma." KINDSTR " [%0], [at], d, %5, pt;\n\t"                                                       \
+            "add.u32 lo, lo1, 2;\n\t add.u32 at, %1, 40;\n\t mov.b64 d, {lo, %3};\n\t"                                    \
+            "@q tcgen05.mma." KINDSTR " [%0], [at], d, %5, pt;\n\t"                                                       \
+            "add.u32 lo, lo1, 4;\n\t add.u32 at, %1, 48;\n\t mov.b64 d, {lo, %3};\n\t"                                    \
+            "@q tcgen05.mma." KINDSTR " [%0], [at], d, %5, pt;\n\t"                                                       \
+            "add.u32 lo, lo1, 6;\n\t add.u32 at, %1, 56;\n\t mov.b64 d, {lo, %3};\n\t"                                    \
+            "@q tcgen05.mma." KINDSTR " [%0], [at], d, %5, pt;\n\t"                                                       \
+            "}"                                                                                                           \
+            :                                                                                                             \
+            : "r"(d_tmem), "r"(a_tmem), "r"(desc_lo), "r"(desc_hi), "r"(stage16), "r"(idesc), "r"(accum_first),           \
+              "r"(two_steps)                                                                                              \
+            : "memory");                                                                                                  \
+    }
+TQT_MMA_TS_GROUP8(mma_i8_ts_group8, "cta_group::1.kind::i8")
+TQT_MMA_TS_GROUP8(mma_f16_ts_group8, "cta_group::1.kind::f16")
+TQT_MMA_TS_GROUP8(mma_i8_ts_pair_group8, "cta_group::2.kind::i8")
+TQT_MMA_TS_GROUP8(mma_f16_ts_pair_group8, "cta_group::2.kind::f16")
+#undef TQT_MMA_TS_GROUP8
 
 // 32 lanes x 32 consecutive 32-bit columns, registers -> tensor memory.
 __device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32])
