@@ -153,43 +153,52 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
             }
         }
     } else if (warp == 1 && rank == 0) {
-        // ===================== MMA issuer (leader CTA) =====================
-        const uint32_t idesc256 = ptx::make_idesc(2u, 1u, 1u, 256, 256);
-        const uint32_t idesc128 = ptx::make_idesc(2u, 1u, 1u, 256, 128);
-        uint32_t it = 0, ti = 0;
-        bool ok = true;
-        for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
-            uint32_t pm_unused, tn;
-            tile_coords(t, pmc, tnc, args.band_m, pm_unused, tn);
-            const uint32_t nblk = min(2u, nblocks - tn * 2);
-            const uint32_t idesc = nblk == 2 ? idesc256 : idesc128;
-            const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
-            if (!TQT_PTIMED(0, ptx::mbar_wait_cluster(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
-                ok = false;
-                break;
-            }
-            ptx::tc_fence_after();
-            const uint32_t d_tmem = tmem_base + acc * 256u;
-            for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
-                const uint32_t s = it % S, ph = (it / S) & 1u;
-                if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull)) ||
-                    !TQT_PTIMED(2, ptx::mbar_wait_cluster(BAR(kPeerFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull))) {
+        // ===================== MMA issuer (one thread of the leader CTA) =====================
+        // The issuing thread bounds this mainloop as it does the tensor-memory kernels' (a K step occupies the
+        // pipe for ~680 cycles; the thread needed ~1100 with two waits, a fence, four separate MMA issues and a
+        // commit per step): so one thread runs the loop, the four MMAs of a step go out in one instruction block
+        // from precomputed descriptor words, and whether the NEXT step's two barriers (own stage landed, peer's
+        // stage landed) have completed is tested after this step's MMAs and read after its commit, which takes the
+        // latency of the test (~200 cycles even on a long-completed phase) off the critical path.
+        if (lane == 0) {
+            const uint32_t idesc256 = ptx::make_idesc(2u, 1u, 1u, 256, 256);
+            const uint32_t idesc128 = ptx::make_idesc(2u, 1u, 1u, 256, 128);
+            const uint64_t a_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sA)), b_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sB));
+            const uint32_t a_lo0 = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
+            const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
+            uint32_t it = 0, ti = 0, s = 0, ph = 0;
+            bool ok = true, ready = false;
+            for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
+                uint32_t pm_unused, tn;
+                tile_coords(t, pmc, tnc, args.band_m, pm_unused, tn);
+                const uint32_t nblk = min(2u, nblocks - tn * 2);
+                const uint32_t idesc = nblk == 2 ? idesc256 : idesc128;
+                const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
+                if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
                     ok = false;
                     break;
                 }
-                ptx::tc_fence_after();
-                if (lane == 0) {
-                    const uint64_t a_desc = ptx::make_desc_k_sw128(ptx::smem_u32(sA + s * 16384));
-                    const uint64_t b_desc = ptx::make_desc_k_sw128(ptx::smem_u32(sB + s * 16384));
-#pragma unroll
-                    for (uint32_t j = 0; j < 4; ++j)
-                        ptx::mma_i8_ss_pair(d_tmem, a_desc + 2 * j, b_desc + 2 * j, idesc, (kb | j) ? 1u : 0u);
+                const uint32_t d_tmem = tmem_base + acc * 256u;
+                for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
+                    if (!ready && (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, 0u)) ||
+                                   !TQT_PTIMED(2, ptx::mbar_wait(BAR(kPeerFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, 0u)))) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    ptx::mma_i8_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);   // 16 KiB stages = 1024 units
+                    // the next step's stage (a phase seen complete stays complete until this thread commits it free again)
+                    const uint32_t s1 = s + 1u == S ? 0u : s + 1u, ph1 = s + 1u == S ? ph ^ 1u : ph;
+                    const bool next_ready = ptx::mbar_test_wait(BAR(kFull + s1), ph1) && ptx::mbar_test_wait(BAR(kPeerFull + s1), ph1);
                     ptx::tc_commit_pair(BAR(kEmpty + s), 3);
                     if (kb == KB - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
+                    ready = next_ready;
+                    s = s1;
+                    ph = ph1;
                 }
-                __syncwarp();
             }
         }
+        __syncwarp();
     } else if (warp == 1) {
         // ===================== relay (peer CTA): tells the leader that this CTA's stage has landed =====
         uint32_t it = 0;
@@ -585,8 +594,13 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
             const uint64_t desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sAct));
             const uint32_t desc0_lo = (uint32_t)desc0, desc0_hi = (uint32_t)(desc0 >> 32);
             constexpr uint32_t kDescStage = kActBytes >> 4;   // descriptor address field counts 16-byte units
-            uint32_t Gc = 0, ti = 0;
+            uint32_t Gc = 0, ti = 0, gs = 0;
             bool ok = true;
+            // Whether the next group's operands are ready is tested one group ahead: the test is issued after the
+            // current group's MMAs and its result read after the commit, so its latency (~150-250 cycles even on a phase
+            // that completed long ago) is off the issuing thread's critical path.  A phase seen complete stays
+            // complete: the converters can only arrive for it again after the MMAs that are about to be issued.
+            bool ready = false;
             for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
                 const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
                 if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
@@ -595,21 +609,17 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 }
                 const uint32_t d_tmem = tmem_base + acc * mt;
                 for (uint32_t g = 0; g < ngroups; ++g, ++Gc) {
-                    const uint32_t gs = Gc % NG, slot = Gc & 1u;
+                    const uint32_t slot = Gc & 1u;
                     const bool tr = trace && Gc < 64u;   // diagnostic trace: first 64 groups of pair 0
                     if (tr) trace[Gc * 8 + 0] = clock64();
                     // all converter warps of both steps have written operand stages 2 slot, 2 slot + 1 (which also
                     // means the activation rows of the two shared-memory stages have landed, in both CTAs of a pair)
-                    if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kConvFull + slot), (Gc >> 1) & 1u, sAbort, args.fault, kFaultMmaWaitFull,
-                                                      hint_mma))) {
+                    if (!ready && !TQT_PTIMED(1, ptx::mbar_wait(BAR(kConvFull + slot), (Gc >> 1) & 1u, sAbort, args.fault,
+                                                                kFaultMmaWaitFull, hint_mma))) {
                         ok = false;
                         break;
                     }
-                    if (tr) {
-                        trace[Gc * 8 + 4] = clock64();
-                        ptx::mbar_wait(BAR(kConvFull + slot), (Gc >> 1) & 1u, sAbort, args.fault, kFaultMmaWaitFull, hint_mma);   // a completed phase: the floor
-                        trace[Gc * 8 + 5] = clock64();
-                    }
+                    if (tr) trace[Gc * 8 + 4] = trace[Gc * 8 + 5] = clock64();
                     ptx::tc_fence_after();
                     if (tr) trace[Gc * 8 + 1] = clock64();
                     const uint32_t two = (ksteps - g * 2u) >= 2u ? 1u : 0u;
@@ -622,6 +632,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                         else ptx::mma_i8_ts_group8(d_tmem, a_t, dlo, desc0_hi, kDescStage, idesc, g, two);
                     }
                     if (tr) trace[Gc * 8 + 2] = clock64();
+                    // the next group's barrier (the other slot; same parity formula with Gc + 1): tested between the MMAs
+                    // and the commit, read at the top of the next iteration
+                    const bool next_ready = ptx::mbar_test_wait(BAR(kConvFull + (slot ^ 1u)), ((Gc + 1u) >> 1) & 1u);
                     if constexpr (PAIR) {
                         ptx::tc_commit_pair(BAR(kGroupDone + gs), 3);
                         if (g == ngroups - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
@@ -630,6 +643,8 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                         if (g == ngroups - 1) ptx::tc_commit(BAR(kTmemFull + acc));
                     }
                     if (tr) trace[Gc * 8 + 3] = clock64();
+                    ready = next_ready;
+                    gs = gs + 1u == NG ? 0u : gs + 1u;
                 }
             }
         }
@@ -903,8 +918,6 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                 // Eight columns at a time in a rolled loop: the strip's code is a quarter of the fully unrolled
                 // form.  The kernel's warps share one instruction cache, and the MMA issuer, whose instruction
                 // stream is the bottleneck of the mainloop, slowed down whenever the epilogue's code grew.
-                // timing experiment (output incomplete): the warps of the lane quadrants named by inject bits 8..11 skip their work
-                if ((args.inject >> 8) & (1u << quad) & 0xFu) continue;
 #pragma unroll 1
                 for (uint32_t q8 = 0; q8 < 32u && q8 < nvalid; q8 += 8u) {
                     uint32_t r[8];

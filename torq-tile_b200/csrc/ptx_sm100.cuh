@@ -373,6 +373,32 @@ __device__ __forceinline__ void mma_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem
         : "memory");
 }
 
+// The four K slices of one K step of the CTA-pair SS MMA in one instruction block (only the low words of the two
+// descriptors advance, by two 16-byte units per K slice of 32 bytes).
+__device__ __forceinline__ void mma_i8_ss_pair_group4(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                      uint32_t idesc, uint32_t accum_first)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pt;\n\t"
+        ".reg .b32 la, lb;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, p;\n\t"
+        "add.u32 la, %1, 2;\n\t add.u32 lb, %3, 2;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, pt;\n\t"
+        "add.u32 la, %1, 4;\n\t add.u32 lb, %3, 4;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, pt;\n\t"
+        "add.u32 la, %1, 6;\n\t add.u32 lb, %3, 6;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, pt;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accum_first)
+        : "memory");
+}
+
 // A group of eight TS MMAs (two K steps of four K slices) in one instruction block, to keep the issuing
 // thread's instruction count per MMA at its minimum (the thread is the bottleneck of the mainloop).  MMA q = 4 h + j
 // takes its M-side operand at a_tmem + 8 q, its N-side descriptor at desc + h * stage16 + 2 j (only the low word of
