@@ -1,29 +1,26 @@
-// HBM-streaming W4A8 GEMV for decode (m <= 16; more rows run on the tensor-core kernel): no tensor
-// cores, no clusters, no shared-memory staging of weights, no scratch memory.
+// HBM-streaming W4A8 GEMV for decode (m <= 16; more rows run on the tensor-core kernel): no tcgen05, no
+// clusters, no shared-memory staging of weights, no scratch memory.  Two kernels share the structure below:
+// gemv_w4a8_kernel (m = 1, dp4a) and gemv_mma_kernel (2 <= m <= 16, mma.sync m16n8k32: the 16-row A fragment is a
+// decode batch, so every batch size costs nearly what m = 2 does).
 //
-// A CTA owns 8 consecutive output columns (8 rows of one 128-row block tile of B_packed) and loops
-// over such groups when there are more groups than resident CTAs; its eight warps take interleaved
-// K blocks.  Inside a warp lane = (row, 16-byte segment), so one warp-wide 128-bit load covers 512
-// contiguous bytes of a packed block: every 32-byte sector is used whole, once.  A thread holds four
-// weight loads at a time (64 registers in all), so four CTAs (32 warps) are resident per SM: on this
-// part a streaming read reaches full bandwidth with many warps that each have a few loads
-// outstanding, not with few warps that have many.  The next group's (or round's) loads are issued
-// as soon as the registers are free, before the current group is combined and stored.
-// Nibbles are expanded with two logic ops per 8 weights (operands 16*q, as in the tensor-core
-// kernel) and accumulated with dp4a; the zero-point correction uses the int16 partial row sums
-// stored at the tail of every packed block.  The four segments of a row are combined with warp
-// shuffles and the eight warps through shared memory: integer sums, so the result is exact and
-// independent of the split.  The epilogue is the GEMM's (reference:
+// A CTA owns one or two groups of 8 consecutive output columns (8 rows of one 128-row block tile of B_packed) and
+// loops over such sets when there are more than resident CTAs; its eight warps take interleaved K blocks.  Inside
+// a warp lane = (row, 16-byte segment), so one warp-wide 128-bit load covers 512 contiguous bytes of a packed
+// block: every 32-byte sector is used whole, once.  A thread holds four weight loads per group at a time: on this
+// part a streaming read reaches full bandwidth with many warps that each have a few loads outstanding, not with
+// few warps that have many.  The next set's loads are issued as soon as the registers are free, before the
+// current set is combined and stored.
+// Nibbles are expanded with two logic ops per 8 weights (operands 16*q, as in the tensor-core kernel); the
+// zero-point correction uses the int16 partial row sums stored at the tail of every packed block (dp4a kernel) or
+// sums the same words against ones (mma kernel).  The segments of a row are combined with warp shuffles and the
+// eight warps through shared memory: integer sums, so the result is exact and independent of the split.  The
+// epilogue is the GEMM's (reference:
 // src/gemm/gemm_i8_i4/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp/..._4x1vl_rvv.cpp:118-177).
 //
-// Programmatic dependent launch: the kernel lets its successor start at once and requests its
-// weights and per-column constants before waiting for its predecessor, so back-to-back GEMVs (the
-// layers of a decode step) overlap their memory phases.  Everything after that wait is on the
-// critical path of the chain (a kernel's wait ends only when its predecessor has completed), so it
-// is kept short: the activation words of a whole chunk are requested together, straight into
-// registers (staging them in shared memory, or fetching the weights with bulk copies to make room
-// for more resident kernels, both measured slower).  Activations, C and D are touched only after
-// the wait.
+// Programmatic dependent launch: the kernel lets its successor start at once and requests its weights before
+// waiting for its predecessor, so back-to-back GEMVs (the layers of a decode step) overlap their memory phases.
+// Everything after that wait is on the critical path of the chain (a kernel's wait ends only when its
+// predecessor has completed), so it is kept short.  Activations, C and D are touched only after the wait.
 // TQT_B200_PDL=0 switches this off.
 #include <cstdlib>
 
@@ -53,8 +50,6 @@ struct GemvArgs {
     const float *scale_b;
     float cmin, cmax;
     int pdl;
-    int exp_flags;   // experiment switches (TQT_B200_GEMV_EXP, diagnostics only): 1 = no wait for the predecessor,
-                     // 2 = activations requested before the wait (both valid only while the inputs are static)
 };
 
 // 128-bit streaming load: read-only path, do not keep the line in L1.
@@ -67,15 +62,6 @@ __device__ __forceinline__ uint4 ldg_stream(const void *p)
     return v;
 }
 
-// 16-byte asynchronous copy global -> shared (L2 only, not through registers); bytes = 0 writes zeros and reads
-// nothing.  A thread that waits for its own copies (cp_async_wait_all) may read what they wrote without a barrier.
-__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void *src, uint32_t bytes)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
 constexpr uint32_t kGemvSlices = kGemvThreads / 32;   // warps of a CTA = interleaved K slices
 constexpr uint32_t kGemvChunk = 4;                   // loads in flight per thread
 
@@ -86,23 +72,20 @@ constexpr uint32_t kGemvChunk = 4;                   // loads in flight per thre
 // flight per thread, the activation words shared by both groups), the launch takes two slots per SM, and the
 // next GEMV of the chain is resident and has its weights in flight while this one runs its post-wait tail.
 //
-// STAGED: the weight loads in flight are held in shared memory (16-byte cp.async, one private slot per thread and
-// load) instead of registers.  A decode-sized launch then needs about a third of the register file instead of
-// most of it, so the CTAs of the next GEMV of a chain find room beside this one's: its weights stream in while
-// this kernel runs the serial tail that follows its wait for the predecessor.
-template <int MR, int G, bool STAGED>
-constexpr int gemv_min_ctas() { return STAGED ? (MR <= 4 ? 4 : 3) : (G == 2 ? 2 : (MR <= 2 ? 4 : (MR <= 8 ? 3 : 2))); }
+// Measured on chains of 48 GEMVs (M = 1, K = N = 4096, programmatic dependent launch): G = 2 2.3-2.5 us per GEMV,
+// G = 1 3.4 us; the same kernel without the wait for its predecessor 1.85 us, a kernel that only reads the bytes
+// 1.2 us.  Holding the loads in flight in shared memory instead of registers (cp.async or bulk copies, to make room
+// for the successor's CTAs) was slower in every form tried: a kernel's shared-memory carve-out is sized for its own
+// CTAs, so the successor's CTAs did not become resident beside it, and static shared memory of a few KiB alone cost
+// the chain 1 us per GEMV.
+template <int MR, int G>
+constexpr int gemv_min_ctas() { return G == 2 ? 2 : (MR <= 2 ? 4 : (MR <= 8 ? 3 : 2)); }
 
-template <int MR, int G, bool STAGED, Dtype TD>
-__global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G, STAGED>()) gemv_w4a8_kernel(const GemvArgs args)
+template <int MR, int G, Dtype TD>
+__global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a8_kernel(const GemvArgs args)
 {
     constexpr uint32_t S = kGemvSlices, CH = kGemvChunk;
     __shared__ int32_t sRed[(S - 1) * G * kGemvWarpRows * (MR + 1)];
-    __shared__ uint4 sW[STAGED ? G * CH * kGemvThreads : 1];   // slot (gi, i) of thread t at [(gi * CH + i) * threads + t]
-#ifdef TQT_GEMV_PAD_SMEM
-    __shared__ int32_t sPad[TQT_GEMV_PAD_SMEM / 4];
-    if (args.exp_flags & 512) sPad[threadIdx.x] = 1;
-#endif
     const uint32_t tid = threadIdx.x, ks = tid >> 5, lane = tid & 31u;
     const uint32_t rr = lane >> 2;                                 // row inside the group
     const uint32_t pos = lane & 3u;                                // physical 16-byte segment
@@ -128,24 +111,18 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G, STAGED>()) 
             rp[gi] = blk + kI4NibBytes + r_blk * 2u;   // tail of every packed block: the zero-point correction terms
         }
     };
-    uint4 w[STAGED ? 1 : G][STAGED ? 1 : CH];
+    uint4 w[G][CH];
     int32_t rsv[G][CH];
-    const uint32_t sw0 = ptx::smem_u32(sW) + tid * 16u;
     auto load_chunk = [&](uint32_t t0) {   // K blocks t0 .. t0 + CH - 1 of this warp
 #pragma unroll
         for (int gi = 0; gi < G; ++gi) {
 #pragma unroll
             for (uint32_t i = 0; i < CH; ++i) {
                 const bool ok = gok[gi] && t0 + i < T;
-                if constexpr (STAGED)
-                    cp_async16(sw0 + (uint32_t)(gi * CH + i) * (kGemvThreads * 16u), ok ? wp[gi] + (size_t)(t0 + i) * kWStep : args.B,
-                               ok ? 16u : 0u);
-                else
-                    w[gi][i] = ok ? ldg_stream(wp[gi] + (size_t)(t0 + i) * kWStep) : make_uint4(0, 0, 0, 0);
-                rsv[gi][i] = (ok && pos == 0 && !(args.exp_flags & 4)) ? (int32_t)__ldg(reinterpret_cast<const int16_t *>(rp[gi] + (size_t)(t0 + i) * kWStep)) : 0;
+                w[gi][i] = ok ? ldg_stream(wp[gi] + (size_t)(t0 + i) * kWStep) : make_uint4(0, 0, 0, 0);
+                rsv[gi][i] = (ok && pos == 0) ? (int32_t)__ldg(reinterpret_cast<const int16_t *>(rp[gi] + (size_t)(t0 + i) * kWStep)) : 0;
             }
         }
-        if constexpr (STAGED) cp_async_commit();
     };
     uint32_t sg = blockIdx.x;
     set_group(sg);
@@ -167,7 +144,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G, STAGED>()) 
     };
     load_column_constants(sg);
     // everything else may have been produced by the preceding kernel
-    if (args.pdl && !(args.exp_flags & 1)) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     float sa[MR];
     int32_t zp[MR];
@@ -193,7 +170,6 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G, STAGED>()) 
         }
 
         for (uint32_t t0 = 0; t0 < T; t0 += CH) {
-            if constexpr (STAGED) cp_async_wait_all();   // this thread's own copies: no barrier needed to read them
 #pragma unroll
             for (int mi = 0; mi < MR; ++mi) {
                 if (MR == 1 || (uint32_t)mi < args.m) {
@@ -202,11 +178,11 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G, STAGED>()) 
 #pragma unroll
                     for (uint32_t i = 0; i < CH; ++i) {
                         const uint8_t *act = ap + (size_t)(t0 + i) * kAStep;
-                        const bool ok = t0 + i < T && !(args.exp_flags & 8);
+                        const bool ok = t0 + i < T;
                         av[i][0] = ok ? __ldg(reinterpret_cast<const uint4 *>(act + sw128_byte((uint32_t)mi, seg * 32u)))
-                                      : make_uint4(1, 2, 3, 4);
+                                      : make_uint4(0, 0, 0, 0);
                         av[i][1] = ok ? __ldg(reinterpret_cast<const uint4 *>(act + sw128_byte((uint32_t)mi, seg * 32u + 16u)))
-                                      : make_uint4(5, 6, 7, 8);
+                                      : make_uint4(0, 0, 0, 0);
                     }
 #pragma unroll
                     for (uint32_t i = 0; i < CH; ++i) {
@@ -214,10 +190,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G, STAGED>()) 
                         const uint32_t ah[4] = {av[i][1].x, av[i][1].y, av[i][1].z, av[i][1].w};
 #pragma unroll
                         for (int gi = 0; gi < G; ++gi) {
-                            uint4 wv;
-                            if constexpr (STAGED) wv = sW[(gi * CH + i) * kGemvThreads + tid];
-                            else wv = w[gi][i];
-                            const uint32_t ws[4] = {wv.x, wv.y, wv.z, wv.w};
+                            const uint32_t ws[4] = {w[gi][i].x, w[gi][i].y, w[gi][i].z, w[gi][i].w};
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const uint32_t lo = (ws[j] << 4) & 0xF0F0F0F0u;   // 16*q for k = 32*seg + 4j .. +3
@@ -255,12 +228,6 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G, STAGED>()) 
                 v += __shfl_xor_sync(0xffffffffu, v, 2);
                 acc[gi][mi] = v;
             }
-        }
-        if (args.exp_flags & 16) {   // experiment: no cross-warp combine, no epilogue (keeps the loads alive)
-            if (acc[0][0] == 0x7f123456) static_cast<int *>(args.D)[tid] = rsum[0];
-            if (next >= sgroups) break;
-            sg = next;
-            continue;
         }
         // ... and the eight warps through shared memory
         if (ks > 0 && pos == 0) {
@@ -403,7 +370,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_mma_min_ctas<G>()) gemv_mma
         }
     };
     // everything else may have been produced by the preceding kernel
-    if (args.pdl && !(args.exp_flags & 1)) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     load_column_constants(sg);
 
     float sa[2] = {0.0f, 0.0f};
@@ -498,12 +465,6 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_mma_min_ctas<G>()) gemv_mma
                 dst[4 * 32] = rs[gi];
             }
         }
-        if (args.exp_flags & 128) {   // experiment: no combine, no epilogue
-            if (acc[0][0] == 0x7f123456) static_cast<int *>(args.D)[tid] = rs[0];
-            if (next >= sets) break;
-            sg = next;
-            continue;
-        }
         __syncthreads();
         if (ks == 0) {
 #pragma unroll
@@ -563,30 +524,15 @@ static int gemv_forced_groups()
     return cached;
 }
 
-// TQT_B200_GEMV_STAGE=0|1 forces register-held or shared-memory-held weight loads (read once).
-static int gemv_forced_stage()
-{
-    static const int cached = [] {
-        const char *e = std::getenv("TQT_B200_GEMV_STAGE");
-        return e ? std::atoi(e) : -1;
-    }();
-    return cached;
-}
-
-template <int MR, int G, bool STAGED, Dtype TD>
+template <int MR, int G, Dtype TD>
 static Result launch_gemv_t(GemvArgs a, cudaStream_t st)
 {
     a.pdl = pdl_enabled() ? 1 : 0;
-    static const int exp_flags = [] {
-        const char *e = std::getenv("TQT_B200_GEMV_EXP");
-        return e ? std::atoi(e) : 0;
-    }();
-    a.exp_flags = exp_flags;
     cudaLaunchConfig_t cfg = {};
     // CTA c owns the sets of G 8-column groups c, c + grid, ...: one set each while they all fit on the GPU at once
     const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
     const uint32_t sgroups = (groups + G - 1) / G;
-    const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_min_ctas<MR, G, STAGED>();
+    const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_min_ctas<MR, G>();
     cfg.gridDim = dim3(sgroups < resident ? sgroups : resident, 1, 1);
     cfg.blockDim = dim3(kGemvThreads, 1, 1);
     cfg.dynamicSmemBytes = 0;
@@ -596,7 +542,7 @@ static Result launch_gemv_t(GemvArgs a, cudaStream_t st)
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a8_kernel<MR, G, STAGED, TD>, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_w4a8_kernel<MR, G, TD>, a);
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
     return Result{kOk, 0};
 }
@@ -604,19 +550,15 @@ static Result launch_gemv_t(GemvArgs a, cudaStream_t st)
 template <int MR, Dtype TD>
 static Result launch_gemv_g(const GemvArgs &a, cudaStream_t st)
 {
-    if constexpr (MR <= 8) {
-        const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
-        const int forced = gemv_forced_groups(), stage = gemv_forced_stage();
-        const bool two = forced ? forced == 2 : (groups + 1) / 2 <= (uint32_t)sm_count_cached() * 2u;
-        if (two) {
-            if (stage == 1) return launch_gemv_t<MR, 2, true, TD>(a, st);
-            return launch_gemv_t<MR, 2, false, TD>(a, st);
-        }
-    }
-    return launch_gemv_t<MR, 1, false, TD>(a, st);
+    // two column groups per CTA while the launch then still fits the GPU in one round (decode-sized N)
+    const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
+    const int forced = gemv_forced_groups();
+    const bool two = forced ? forced == 2 : (groups + 1) / 2 <= (uint32_t)sm_count_cached() * 2u;
+    if (two) return launch_gemv_t<MR, 2, TD>(a, st);
+    return launch_gemv_t<MR, 1, TD>(a, st);
 }
 
-// TQT_B200_GEMV_KERNEL=regs|mma forces the register-held dp4a kernel or the shared-memory mma.sync kernel (read once).
+// TQT_B200_GEMV_KERNEL=regs|mma forces the dp4a kernel (one row only) or the mma.sync kernel (read once).
 static int gemv_forced_kernel()
 {
     static const int cached = [] {
@@ -631,22 +573,6 @@ template <int G, bool R16, Dtype TD>
 static Result launch_gemv_mma(GemvArgs a, cudaStream_t st)
 {
     a.pdl = pdl_enabled() ? 1 : 0;
-    static const int exp_flags = [] {
-        const char *e = std::getenv("TQT_B200_GEMV_EXP");
-        return e ? std::atoi(e) : 0;
-    }();
-    a.exp_flags = exp_flags;
-    static const int carve = [] {
-        const char *e = std::getenv("TQT_B200_GEMV_CARVEOUT");
-        return e ? std::atoi(e) : -1;
-    }();
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (carve >= 0 && dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaFuncSetAttribute(gemv_mma_kernel<G, R16, TD>, cudaFuncAttributePreferredSharedMemoryCarveout, carve);
-        attr_set[dev] = true;
-    }
     const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows, sets = (groups + G - 1) / G;
     const uint32_t resident = (uint32_t)sm_count_cached() * (uint32_t)gemv_mma_min_ctas<G>();
     cudaLaunchConfig_t cfg = {};
@@ -667,21 +593,12 @@ static Result launch_gemv_mma(GemvArgs a, cudaStream_t st)
 template <Dtype TD>
 static Result launch_gemv_m(const GemvArgs &a, cudaStream_t st)
 {
-    const int forced = gemv_forced_kernel();
-    if (forced == 2 || (forced == 0 && a.m > 1)) {
-        // four column groups per CTA while the launch still fills the GPU (two CTAs per SM), two otherwise
-        const uint32_t groups = (a.n + kGemvWarpRows - 1) / kGemvWarpRows;
-        const int fg = gemv_forced_groups();
-        (void)groups;
-        const bool one = fg == 1;
-        if (a.m > 8) return one ? launch_gemv_mma<1, true, TD>(a, st) : launch_gemv_mma<2, true, TD>(a, st);
-        return one ? launch_gemv_mma<1, false, TD>(a, st) : launch_gemv_mma<2, false, TD>(a, st);
-    }
-    if (a.m <= 1) return launch_gemv_g<1, TD>(a, st);
-    if (a.m <= 2) return launch_gemv_g<2, TD>(a, st);
-    if (a.m <= 4) return launch_gemv_g<4, TD>(a, st);
-    if (a.m <= 8) return launch_gemv_g<8, TD>(a, st);
-    return launch_gemv_g<16, TD>(a, st);
+    // one row: dp4a kernel; a decode batch: mma kernel (TQT_B200_GEMV_KERNEL=mma forces it for one row too)
+    const int forced = gemv_forced_kernel(), fg = gemv_forced_groups();
+    if (a.m == 1 && forced != 2) return launch_gemv_g<1, TD>(a, st);
+    const bool one = fg == 1;
+    if (a.m > 8) return one ? launch_gemv_mma<1, true, TD>(a, st) : launch_gemv_mma<2, true, TD>(a, st);
+    return one ? launch_gemv_mma<1, false, TD>(a, st) : launch_gemv_mma<2, false, TD>(a, st);
 }
 
 Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
