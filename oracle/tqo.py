@@ -74,6 +74,7 @@ class Oracle:
         lib.tqo_gemm_qai8dx_qsi8cx.argtypes = [_sz, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int, _vp, _vp,
                                                _vp, _vp, _vp, _sz, C.c_float, C.c_float, C.c_int]
 
+        lib.tqo_im2col_i8.argtypes = [C.c_int, _sz, _vp, _vp, _vp]
         lib.tqo_fill_uniform_f32.argtypes = [_vp, _sz, C.c_float, C.c_float, C.c_uint32]
         lib.tqo_fill_uniform_i8.argtypes = [_vp, _sz, C.c_int, C.c_int, C.c_uint32]
         lib.tqo_fill_uniform_i32.argtypes = [_vp, _sz, C.c_int32, C.c_int32, C.c_uint32]
@@ -96,6 +97,14 @@ class Oracle:
         a = np.empty(shape, np.float32)
         self.lib.tqo_fill_normal_f32(_ptr(a), a.size, float(mean), float(sigma), int(seed))
         return a
+
+    def im2col_i8(self, activation, geom, channel_first, group_idx=0):
+        """``geom``: ConvGeometry.  Returns [M, K] (channel-last) or [K, N] (channel-first)."""
+        rows, k = geom.rows, geom.k
+        out = np.empty((k, rows) if channel_first else (rows, k), np.int8)
+        g = geom.as_array()
+        self.lib.tqo_im2col_i8(int(channel_first), group_idx, _ptr(activation), _ptr(out), _ptr(g))
+        return out
 
     # ---- helpers -----------------------------------------------------------------------
     def max_threads(self) -> int:
@@ -201,6 +210,32 @@ class Oracle:
         return D
 
 
+class ConvGeometry:
+    """The members of the reference's tqt_conv_params (src/common/tqt_conv.h:23-34); the output shape is computed
+    the way the reference's test suites do (test/common/conv_test_runner.h:95-114)."""
+
+    def __init__(self, input_channel, output_channel, groups, input_shape, kernel_shape, stride=(1, 1, 1),
+                 dilation=(1, 1, 1), pad=(0, 0, 0)):
+        self.input_channel, self.output_channel, self.groups = input_channel, output_channel, groups
+        self.input_shape, self.kernel_shape = tuple(input_shape), tuple(kernel_shape)
+        self.stride, self.dilation, self.pad = tuple(stride), tuple(dilation), tuple(pad)
+        self.output_shape = tuple((self.input_shape[i] + 2 * self.pad[i] - self.dilation[i] * (self.kernel_shape[i] - 1) - 1)
+                                  // self.stride[i] + 1 for i in range(3))
+
+    @property
+    def rows(self):
+        return int(np.prod(self.output_shape))
+
+    @property
+    def k(self):
+        return int(np.prod(self.kernel_shape)) * (self.input_channel // self.groups)
+
+    def as_array(self):
+        return np.array(list(self.input_shape) + list(self.output_shape) + list(self.kernel_shape) + list(self.stride)
+                        + list(self.dilation) + list(self.pad) + [self.input_channel, self.output_channel, self.groups],
+                        dtype=np.uint64)
+
+
 class Reference:
     """The reference's own portable C++ (oracle/_ref).  ``available()`` is False on machines that
     have neither the prebuilt library nor the reference checkout."""
@@ -240,6 +275,18 @@ class Reference:
             lib.ref_w4a8_quantize_b_per_channel_sym_int4.argtypes = [_vp, _sz, _sz, _vp, _vp]
             lib.ref_w4a8_gemm.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_float,
                                           C.c_float, C.c_int]
+
+    def has_conv(self) -> bool:
+        return self.lib is not None and hasattr(self.lib, "ref_im2col_i8")
+
+    def im2col_i8(self, activation, geom, channel_first, group_idx=0):
+        """tqt_im2col_cf / tqt_im2col_cl of the reference on int8."""
+        rows, k = geom.rows, geom.k
+        out = np.empty((k, rows) if channel_first else (rows, k), np.int8)
+        g = geom.as_array()
+        self.lib.ref_im2col_i8.argtypes = [C.c_int, _sz, _vp, _vp, _vp]
+        self.lib.ref_im2col_i8(int(channel_first), group_idx, _ptr(activation), _ptr(out), _ptr(g))
+        return out
 
     def has_w4a8(self) -> bool:
         """True when the library carries the W4A8 helpers cut out of the reference's gtest suite."""

@@ -591,3 +591,55 @@ void tqo_gemm_qai8dx_qsi8cx(size_t m, size_t n, size_t k, const int8_t *A, size_
         }
     }
 }
+
+/* ------------------------------------------------------------------------- */
+/* im2col of the int8 convolution wrappers.                                   */
+/* Follows src/common/tqt_conv.h: channel-first (:52-121) input [C,D,H,W],    */
+/* matrix [K, N] with K order (ic, kd, kh, kw) and N = output positions;      */
+/* channel-last (:124-196) input [D,H,W,C], matrix [M, K] with M = output     */
+/* positions and K order (kd, kh, kw, ic).  Padding positions hold 0.         */
+/* geom: the 21 size_t members of tqt_conv_params in declaration order        */
+/* (:23-34): input, output, kernel, stride, dilation, pad (3 each),           */
+/* input_channel, output_channel, groups.                                     */
+/* Written per matrix element (the reference walks the input in nested loops  */
+/* and copies channel runs).                                                  */
+/* ------------------------------------------------------------------------- */
+void tqo_im2col_i8(int channel_first, size_t group_idx, const int8_t *act, int8_t *out,
+                   const size_t *geom)
+{
+    const size_t *in = geom, *o = geom + 3, *ker = geom + 6, *st = geom + 9, *dil = geom + 12,
+                 *pad = geom + 15;
+    const size_t c_total = geom[18], groups = geom[20];
+    const size_t ic_pg = c_total / groups, c_off = group_idx * ic_pg;
+    const size_t rows = o[0] * o[1] * o[2], kvol = ker[0] * ker[1] * ker[2], K = kvol * ic_pg;
+    const size_t in_vol = in[0] * in[1] * in[2];
+    for (size_t pos = 0; pos < rows; ++pos) {
+        const size_t ow = pos % o[2], oh = (pos / o[2]) % o[1], od = pos / (o[2] * o[1]);
+        for (size_t k = 0; k < K; ++k) {
+            size_t ic, kpos;
+            if (channel_first) {
+                ic = k / kvol;
+                kpos = k % kvol;
+            } else {
+                kpos = k / ic_pg;
+                ic = k % ic_pg;
+            }
+            const size_t kw = kpos % ker[2], kh = (kpos / ker[2]) % ker[1],
+                         kd = kpos / (ker[2] * ker[1]);
+            const long id = (long)(od * st[0] + kd * dil[0]) - (long)pad[0];
+            const long ih = (long)(oh * st[1] + kh * dil[1]) - (long)pad[1];
+            const long iw = (long)(ow * st[2] + kw * dil[2]) - (long)pad[2];
+            int8_t v = 0;
+            if (id >= 0 && id < (long)in[0] && ih >= 0 && ih < (long)in[1] && iw >= 0 &&
+                iw < (long)in[2]) {
+                const size_t sp = ((size_t)id * in[1] + (size_t)ih) * in[2] + (size_t)iw;
+                v = channel_first ? act[(c_off + ic) * in_vol + sp]
+                                  : act[sp * c_total + c_off + ic];
+            }
+            if (channel_first)
+                out[k * rows + pos] = v;
+            else
+                out[pos * K + k] = v;
+        }
+    }
+}

@@ -14,7 +14,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
-from oracle.tqo import TD_BF16, TD_F16, TD_F32, Reference  # noqa: E402
+from oracle.tqo import TD_BF16, TD_F16, TD_F32, ConvGeometry, Reference  # noqa: E402
 
 I8_SHAPES = [(32, 32, 32, False), (3, 8, 11, False), (5, 11, 10, False), (9, 19, 23, False),
              (15, 32, 25, False), (60, 63, 127, False), (32, 32, 32, True), (60, 63, 127, True)]
@@ -30,6 +30,22 @@ W4A8_CASES = [(8, 8, 8, 0, 0, None), (16, 16, 16, 0, 0, None), (32, 32, 32, 0, 0
               (7, 3, 8, 0, 0, None), (17, 19, 24, 0, 0, None), (31, 35, 64, 0, 0, None), (60, 61, 128, 0, 0, None),
               (32, 32, 32, 1, 0, None), (17, 19, 24, 1, 0, None), (32, 32, 32, 0, 0, (-0.5, 0.5)),
               (32, 32, 32, 0, 1, None), (32, 32, 32, 1, 1, (-0.5, 0.5))]
+# test/conv/test_conv_i8_i8_rvv.cpp:21-41 (ic, oc, groups, ih, iw, kh, kw + stride / pad / dilation setters), then
+# cases the reference's list lacks: depth, groups (group index 1), channel counts that are multiples of 16, 1x1 stride 2
+def _conv2d(ic, oc, g, ih, iw, kh, kw, stride=(1, 1), pad=(0, 0), dil=(1, 1), group_idx=0):
+    return (ConvGeometry(ic, oc, g, (1, ih, iw), (1, kh, kw), (1,) + stride, (1,) + dil, (0,) + pad), group_idx)
+
+
+CONV_CASES = [_conv2d(3, 16, 1, 8, 8, 3, 3), _conv2d(16, 32, 1, 8, 8, 3, 3), _conv2d(16, 32, 1, 8, 8, 1, 1),
+              _conv2d(3, 16, 1, 8, 8, 3, 3, pad=(1, 1)), _conv2d(3, 16, 1, 8, 8, 3, 3, stride=(2, 2)),
+              _conv2d(3, 16, 1, 8, 8, 3, 3, dil=(2, 2), pad=(2, 2)),
+              _conv2d(3, 16, 1, 8, 8, 3, 3, pad=(1, 1), stride=(2, 2)), _conv2d(8, 16, 1, 7, 11, 3, 5),
+              _conv2d(64, 128, 1, 4, 4, 1, 1), _conv2d(3, 32, 1, 16, 16, 3, 3, pad=(1, 1)), _conv2d(3, 8, 1, 6, 6, 3, 3),
+              _conv2d(64, 32, 1, 4, 4, 3, 3, pad=(1, 1)),
+              (ConvGeometry(4, 8, 1, (3, 5, 6), (2, 3, 2), (1, 2, 1), (1, 1, 2), (1, 0, 1)), 0),
+              _conv2d(8, 16, 2, 9, 7, 3, 3, pad=(1, 1), group_idx=1),
+              _conv2d(32, 32, 2, 12, 13, 3, 3, pad=(1, 1), group_idx=1),
+              _conv2d(16, 8, 1, 9, 9, 1, 1, stride=(2, 2))]
 MULTIPLIERS = [0.0025, 0.0, 1.0, 0.5, 0.75, 1e-12, 1e-9, 2.0 ** -31, 2.0 ** -32, 2.0 ** -33, 123.456,
                0.05 * 0.001 / 0.1, 0.05 * 0.01 / 0.1, 0.9999999999, 0.99999999999999989,
                1.0 - 2.0 ** -31, 1.0 - 2.0 ** -32, 0.5 + 2.0 ** -32, 0.5 + 3 * 2.0 ** -33,
@@ -160,6 +176,13 @@ def main():
     out["w4a8_edge_W"] = Wq
     nib, sb = ref.w4a8_quantize_b_per_channel_sym_int4(Wq)
     out["w4a8_edge_nib"], out["w4a8_edge_sb"] = nib, sb
+    # ---- im2col of the int8 convolution wrappers: the same flat input read as [C,D,H,W] and as [D,H,W,C] ----
+    for idx, (geom, group_idx) in enumerate(CONV_CASES):
+        act = ref.fill_uniform((int(np.prod(geom.input_shape)), geom.input_channel), np.int8, -128, 127, 42)
+        out[f"conv_{idx}_geom"] = np.concatenate([geom.as_array().astype(np.int64), [group_idx]])
+        out[f"conv_{idx}_cl"] = ref.im2col_i8(act, geom, False, group_idx)
+        out[f"conv_{idx}_cf"] = ref.im2col_i8(act, geom, True, group_idx)
+    out["conv_cases"] = np.array([len(CONV_CASES)], np.int64)
     path = os.path.join(HERE, "ref_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

@@ -25,7 +25,7 @@ def _declared_symbols():
     import subprocess
     names = set()
     for h in ("tqt_b200_common.h", "tqt_b200_gemm_i8_i8.h", "tqt_b200_gemm_i8_i4.h", "tqt_b200_gemm_f16_i4.h", "tqt_b200_gemm_siblings.h",
-              "tqt_b200_ext.h"):
+              "tqt_b200_conv_i8_i8.h", "tqt_b200_ext.h"):
         out = subprocess.check_output(["/usr/bin/g++", "-E", "-P", "-x", "c++", os.path.join(ROOT, "include", h)], text=True)
         names |= set(re.findall(r"\b(tqt_[a-z0-9_]+?)\s*\(", out))
     return {n for n in names if not n.endswith("_t")}
@@ -131,6 +131,61 @@ def test_status_word_without_gpu(pkg):
     assert pkg.lib().tqt_cuda_get_last_status() == 0
     assert pkg.lib().tqt_cuda_kernel_choice_w4a8(1, 4096, 4096) == 1
     assert pkg.lib().tqt_cuda_kernel_choice_w4a8(2048, 14336, 4096) == 0
+
+
+def test_conv_wrappers_without_gpu(pkg, tmp_path):
+    """The convolution wrappers' helpers are the GEMM types' helpers (reference: src/conv/conv_i8_i8/*/
+    tqt_conv*_4x1vl_rvv.cpp forward the same way); a geometry that cannot be narrowed is rejected before any launch; a C
+    caller fills every ukernel table positionally, which checks member order and signatures at compile time."""
+    import subprocess
+    g = pkg.GemmReqI8()
+    for t in pkg.CONV_TYPES:
+        c = pkg.ConvI8(t)
+        assert c.get_m_step() == 128 and c.get_n_step() == 128
+        assert c.get_d_size(5, 7) == 35 and c.get_c_offset(128, 256, 1000) == (128 * 1000 + 256) * 4
+        assert c.get_bias_offset(128) == 512 and c.get_d_offset(128, 256, 1000) == 128 * 1000 + 256
+    c = pkg.ConvI8(pkg.CONV_TYPES[0])
+    assert c.get_a_im2colpack_size(200, 300) == g.get_a_packed_size(200, 300) == 2 * 3 * 16384
+    assert c.get_a_im2colpack_offset(128, 256, 300, 72) == g.get_a_packed_offset(128, 256, 300, 72)
+    assert c.get_b_packed_offset(256, 128, 300, 44) == g.get_b_packed_offset(256, 128, 300, 44)
+    c = pkg.ConvI8(pkg.CONV_TYPES[1])
+    assert c.get_a_im2col_size(10, 27) == 270 and c.get_a_im2col_offset(3, 5, 27) == 86 and c.get_b_offset(3, 5, 27) == 86
+    c = pkg.ConvI8(pkg.CONV_TYPES[2])
+    assert c.get_b_im2col_size(27, 10) == 270 and c.get_b_im2col_offset(3, 5, 10) == 53 and c.get_a_offset(3, 5, 27) == 86
+    c = pkg.ConvI8(pkg.CONV_TYPES[3])
+    assert c.get_b_im2colpack_size(200, 300) == 2 * 3 * 16384 and c.get_a_packed_size(1, 1) == 16384
+    # rejected before any launch: group index out of range, channels not divisible by groups, k_idx off the K step,
+    # an extent of 2^31; NULL geometry returns silently
+    cp = pkg.ConvParams.make(8, 8, 2, (1, 4, 4), (1, 3, 3))
+    for args in ((2, 16, 36, 0, 16, cp), (0, 16, 36, 64, 16, cp), (0, 16, 36, 0, 16, pkg.ConvParams.make(9, 8, 2, (1, 4, 4), (1, 3, 3))),
+                 (0, 16, 36, 0, 16, pkg.ConvParams.make(8, 8, 2, (1, 4, 1 << 31), (1, 3, 3))), (0, None, 36, 0, 16, cp)):
+        with pytest.raises(pkg.TqtError):
+            pkg.ConvI8(pkg.CONV_TYPES[0]).run_im2colpack(*args)
+        assert pkg.lib().tqt_cuda_get_last_status() == 1
+    with pytest.raises(pkg.TqtError):
+        pkg.ConvI8(pkg.CONV_TYPES[2]).run_im2col(5, 16, 16, cp)
+    pkg.ConvI8(pkg.CONV_TYPES[0]).run_im2colpack(0, 16, 36, 0, 16, None)
+    assert pkg.lib().tqt_cuda_get_last_status() == 0
+    libdir = os.path.join(ROOT, "torq-tile_b200")
+    S = "_128x128_sm100a"
+    tables = []
+    for t, members in ((pkg.CONV_TYPES[0], ("get_m_step get_n_step get_a_im2colpack_offset get_b_packed_offset get_c_offset get_bias_offset "
+                                            "get_d_offset get_d_size get_a_im2colpack_size get_b_packed_size run_bt_pack run_a_im2colpack run_conv")),
+                       (pkg.CONV_TYPES[1], ("get_m_step get_n_step get_b_offset get_c_offset get_bias_offset get_d_offset get_d_size "
+                                            "get_a_im2col_size get_a_im2col_offset run_im2col run_conv")),
+                       (pkg.CONV_TYPES[2], ("get_m_step get_n_step get_a_offset get_c_offset get_bias_offset get_d_offset get_d_size "
+                                            "get_b_im2col_size get_b_im2col_offset run_im2col run_conv")),
+                       (pkg.CONV_TYPES[3], ("get_m_step get_n_step get_a_packed_offset get_b_im2colpack_offset get_c_offset get_bias_offset "
+                                            "get_d_offset get_d_size get_a_packed_size get_b_im2colpack_size run_a_pack run_b_im2colpack run_conv"))):
+        tables.append(f"    struct tqt_{t}_ukernel u{len(tables)} = {{" + ", ".join(f"tqt_{m}_{t}{S}" for m in members.split()) + "};")
+    src = tmp_path / "conv_tables.c"
+    src.write_text('#include "tqt_b200_conv_i8_i8.h"\nint main(void) {\n' + "\n".join(tables) +
+                   "\n    return (int)u0.get_m_step() + (u1.run_conv && u2.run_im2col && u3.run_b_im2colpack);\n}\n")
+    exe = tmp_path / "conv_tables"
+    r = subprocess.run(["/usr/bin/gcc", "-std=c11", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"), str(src),
+                        "-L", libdir, "-ltorq_tile_b200", f"-Wl,-rpath,{libdir}", "-o", str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    assert subprocess.run([str(exe)]).returncode == 129
 
 
 def test_output_replicas_argument_checks(pkg):

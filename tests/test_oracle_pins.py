@@ -308,3 +308,53 @@ def test_live_reference_when_built(oracle):
     for x in f[::7]:
         assert oracle.lib.tqo_f32_to_f16(float(x)) == ref.lib.ref_f32_to_f16(float(x)), x
         assert oracle.lib.tqo_f32_to_bf16(float(x)) == ref.lib.ref_f32_to_bf16(float(x)), x
+
+
+def _conv_cases(golden):
+    from tqt_conv_cases import conv_geometry_from_golden
+    for idx in range(int(golden["conv_cases"][0])):
+        geom, group_idx = conv_geometry_from_golden(golden[f"conv_{idx}_geom"])
+        yield idx, geom, group_idx
+
+
+def test_im2col_golden(oracle, golden):
+    """The im2col restatement against outputs of the reference's tqt_im2col_cf / tqt_im2col_cl (src/common/tqt_conv.h:
+    52-196, compiled by oracle/Makefile ref) on the shapes of its int8 convolution suite
+    (test/conv/test_conv_i8_i8_rvv.cpp:21-41) plus depth, groups and 16-multiple channel counts, both layouts."""
+    from tqt_conv_cases import im2col_index
+    n = 0
+    for idx, geom, group_idx in _conv_cases(golden):
+        act = oracle.fill_uniform((int(np.prod(geom.input_shape)) * geom.input_channel,), np.int8, -128, 127, 42)
+        for cf, tag in ((False, "cl"), (True, "cf")):
+            want = golden[f"conv_{idx}_{tag}"]
+            got = oracle.im2col_i8(act, geom, cf, group_idx)
+            assert got.shape == want.shape and np.array_equal(got, want), (idx, tag)
+            # the vectorised index map the GPU tests build real-valued convolutions with
+            ix = im2col_index(geom, cf, group_idx)
+            via = np.where(ix >= 0, act[np.maximum(ix, 0)], 0).astype(np.int8)
+            assert np.array_equal(via.T if cf else via, want), (idx, tag)
+        n += 1
+    assert n >= 16
+
+
+def test_im2col_live_reference_when_built(oracle):
+    """Where oracle/_ref carries the reference's im2col, random geometries (depth, groups, stride, dilation, padding)
+    through both implementations."""
+    from oracle.tqo import ConvGeometry, Reference
+    ref = Reference()
+    if not (ref.available() and ref.has_conv()):
+        pytest.skip("oracle/_ref without the im2col shim on this machine")
+    rng = np.random.default_rng(11)
+    for _ in range(40):
+        groups = int(rng.choice([1, 1, 2, 3]))
+        ic = groups * int(rng.integers(1, 7))
+        ker = [int(rng.integers(1, 4)) for _ in range(3)]
+        dil = [int(rng.integers(1, 3)) for _ in range(3)]
+        pad = [int(rng.integers(0, 3)) for _ in range(3)]
+        stride = [int(rng.integers(1, 3)) for _ in range(3)]
+        shape = [int(rng.integers(dil[i] * (ker[i] - 1) + 1, dil[i] * (ker[i] - 1) + 6)) for i in range(3)]
+        geom = ConvGeometry(ic, groups * 2, groups, shape, ker, stride, dil, pad)
+        act = rng.integers(-128, 128, int(np.prod(shape)) * ic).astype(np.int8)
+        g = int(rng.integers(0, groups))
+        for cf in (False, True):
+            assert np.array_equal(oracle.im2col_i8(act, geom, cf, g), ref.im2col_i8(act, geom, cf, g))

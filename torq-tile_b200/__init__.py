@@ -438,6 +438,90 @@ SIBLING_TYPES = (
 )
 
 
+# ---- int8 convolution wrappers (include/tqt_b200_conv_i8_i8.h) ---------------------------------------
+class ConvParams(C.Structure):
+    """struct tqt_conv_params (host struct; reference src/common/tqt_conv.h:23-34)."""
+    _fields_ = [(n, _sz * 3) for n in ("input_shape", "output_shape", "kernel_shape", "stride", "dilation", "pad")] + \
+               [("input_channel", _sz), ("output_channel", _sz), ("groups", _sz)]
+
+    @classmethod
+    def make(cls, input_channel, output_channel, groups, input_shape, kernel_shape, stride=(1, 1, 1), dilation=(1, 1, 1),
+             pad=(0, 0, 0), output_shape=None):
+        p = cls()
+        if output_shape is None:   # the caller computes it; this is the usual formula
+            output_shape = [(input_shape[i] + 2 * pad[i] - dilation[i] * (kernel_shape[i] - 1) - 1) // stride[i] + 1
+                            for i in range(3)]
+        for name, v in (("input_shape", input_shape), ("output_shape", output_shape), ("kernel_shape", kernel_shape),
+                        ("stride", stride), ("dilation", dilation), ("pad", pad)):
+            setattr(p, name, (_sz * 3)(*[int(x) for x in v]))
+        p.input_channel, p.output_channel, p.groups = input_channel, output_channel, groups
+        return p
+
+
+CONV_TYPES = ("convcl_1xnbias_reqi32toi8_clamp_qai8_qai8p_qsi8cxp", "convcl_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxt",
+              "convcf_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8", "convcf_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8p")
+
+
+class ConvI8(_UKernel):
+    """One of the int8 convolution wrappers: an im2col step (plain, or fused with the pack) and run_conv, which is the
+    run_gemm of the requantising GEMM type of the same name."""
+
+    def __init__(self, type_name: str):
+        self.type_name = type_name
+        self.channel_first = type_name.startswith("convcf")
+        self.packed = type_name.endswith("p")
+        common = (("get_m_step", 0), ("get_n_step", 0), ("get_c_offset", 3), ("get_bias_offset", 1), ("get_d_offset", 3),
+                  ("get_d_size", 2))
+        if self.channel_first and self.packed:
+            own = (("get_a_packed_offset", 4), ("get_b_im2colpack_offset", 4), ("get_a_packed_size", 2),
+                   ("get_b_im2colpack_size", 2))
+            runs = ["run_a_pack", "run_b_im2colpack"]
+        elif self.channel_first:
+            own = (("get_a_offset", 3), ("get_b_im2col_size", 2), ("get_b_im2col_offset", 3))
+            runs = ["run_im2col"]
+        elif self.packed:
+            own = (("get_a_im2colpack_offset", 4), ("get_b_packed_offset", 4), ("get_a_im2colpack_size", 2),
+                   ("get_b_packed_size", 2))
+            runs = ["run_bt_pack", "run_a_im2colpack"]
+        else:
+            own = (("get_b_offset", 3), ("get_a_im2col_size", 2), ("get_a_im2col_offset", 3))
+            runs = ["run_im2col"]
+        self.helpers_size = common + own
+        self.actions = [h[0] for h in self.helpers_size] + runs + ["run_conv"]
+        self.params_cls = QaI8QsI8DxQaI8Params if self.channel_first else QaI8QaI8QsI8CxParams
+        super().__init__()
+
+    def run_a_pack(self, m, k, lda, lda_packed, k_idx, A, A_packed):
+        self._pack("run_a_pack", m, k, lda, lda_packed, k_idx, A, A_packed)
+
+    def run_bt_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_bt_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def run_im2col(self, group_idx, activation, im2col_buf, params):
+        f = self._sym("run_im2col")
+        f.argtypes = [_sz, _vp, _vp, C.POINTER(ConvParams)]
+        f.restype = None
+        f(group_idx, _addr(activation), _addr(im2col_buf), None if params is None else C.byref(params))
+        check("run_im2col " + self.type_name)
+
+    def run_im2colpack(self, group_idx, activation, ld_packed, k_idx, packed, params):
+        """run_a_im2colpack (channel-last) / run_b_im2colpack (channel-first)."""
+        f = self._sym("run_b_im2colpack" if self.channel_first else "run_a_im2colpack")
+        f.argtypes = [_sz, _vp, _sz, _sz, _vp, C.POINTER(ConvParams)]
+        f.restype = None
+        f(group_idx, _addr(activation), ld_packed, k_idx, _addr(packed), None if params is None else C.byref(params))
+        check("run_im2colpack " + self.type_name)
+
+    def run_conv(self, m, n, k, A, lda, k_idx_a, B, ldb, k_idx_b, Cm, ldc, D, ldd, bias, clamp_min, clamp_max, params):
+        f = self._sym("run_conv")
+        f.argtypes = [_sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, C.c_int8, C.c_int8,
+                      C.POINTER(self.params_cls)]
+        f.restype = None
+        f(m, n, k, _addr(A), lda, k_idx_a, _addr(B), ldb, k_idx_b, _addr(Cm), ldc, _addr(D), ldd, _addr(bias),
+          int(clamp_min), int(clamp_max), None if params is None else C.byref(params))
+        check("run_conv " + self.type_name)
+
+
 # ---- extensions ------------------------------------------------------------------------------------
 _TA_NAMES = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}
 
@@ -502,4 +586,5 @@ EXTENSION_SYMBOLS = (
 
 def all_ukernels():
     return [GemmClampI32I8I8(), GemmClampI32I8pI8p(), GemmReqI8(), GemmW4A8("f32"), GemmW4A8("f16"),
-            GemmW4A8("bf16"), GemmW4A16("f16"), GemmW4A16("f32")] + [SiblingGemm(t) for t in SIBLING_TYPES]
+            GemmW4A8("bf16"), GemmW4A16("f16"), GemmW4A16("f32")] + [SiblingGemm(t) for t in SIBLING_TYPES] + \
+           [ConvI8(t) for t in CONV_TYPES]

@@ -2,6 +2,7 @@
 // types take _Float16 / __bf16 clamp arguments by value, as the reference's prototypes do).
 // Argument checks mirror the reference's TQT_ASSUME preconditions but never abort: a failed check
 // records TQT_CUDA_INVALID_ARGUMENT for tqt_cuda_get_last_status() and returns without launching.
+#include "../../include/tqt_b200_conv_i8_i8.h"
 #include "../../include/tqt_b200_ext.h"
 #include "../../include/tqt_b200_gemm_f16_i4.h"
 #include "../../include/tqt_b200_gemm_i8_i4.h"
@@ -498,6 +499,7 @@ void tqt_cuda_set_output_replicas(const void *local_base, size_t local_bytes, vo
 }
 
 #include "abi_siblings.inc"
+#include "abi_conv.inc"
 
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k)
 {

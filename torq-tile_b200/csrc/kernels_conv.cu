@@ -1,0 +1,182 @@
+// im2col for the int8 convolution wrappers: the activation tensor is gathered either into a plain matrix or straight
+// into the 16 KiB swizzled int8 blocks the tensor-core GEMMs copy into shared memory, so a convolution is one
+// gather launch followed by the requantising GEMM of the same kernel type.
+//
+// Reference counterparts: src/common/tqt_conv.h:52-121 (channel-first im2col: K order (ic, kd, kh, kw), matrix [K, N]),
+// :124-196 (channel-last im2col: K order (kd, kh, kw, ic), matrix [M, K]) and the fused im2col + pack of
+// src/conv/conv_i8_i8/convcl_1xnbias_reqi32toi8_clamp_qai8_qai8p_qsi8cxp/
+// tqt_convcl_1xnbias_reqi32toi8_clamp_qai8_qai8p_qsi8cxp_4x1vl_rvv.cpp:96-182.  Padding positions hold 0 there and
+// here.  Streaming kernels, bounded by HBM bandwidth on the written matrix.
+#include "dev_common.cuh"
+
+namespace tqt {
+
+namespace {
+
+inline Result conv_check_launch()
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
+    return Result{kOk, 0};
+}
+
+// Where a column index of the im2col matrix points inside the kernel window.
+template <bool CF>
+struct KCursor {
+    uint32_t kd, kh, kw, ic;
+
+    __device__ __forceinline__ void seek(const ConvGeom &g, uint32_t k)
+    {
+        uint32_t kpos;
+        if (CF) {
+            const uint32_t kvol = g.ker[0] * g.ker[1] * g.ker[2];
+            ic = k / kvol;
+            kpos = k - ic * kvol;
+        } else {
+            kpos = k / g.ic_pg;
+            ic = k - kpos * g.ic_pg;
+        }
+        const uint32_t q = kpos / g.ker[2];
+        kw = kpos - q * g.ker[2];
+        kd = q / g.ker[1];
+        kh = q - kd * g.ker[1];
+    }
+
+    __device__ __forceinline__ void next(const ConvGeom &g)
+    {
+        if (CF) {
+            if (++kw == g.ker[2]) { kw = 0; if (++kh == g.ker[1]) { kh = 0; if (++kd == g.ker[0]) { kd = 0; ++ic; } } }
+        } else {
+            if (++ic == g.ic_pg) { ic = 0; if (++kw == g.ker[2]) { kw = 0; if (++kh == g.ker[1]) { kh = 0; ++kd; } } }
+        }
+    }
+
+    // Offset of the input element this column reads for output position (od, oh, ow); false inside the padding.
+    __device__ __forceinline__ bool source(const ConvGeom &g, uint32_t od, uint32_t oh, uint32_t ow, size_t &off) const
+    {
+        const int id = (int)(od * g.stride[0] + kd * g.dil[0]) - (int)g.pad[0];
+        const int ih = (int)(oh * g.stride[1] + kh * g.dil[1]) - (int)g.pad[1];
+        const int iw = (int)(ow * g.stride[2] + kw * g.dil[2]) - (int)g.pad[2];
+        if (id < 0 || id >= (int)g.in[0] || ih < 0 || ih >= (int)g.in[1] || iw < 0 || iw >= (int)g.in[2]) return false;
+        const size_t sp = ((size_t)id * g.in[1] + (size_t)ih) * g.in[2] + (size_t)iw;
+        off = CF ? (size_t)(g.c_off + ic) * ((size_t)g.in[0] * g.in[1] * g.in[2]) + sp
+                 : sp * g.c_total + g.c_off + ic;
+        return true;
+    }
+};
+
+__device__ __forceinline__ void split_position(const ConvGeom &g, uint32_t pos, uint32_t &od, uint32_t &oh, uint32_t &ow)
+{
+    const uint32_t q = pos / g.out[2];
+    ow = pos - q * g.out[2];
+    od = q / g.out[1];
+    oh = q - od * g.out[1];
+}
+
+// One thread per 16-byte chunk of the packed matrix: row = output position, 16 consecutive columns.  Channel-last
+// inputs whose channel counts are multiples of 16 move each chunk with one 128-bit load (the 16 columns are 16
+// consecutive channels of one input pixel); everything else gathers bytes.  Channel-first: consecutive threads take
+// consecutive rows, which are consecutive input pixels along w for stride 1.
+template <bool CF>
+__global__ void __launch_bounds__(256) im2col_pack_i8_kernel(ConvGeom g, const int8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                                             size_t kblocks, size_t kblocks_total, size_t total_chunks, int vec_ok)
+{
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total_chunks;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        uint32_t c, r;
+        if (CF) {
+            r = (uint32_t)(idx & 127);
+            c = (uint32_t)((idx >> 7) & 7);
+        } else {
+            c = (uint32_t)(idx & 7);
+            r = (uint32_t)((idx >> 3) & 127);
+        }
+        const size_t blk = idx >> 10, kb = blk % kblocks, tile = blk / kblocks;
+        const size_t row = tile * 128 + r;
+        const uint32_t k0 = (uint32_t)(kb * 128 + c * 16);
+        alignas(16) int8_t v[16];
+        *reinterpret_cast<uint4 *>(v) = make_uint4(0u, 0u, 0u, 0u);
+        if (row < g.rows && k0 < g.k) {
+            uint32_t od, oh, ow;
+            split_position(g, (uint32_t)row, od, oh, ow);
+            KCursor<CF> cur;
+            cur.seek(g, k0);
+            size_t off;
+            if (!CF && vec_ok) {
+                if (cur.source(g, od, oh, ow, off)) *reinterpret_cast<uint4 *>(v) = *reinterpret_cast<const uint4 *>(src + off);
+            } else {
+#pragma unroll 4
+                for (uint32_t e = 0; e < 16; ++e) {
+                    if (k0 + e < g.k && cur.source(g, od, oh, ow, off)) v[e] = src[off];
+                    cur.next(g);
+                }
+            }
+        }
+        uint8_t *blk_base = dst + (tile * kblocks_total + kb) * kI8BlockBytes;
+        *reinterpret_cast<uint4 *>(blk_base + sw128_byte(r, c * 16)) = *reinterpret_cast<const uint4 *>(v);
+    }
+}
+
+// Plain im2col matrix: channel-last [rows, k] (consecutive threads along k = along the input's channels), channel-first
+// [k, rows] (consecutive threads along the output positions).
+template <bool CF>
+__global__ void __launch_bounds__(256) im2col_i8_kernel(ConvGeom g, const int8_t *__restrict__ src, int8_t *__restrict__ dst, size_t total)
+{
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        uint32_t pos, k;
+        if (CF) {
+            k = (uint32_t)(idx / g.rows);
+            pos = (uint32_t)(idx - (size_t)k * g.rows);
+        } else {
+            pos = (uint32_t)(idx / g.k);
+            k = (uint32_t)(idx - (size_t)pos * g.k);
+        }
+        uint32_t od, oh, ow;
+        split_position(g, pos, od, oh, ow);
+        KCursor<CF> cur;
+        cur.seek(g, k);
+        size_t off;
+        dst[idx] = cur.source(g, od, oh, ow, off) ? src[off] : (int8_t)0;
+    }
+}
+
+inline unsigned grid_for(size_t items)
+{
+    const size_t blocks = (items + 255) / 256;
+    return (unsigned)(blocks > 148 * 64 ? 148 * 64 : blocks);
+}
+
+}  // namespace
+
+Result launch_im2col_pack_i8(void *stream, const ConvGeom &g, bool channel_first, const void *activation, size_t ld_packed,
+                             void *packed)
+{
+    if (g.rows == 0 || g.k == 0) return Result{kOk, 0};
+    const size_t kblocks = ceil_div(g.k, 128), kblocks_total = ceil_div(ld_packed, 128);
+    if (kblocks_total < kblocks) return Result{kInvalid, 0};
+    const size_t chunks = ceil_div(g.rows, 128) * kblocks * 1024;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (channel_first) {
+        im2col_pack_i8_kernel<true><<<grid_for(chunks), 256, 0, st>>>(g, (const int8_t *)activation, (uint8_t *)packed, kblocks,
+                                                                     kblocks_total, chunks, 0);
+    } else {
+        const int vec_ok = g.ic_pg % 16 == 0 && g.c_total % 16 == 0 && (reinterpret_cast<uintptr_t>(activation) & 15) == 0;
+        im2col_pack_i8_kernel<false><<<grid_for(chunks), 256, 0, st>>>(g, (const int8_t *)activation, (uint8_t *)packed, kblocks,
+                                                                      kblocks_total, chunks, vec_ok);
+    }
+    return conv_check_launch();
+}
+
+Result launch_im2col_i8(void *stream, const ConvGeom &g, bool channel_first, const void *activation, void *matrix)
+{
+    if (g.rows == 0 || g.k == 0) return Result{kOk, 0};
+    const size_t total = (size_t)g.rows * g.k;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (channel_first)
+        im2col_i8_kernel<true><<<grid_for(total), 256, 0, st>>>(g, (const int8_t *)activation, (int8_t *)matrix, total);
+    else
+        im2col_i8_kernel<false><<<grid_for(total), 256, 0, st>>>(g, (const int8_t *)activation, (int8_t *)matrix, total);
+    return conv_check_launch();
+}
+
+}  // namespace tqt

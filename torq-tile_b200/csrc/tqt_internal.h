@@ -133,6 +133,23 @@ Result launch_gemm_w4a8_unpacked(const GemmCommon &g, const W4A8Params &p, Dtype
 Result launch_gemm_w4a16_unpacked(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td,
                                   float clamp_min, float clamp_max);
 
+// ---- int8 convolution wrappers: im2col ---------------------------------------------------------
+// Geometry of one group of a convolution, every extent checked by the caller to fit 31 bits: index 0 = depth,
+// 1 = height, 2 = width.  rows = output positions, k = kernel volume x channels per group.
+struct ConvGeom {
+    uint32_t in[3], out[3], ker[3], stride[3], dil[3], pad[3];
+    uint32_t c_total;  // channels of the whole input tensor
+    uint32_t ic_pg;    // input channels per group
+    uint32_t c_off;    // first channel of this group
+    uint32_t rows, k;
+};
+// Gather into the packed int8 block layout (rows = output positions).  channel_first: input [C, D, H, W], K order
+// (ic, kd, kh, kw); else input [D, H, W, C], K order (kd, kh, kw, ic).
+Result launch_im2col_pack_i8(void *stream, const ConvGeom &g, bool channel_first, const void *activation, size_t ld_packed,
+                             void *packed);
+// Gather into a plain matrix: [rows, k] for channel-last, [k, rows] for channel-first.
+Result launch_im2col_i8(void *stream, const ConvGeom &g, bool channel_first, const void *activation, void *matrix);
+
 // Reads (and clears) the device-side watchdog word of the current device after synchronising
 // the stream.  0 = no fault.
 int read_device_fault(void *stream);
