@@ -77,6 +77,12 @@ void tqt_cuda_set_output_replicas(const void *local_base, size_t local_bytes, vo
  * GEMM, 1 = HBM-streaming GEMV (m <= 16), 2 = generic CUDA-core kernel (unpacked operands). */
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k);
 
+/* Diagnostic for tests: the kernel family the process's most recent int8 x int8 launch used.  0 = none yet,
+ * 1 = generic CUDA-core kernel, 2 = tcgen05 CTA-pair kernel on packed blocks, 3 = tcgen05 CTA-pair kernel with a
+ * row-major operand fetched by tiled TMA loads (taken when the operand's base address and row stride are
+ * multiples of 16 bytes; other row-major operands run on the generic kernel). */
+int tqt_cuda_debug_last_kernel(void);
+
 /* Test switch: force a kernel path ("auto" | "umma" | "gemv" | "simt") and a tensor-core kernel ("single" |
  * "pair" | "ts"; NULL = automatic) for all later run_gemm calls of the process, replacing what the environment
  * variables TQT_B200_PATH / TQT_B200_UMMA (read once, at the first call) gave.  A forced path that cannot take a

@@ -152,6 +152,11 @@ def debug_set_path(path=None, umma=None) -> None:
     f(None if path is None else path.encode(), None if umma is None else umma.encode())
 
 
+def debug_last_kernel() -> int:
+    """0 none, 1 generic CUDA-core kernel, 2 tcgen05 CTA-pair kernel on packed blocks, 3 the same with tiled TMA loads."""
+    return int(lib().tqt_cuda_debug_last_kernel())
+
+
 def read_device_fault() -> int:
     return int(lib().tqt_cuda_read_device_fault())
 
@@ -577,7 +582,8 @@ EXTENSION_SYMBOLS = (
     ["tqt_cuda_set_stream", "tqt_cuda_get_stream", "tqt_cuda_get_last_status", "tqt_cuda_get_last_cuda_error",
      "tqt_cuda_read_device_fault", "tqt_cuda_version", "tqt_shard_plan_n", "tqt_cuda_kernel_choice_w4a8",
      "tqt_cuda_debug_f16_bits", "tqt_cuda_debug_bf16_bits", "tqt_cuda_debug_set_timing_buffer",
-     "tqt_cuda_debug_stream_read", "tqt_cuda_set_output_replicas", "tqt_cuda_debug_set_path", "tqt_cuda_debug_inject_wait_failure"]
+     "tqt_cuda_debug_stream_read", "tqt_cuda_set_output_replicas", "tqt_cuda_debug_set_path", "tqt_cuda_debug_inject_wait_failure",
+     "tqt_cuda_debug_last_kernel"]
     + [f"tqt_run_quant_pack_qai8dxp_{t}_{VARIANT}" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_quant_qai8dx_{t}_sm100a" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_{n}_{VARIANT}" for n in ("a_unpack_i8", "a_unpack_f16", "bt_unpack_qsi4cxp", "bt_unpack_qsi4c2p")]

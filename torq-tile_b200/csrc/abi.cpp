@@ -501,6 +501,8 @@ void tqt_cuda_set_output_replicas(const void *local_base, size_t local_bytes, vo
 #include "abi_siblings.inc"
 #include "abi_conv.inc"
 
+int tqt_cuda_debug_last_kernel(void) { return last_kernel(); }
+
 int tqt_cuda_kernel_choice_w4a8(size_t m, size_t n, size_t k)
 {
     (void)n;

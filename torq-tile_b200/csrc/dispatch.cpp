@@ -22,6 +22,7 @@ Result simt_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float 
 Result simt_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td, float cmin,
                        float cmax);
 Result umma_gemm_i32(const GemmCommon &g, int32_t cmin, int32_t cmax);
+Result umma_gemm_i32_layouts(const GemmCommon &g, int32_t cmin, int32_t cmax, Layout la, Layout lb);
 Result umma_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmin, int cmax);
 Result umma_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax);
 Result umma_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td, float cmin,
@@ -76,12 +77,22 @@ void set_path_switches(const char *path, const char *umma)
     g_umma.store(parse_umma(umma));
 }
 
+static std::atomic<int> g_last_kernel{0};
+void note_kernel(int family) { g_last_kernel.store(family, std::memory_order_relaxed); }
+int last_kernel() { return g_last_kernel.load(std::memory_order_relaxed); }
+
 static inline bool empty_problem(const GemmCommon &g) { return g.m == 0 || g.n == 0; }
 
 Result launch_gemm_i32(const GemmCommon &g, bool packed, int32_t cmin, int32_t cmax, Path path)
 {
     if (empty_problem(g)) return Result{kOk, 0};
     if (path == Path::Gemv) return Result{kUnsupported, 0};
+    if (!packed && g.k != 0 && path != Path::Simt) {
+        // unpacked operands (A [m, lda], B [k, ldb]): tensor cores through tiled TMA loads when base addresses and row
+        // strides are multiples of 16 bytes, else the generic kernel
+        Result r = umma_gemm_i32_layouts(g, cmin, cmax, Layout::RowMajor, Layout::KMajor);
+        if (r.status != kUnsupported || path == Path::Umma) return r;
+    }
     if (!packed || g.k == 0 || path == Path::Simt) {
         if (path == Path::Umma || g.n_replicas) return Result{kUnsupported, 0};
         return simt_gemm_i32(g, packed, cmin, cmax);

@@ -24,6 +24,8 @@
 // waits are bounded; teardown is a hardware cluster barrier that every path reaches.
 //
 // Reference semantics of the epilogues: see kernels_umma.cu.
+#include <cuda.h>   // tensor-map types and enumerators only: the encode function is looked up at run time
+
 #include <cstdlib>
 #include <type_traits>
 
@@ -49,8 +51,13 @@ constexpr uint32_t kI8Stages = 6;
 constexpr uint32_t kI8Threads = 352;   // warp 0 producer (even K steps), warp 1 MMA / relay, warps 2..9 epilogue, warp 10 producer (odd K steps)
 constexpr uint32_t kI8Smem = 1024 + kI8Stages * 32768 + 8 * 3 * 128 * 4 + 256;
 
-template <EpiKind EK, Dtype TD = Dtype::F32>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_pair_i8_kernel(const UmmaArgs args)
+// TMA = true: an operand whose args.a_src / args.b_src is not kSrcBlocks comes straight from the caller's row-major
+// matrix through a tiled TMA load (one 128 x 128-byte box per stage, 128-byte swizzle: the box lands in exactly the
+// layout a packed block has); cells outside the matrix read as zero, so ragged edges need no packing either.  A
+// K-major box ([rows, k], k contiguous) is what a packed block holds; an MN-major box of B ([k, n], n contiguous)
+// is consumed with the instruction descriptor's b_major bit and K slices 32 rows (4 KiB) apart.
+template <EpiKind EK, Dtype TD, bool TMA>
+__device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOperands *maps)
 {
     using OutT = typename OutType<EK, TD>::type;
     constexpr uint32_t S = kI8Stages;
@@ -112,7 +119,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs) {
             uint32_t pm, tn;
             tile_coords(t, pmc, tnc, args.band_m, pm, tn);
-            const uint32_t nblk = min(2u, nblocks - tn * 2);
+            const bool b_tma = TMA && args.b_src != kSrcBlocks, a_tma = TMA && args.a_src != kSrcBlocks;
+            const uint32_t nblk = b_tma ? 2u : min(2u, nblocks - tn * 2);   // a box beyond the matrix is zeros
             const uint32_t mtile = pm * 2 + rank;
             const bool a_valid = mtile < tiles_m;
             const uint32_t b_bytes = nblk == 2 ? 16384u : 8192u;
@@ -129,11 +137,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                 }
                 if (lane == 0) ptx::mbar_arrive_expect_tx(BAR(kFull + s), (a_valid ? 16384u : 0u) + b_bytes);
                 __syncwarp();
-                // two lanes issue one bulk copy each in the same instruction
+                // two lanes issue one copy each in the same instruction
                 if (lane == 0) {
-                    ptx::bulk_g2s(ptx::smem_u32(sB + s * 16384), b_src + (size_t)kb * bbb, b_bytes, BAR(kFull + s));
+                    if (b_tma) {
+                        const int32_t rows0 = (int32_t)((tn * 2 + rank) * 128u), k0 = (int32_t)(kb * 128u);
+                        if (args.b_src == kSrcTmaMn)
+                            ptx::tma_load_2d(ptx::smem_u32(sB + s * 16384), &maps->b, rows0, k0, BAR(kFull + s));
+                        else
+                            ptx::tma_load_2d(ptx::smem_u32(sB + s * 16384), &maps->b, k0, rows0, BAR(kFull + s));
+                    } else {
+                        ptx::bulk_g2s(ptx::smem_u32(sB + s * 16384), b_src + (size_t)kb * bbb, b_bytes, BAR(kFull + s));
+                    }
                 } else if (lane == 1 && a_valid) {
-                    ptx::bulk_g2s(ptx::smem_u32(sA + s * 16384), a_src + (size_t)kb * kI8BlockBytes, 16384u, BAR(kFull + s));
+                    if (a_tma)
+                        ptx::tma_load_2d(ptx::smem_u32(sA + s * 16384), &maps->a, (int32_t)(kb * 128u), (int32_t)(mtile * 128u),
+                                         BAR(kFull + s));
+                    else
+                        ptx::bulk_g2s(ptx::smem_u32(sA + s * 16384), a_src + (size_t)kb * kI8BlockBytes, 16384u, BAR(kFull + s));
                 }
                 __syncwarp();
             }
@@ -161,7 +181,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
         // stage landed) have completed is tested after this step's MMAs and read after its commit, which takes the
         // latency of the test (~200 cycles even on a long-completed phase) off the critical path.
         if (lane == 0) {
-            const uint32_t idesc256 = ptx::make_idesc(2u, 1u, 1u, 256, 256);
+            const bool b_mn = TMA && args.b_src == kSrcTmaMn;
+            const uint32_t idesc256 = ptx::make_idesc(2u, 1u, 1u, 256, 256) | (b_mn ? ptx::kIdescBMajorMn : 0u);
             const uint32_t idesc128 = ptx::make_idesc(2u, 1u, 1u, 256, 128);
             const uint64_t a_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sA)), b_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sB));
             const uint32_t a_lo0 = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
@@ -171,7 +192,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
             for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
                 uint32_t pm_unused, tn;
                 tile_coords(t, pmc, tnc, args.band_m, pm_unused, tn);
-                const uint32_t nblk = min(2u, nblocks - tn * 2);
+                const uint32_t nblk = (TMA && args.b_src != kSrcBlocks) ? 2u : min(2u, nblocks - tn * 2);
                 const uint32_t idesc = nblk == 2 ? idesc256 : idesc128;
                 const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
                 if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
@@ -186,7 +207,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                         break;
                     }
                     ptx::tc_fence_after();
-                    ptx::mma_i8_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);   // 16 KiB stages = 1024 units
+                    if (b_mn)
+                        ptx::mma_i8_ss_pair_group4<256>(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
+                    else
+                        ptx::mma_i8_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);   // 16 KiB stages = 1024 units
                     // the next step's stage (a phase seen complete stays complete until this thread commits it free again)
                     const uint32_t s1 = s + 1u == S ? 0u : s + 1u, ph1 = s + 1u == S ? ph ^ 1u : ph;
                     const bool next_ready = ptx::mbar_test_wait(BAR(kFull + s1), ph1) && ptx::mbar_test_wait(BAR(kPeerFull + s1), ph1);
@@ -248,7 +272,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
                 for (uint32_t c = lane; c < 128u; c += 32u) {
                     const bool cok = c < ncols;
                     int32_t rsum = 0;
-                    if (cok) {
+                    if (TMA && args.b_src == kSrcTmaK) {
+                        // row-major B [n, ldb] carries no row sums: add up the row (16-byte aligned by the tensor map's rules)
+                        if (cok) {
+                            const uint8_t *brow = args.B + (size_t)(n0 + c) * args.b_ld;
+                            uint32_t kk = 0;
+                            for (; kk + 16u <= args.k; kk += 16u) {
+                                const uint4 v = *reinterpret_cast<const uint4 *>(brow + kk);
+                                rsum = __dp4a((int)v.x, 0x01010101, rsum);
+                                rsum = __dp4a((int)v.y, 0x01010101, rsum);
+                                rsum = __dp4a((int)v.z, 0x01010101, rsum);
+                                rsum = __dp4a((int)v.w, 0x01010101, rsum);
+                            }
+                            for (; kk < args.k; ++kk) rsum += (int32_t)(int8_t)brow[kk];
+                        }
+                    } else if (cok) {
                         const uint8_t *tail = args.B + (size_t)blk * args.b_kblocks_total * args.b_block_bytes + kI8BlockBytes + c * 2u;
                         for (uint32_t kb = 0; kb < KB; ++kb)
                             rsum += (int32_t) * reinterpret_cast<const int16_t *>(tail + (size_t)kb * args.b_block_bytes);
@@ -375,6 +413,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_
         ptx::tc_fence_after();
         ptx::tmem_dealloc_pair(tmem_base, 512);
     }
+}
+
+template <EpiKind EK, Dtype TD = Dtype::F32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1) gemm_pair_i8_kernel(const UmmaArgs args)
+{
+    pair_i8_body<EK, TD, false>(args, nullptr);
+}
+
+// Operands in the caller's own row-major layouts: the tensor maps travel as a kernel parameter.
+template <EpiKind EK, Dtype TD = Dtype::F32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kI8Threads, 1)
+    gemm_pair_i8_tma_kernel(const UmmaArgs args, const __grid_constant__ TmaOperands maps)
+{
+    pair_i8_body<EK, TD, true>(args, &maps);
 }
 
 // ======================================================================================================
@@ -1003,9 +1055,9 @@ __global__ void __launch_bounds__(kTsThreads, 1) gemm_ts_kernel(const UmmaArgs a
 }
 
 // ---- host side ------------------------------------------------------------------------------------------
-template <class Kern>
+template <class Kern, class... Extra>
 static Result launch_grid(Kern kern, const UmmaArgs &a, uint32_t num_tiles, bool pair, uint32_t threads, uint32_t smem,
-                          cudaStream_t st, bool *attr_set)
+                          cudaStream_t st, bool *attr_set, const Extra &...extra)
 {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1037,7 +1089,7 @@ static Result launch_grid(Kern kern, const UmmaArgs &a, uint32_t num_tiles, bool
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;   // only kernels that execute griddepcontrol.wait set pdl
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a, extra...);
     if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
     return Result{kOk, 0};
 }
@@ -1062,8 +1114,77 @@ Result pair_gemm_i8(const UmmaArgs &a, bool requant, cudaStream_t st)
 {
     const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
     static bool set_s32[64] = {false}, set_req[64] = {false};
+    note_kernel(kKernelPairBlocks);
     if (requant) return launch_grid(gemm_pair_i8_kernel<EpiKind::Req8>, a, tiles, true, kI8Threads, kI8Smem, st, set_req);
     return launch_grid(gemm_pair_i8_kernel<EpiKind::S32>, a, tiles, true, kI8Threads, kI8Smem, st, set_s32);
+}
+
+// ---- tensor maps for row-major operands -------------------------------------------------------------------
+// cuTensorMapEncodeTiled is a driver entry point: it is looked up through the runtime, so the library links no driver
+// library and still loads on machines without one.
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                   const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn()
+{
+    static const EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// int8 matrix [outer, inner] with `inner` contiguous and rows `stride` bytes apart, read in boxes of 128 x 128 bytes
+// with the 128-byte swizzle.  The base and the stride must be multiples of 16 bytes.
+static bool encode_i8_map(TmaDesc *out, const void *base, size_t inner, size_t outer, size_t stride)
+{
+    static_assert(sizeof(CUtensorMap) == sizeof(TmaDesc), "tensor map size");
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || (reinterpret_cast<uintptr_t>(base) & 15) || (stride & 15) || stride == 0 || inner == 0 || outer == 0 ||
+        inner > 0xffffffffull || outer > 0xffffffffull)
+        return false;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {stride};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(reinterpret_cast<CUtensorMap *>(out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box,
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// int8 x int8 with at least one operand in the caller's row-major layout.  a.a_src / a.b_src say how each operand is
+// stored; a.A / a.lda_elems (a.B / a.ldb_elems) describe the row-major ones.  kUnsupported when a matrix cannot be
+// described by a tensor map (base or row stride not a multiple of 16 bytes): the caller falls back to the generic kernel.
+Result pair_gemm_i8_tma(const UmmaArgs &a_in, EpiKind ek, Dtype td, size_t lda, size_t ldb, cudaStream_t st)
+{
+    UmmaArgs a = a_in;
+    a.b_ld = ldb;
+    TmaOperands maps{};
+    if (a.a_src == kSrcTmaK && !encode_i8_map(&maps.a, a.A, a.k, a.m, lda)) return Result{kUnsupported, 0};
+    if (a.b_src == kSrcTmaK && !encode_i8_map(&maps.b, a.B, a.k, a.n, ldb)) return Result{kUnsupported, 0};
+    if (a.b_src == kSrcTmaMn && !encode_i8_map(&maps.b, a.B, a.n, a.k, ldb)) return Result{kUnsupported, 0};
+    const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
+    static bool set_s32[64] = {false}, set_req[64] = {false}, set_row[64] = {false}, set_f32[64] = {false}, set_f16[64] = {false};
+    note_kernel(kKernelPairTma);
+    switch (ek) {
+        case EpiKind::DxCx:
+            if (a.b_src == kSrcTmaMn) return Result{kUnsupported, 0};   // the row sums are taken along rows of B^T
+            if (td == Dtype::F32)
+                return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::DxCx, Dtype::F32>, a, tiles, true, kI8Threads, kI8Smem, st, set_f32, maps);
+            if (td == Dtype::F16)
+                return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::DxCx, Dtype::F16>, a, tiles, true, kI8Threads, kI8Smem, st, set_f16, maps);
+            return Result{kUnsupported, 0};
+        case EpiKind::S32: return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::S32>, a, tiles, true, kI8Threads, kI8Smem, st, set_s32, maps);
+        case EpiKind::Req8: return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::Req8>, a, tiles, true, kI8Threads, kI8Smem, st, set_req, maps);
+        case EpiKind::Req8Row:
+            return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::Req8Row>, a, tiles, true, kI8Threads, kI8Smem, st, set_row, maps);
+        default: return Result{kUnsupported, 0};
+    }
 }
 
 template <TsKind KD, Dtype TD>

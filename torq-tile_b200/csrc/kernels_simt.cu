@@ -129,6 +129,7 @@ static Result run_simt(const GemmCommon &g, LA la, LB lb, Epi epi)
     if (gy > 65535 || gx > 0x7fffffffull) return Result{kUnsupported, 0};
     dim3 grid((unsigned)gx, (unsigned)gy);
     gemm_simt_i8_kernel<LA, LB, Epi, RSUM><<<grid, 256, 0, (cudaStream_t)g.stream>>>(g.m, g.n, g.k, la, lb, epi);
+    note_kernel(kKernelSimt);
     return check_launch();
 }
 
@@ -193,9 +194,19 @@ static Result run_simt_layouts(const GemmCommon &g, Layout la, Layout lb, Epi ep
     });
 }
 
+Result umma_gemm_requant_i8_layouts(const GemmCommon &g, const RequantParams &p, int cmin, int cmax, Layout la, Layout lb);
+Result umma_gemm_requant_rows_i8_layouts(const GemmCommon &g, const RowRequantParams &p, int cmin, int cmax, Layout la,
+                                         Layout lb);
+
 Result launch_gemm_requant_i8_layouts(const GemmCommon &g, const RequantParams &p, int cmin, int cmax, Layout la,
                                       Layout lb)
 {
+    // a row-major operand whose base and row stride are multiples of 16 bytes: tensor cores through tiled TMA loads
+    // (TQT_B200_PATH=simt keeps the generic kernel, for cross-checks; it also takes what a tensor map cannot describe)
+    if (g.m && g.n && g.k && env_path() != Path::Simt) {
+        Result r = umma_gemm_requant_i8_layouts(g, p, cmin, cmax, la, lb);
+        if (r.status != kUnsupported) return r;
+    }
     EpiRequant epi{(const int32_t *)g.C, g.ldc, (const int32_t *)g.bias, (int8_t *)g.D, g.ldd, p.scale_a, p.scale_b,
                    p.quant_channel_b, p.scale_d, p.zero_point_d, cmin, cmax};
     return run_simt_layouts<EpiRequant, false>(g, la, lb, epi);
@@ -211,12 +222,17 @@ Result launch_gemm_requant_rows_i8(const GemmCommon &g, const RowRequantParams &
         Result r = umma_gemm_requant_rows_i8(g, p, cmin, cmax);
         if (r.status != kUnsupported) return r;
     }
+    if (g.m && g.n && g.k && env_path() != Path::Simt) {   // a row-major operand: tiled TMA loads, where a tensor map can describe it
+        Result r = umma_gemm_requant_rows_i8_layouts(g, p, cmin, cmax, la, lb);
+        if (r.status != kUnsupported) return r;
+    }
     EpiRequantRow epi{(const int32_t *)g.C, g.ldc, (const int32_t *)g.bias, (int8_t *)g.D, g.ldd, p.scale_a,
                       p.quant_channel_a, p.scale_b, p.scale_d, p.zero_point_d, cmin, cmax};
     return run_simt_layouts<EpiRequantRow, false>(g, la, lb, epi);
 }
 
 Result umma_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax);
+Result umma_gemm_dxcx_layouts(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax, Layout la, Layout lb);
 
 Result launch_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax, Layout la,
                         Layout lb)
@@ -225,6 +241,10 @@ Result launch_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, floa
     // both operands packed: tensor cores (TQT_B200_PATH=simt keeps the generic kernel, for cross-checks)
     if (la == Layout::Packed && lb == Layout::Packed && g.m && g.n && g.k && env_path() != Path::Simt) {
         Result r = umma_gemm_dxcx(g, p, td, cmin, cmax);
+        if (r.status != kUnsupported) return r;
+    }
+    if (la == Layout::RowMajor && lb == Layout::RowMajor && g.m && g.n && g.k && env_path() != Path::Simt) {
+        Result r = umma_gemm_dxcx_layouts(g, p, td, cmin, cmax, la, lb);   // tiled TMA loads, where tensor maps can describe the operands
         if (r.status != kUnsupported) return r;
     }
     const size_t bb = lb == Layout::Packed ? kI8SumBlockBytes : kI8BlockBytes;   // packed B of these types carries row sums

@@ -645,6 +645,76 @@ Result umma_gemm_requant_i8(const GemmCommon &g, const RequantParams &p, int cmi
 Result pair_gemm_i8_rows(const UmmaArgs &a, cudaStream_t st);
 Result pair_gemm_i8_dxcx(const UmmaArgs &a, Dtype td, cudaStream_t st);
 
+// ---- int8 x int8 with row-major operands: tiled TMA loads into the CTA-pair kernel -------------------------------
+Result pair_gemm_i8_tma(const UmmaArgs &a, EpiKind ek, Dtype td, size_t lda, size_t ldb, cudaStream_t st);
+
+// Fills the operand sources for layouts (la, lb); false for combinations the tensor-core kernel does not take
+// (A stored [k, m]; both packed, which the block kernels handle).
+static bool tma_sources(UmmaArgs &a, Layout la, Layout lb)
+{
+    if (la == Layout::KMajor || (la == Layout::Packed && lb == Layout::Packed)) return false;
+    a.a_src = la == Layout::Packed ? kSrcBlocks : kSrcTmaK;
+    a.b_src = lb == Layout::Packed ? kSrcBlocks : lb == Layout::RowMajor ? kSrcTmaK : kSrcTmaMn;
+    return true;
+}
+
+Result umma_gemm_i32_layouts(const GemmCommon &g, int32_t cmin, int32_t cmax, Layout la, Layout lb)
+{
+    UmmaArgs a{};
+    if (!fill_common(a, g, 4, 128, 128) || a.n_replicas || !tma_sources(a, la, lb)) return Result{kUnsupported, 0};
+    a.cmin_i = cmin;
+    a.cmax_i = cmax;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k);
+    return pair_gemm_i8_tma(a, EpiKind::S32, Dtype::F32, g.lda, g.ldb, (cudaStream_t)g.stream);
+}
+
+Result umma_gemm_requant_i8_layouts(const GemmCommon &g, const RequantParams &p, int cmin, int cmax, Layout la, Layout lb)
+{
+    UmmaArgs a{};
+    if (!fill_common(a, g, 1, 128, 128) || a.n_replicas || !tma_sources(a, la, lb)) return Result{kUnsupported, 0};
+    a.cmin_i = cmin;
+    a.cmax_i = cmax;
+    a.rq_scale_a = p.scale_a;
+    a.scale_b = p.scale_b;
+    a.rq_per_tensor = p.quant_channel_b == 1;
+    a.rq_scale_d = p.scale_d;
+    a.rq_zp_d = p.zero_point_d;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k);
+    return pair_gemm_i8_tma(a, EpiKind::Req8, Dtype::F32, g.lda, g.ldb, (cudaStream_t)g.stream);
+}
+
+Result umma_gemm_requant_rows_i8_layouts(const GemmCommon &g, const RowRequantParams &p, int cmin, int cmax, Layout la,
+                                         Layout lb)
+{
+    UmmaArgs a{};
+    if (!fill_common(a, g, 1, 128, 128) || a.n_replicas || !tma_sources(a, la, lb)) return Result{kUnsupported, 0};
+    a.cmin_i = cmin;
+    a.cmax_i = cmax;
+    a.rq_scale_rows = p.scale_a;
+    a.rq_per_tensor = p.quant_channel_a == 1;
+    a.rq_scale_a = p.scale_b;
+    a.rq_scale_d = p.scale_d;
+    a.rq_zp_d = p.zero_point_d;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k);
+    return pair_gemm_i8_tma(a, EpiKind::Req8Row, Dtype::F32, g.lda, g.ldb, (cudaStream_t)g.stream);
+}
+
+// qai8dx x qsi8cx with float output on row-major operands (A [m, lda], B^T [n, ldb]): the epilogue adds up the rows of B
+// for the zero-point correction that the packed blocks carry in their tails.
+Result umma_gemm_dxcx_layouts(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax, Layout la, Layout lb)
+{
+    UmmaArgs a{};
+    if (la != Layout::RowMajor || lb != Layout::RowMajor) return Result{kUnsupported, 0};
+    if (!fill_common(a, g, td == Dtype::F32 ? 4 : 2, 128, 128) || a.n_replicas || !tma_sources(a, la, lb)) return Result{kUnsupported, 0};
+    a.scale_a = p.scale_a;
+    a.zp_a = p.zp_a;
+    a.scale_b = p.scale_b;
+    a.cmin_f = cmin;
+    a.cmax_f = cmax;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k);
+    return pair_gemm_i8_tma(a, EpiKind::DxCx, td, g.lda, g.ldb, (cudaStream_t)g.stream);
+}
+
 // qai8dxp x qsi8cxp with float output on packed operands (B blocks carry their row sums): the CTA-pair kernel.
 Result umma_gemm_dxcx(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
 {

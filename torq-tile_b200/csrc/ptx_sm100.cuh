@@ -136,6 +136,22 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void *src, uin
                  : "memory");
 }
 
+// Tiled TMA load of one 2-D box global -> shared through a tensor map (a 128-byte opaque descriptor the host encodes
+// with cuTensorMapEncodeTiled and passes as a __grid_constant__ kernel parameter), completion as transaction bytes
+// on an mbarrier of this CTA.  x is the coordinate along the contiguous dimension: x times the element size must be a
+// multiple of 16 bytes.  Cells outside the tensor read as zero and still count towards the box's bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void *tensor_map, int32_t x, int32_t y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     dst_smem),
+                 "l"(tensor_map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_map(const void *tensor_map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
+}
+
 // ---- tensor memory --------------------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols)
 {
@@ -209,8 +225,10 @@ __device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t smem_addr)
 }
 
 // Instruction descriptor (dense, no negate, both operands K-major):
-// [4,6) D format (0 f16, 1 f32, 2 s32); [7,10) A format; [10,13) B format; [17,23) N>>3; [24,29) M>>4.
+// [4,6) D format (0 f16, 1 f32, 2 s32); [7,10) A format; [10,13) B format; bit 15 / 16: A / B operand MN-major;
+// [17,23) N>>3; [24,29) M>>4.
 // kind::i8 formats: 0 = u8, 1 = s8.  kind::f16 formats: 0 = f16, 1 = bf16.
+constexpr uint32_t kIdescBMajorMn = 1u << 16;   // N-side operand MN-major (its rows run along K in shared memory)
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n)
 {
     return (d_fmt << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
@@ -375,6 +393,9 @@ __device__ __forceinline__ void mma_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem
 
 // The four K slices of one K step of the CTA-pair SS MMA in one instruction block (only the low words of the two
 // descriptors advance, by two 16-byte units per K slice of 32 bytes).
+// BSTEP: distance between the N-side operand's K slices in 16-byte units: 2 for a K-major stage (32 bytes along a row),
+// 256 for an MN-major one (32 rows of 128 bytes).
+template <uint32_t BSTEP = 2>
 __device__ __forceinline__ void mma_i8_ss_pair_group4(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
                                                       uint32_t idesc, uint32_t accum_first)
 {
@@ -387,15 +408,16 @@ __device__ __forceinline__ void mma_i8_ss_pair_group4(uint32_t d_tmem, uint32_t 
         "setp.eq.b32 pt, 0, 0;\n\t"
         "mov.b64 da, {%1, %2};\n\t mov.b64 db, {%3, %4};\n\t"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, p;\n\t"
-        "add.u32 la, %1, 2;\n\t add.u32 lb, %3, 2;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "add.u32 la, %1, 2;\n\t add.u32 lb, %3, %7;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, pt;\n\t"
-        "add.u32 la, %1, 4;\n\t add.u32 lb, %3, 4;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "add.u32 la, %1, 4;\n\t add.u32 lb, %3, %8;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, pt;\n\t"
-        "add.u32 la, %1, 6;\n\t add.u32 lb, %3, 6;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "add.u32 la, %1, 6;\n\t add.u32 lb, %3, %9;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %5, pt;\n\t"
         "}"
         :
-        : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accum_first)
+        : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accum_first), "n"(BSTEP), "n"(2 * BSTEP),
+          "n"(3 * BSTEP)
         : "memory");
 }
 

@@ -171,6 +171,10 @@ Result stream_read(const void *src, size_t bytes, void *sink, void *stream);
 // unknown word = automatic choice).  umma_variant: 0 automatic, 1 single CTA, 2 CTA pair, 3 single-CTA
 // tensor-memory kernel.
 Path env_path();
+// Diagnostic for tests: which kernel family the most recent int8 x int8 launch of the process used (kKernel*).
+enum : int { kKernelNone = 0, kKernelSimt = 1, kKernelPairBlocks = 2, kKernelPairTma = 3 };
+void note_kernel(int family);
+int last_kernel();
 int umma_variant();
 void set_path_switches(const char *path, const char *umma);
 

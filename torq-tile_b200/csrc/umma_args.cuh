@@ -8,8 +8,23 @@ namespace tqt {
 enum class BMode : int { I8 = 0, I4Cx = 1, I4C2 = 2 };
 enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3, Req8Row = 4, DxCx = 5 };
 
+// How the int8 CTA-pair kernel fetches an operand: packed 16 KiB blocks by untiled bulk copies, or boxes of the caller's
+// row-major matrix by tiled TMA loads (K-major: k contiguous; MN-major, B only: n contiguous).
+enum : uint32_t { kSrcBlocks = 0, kSrcTmaK = 1, kSrcTmaMn = 2 };
+
+// A tensor map (the driver's opaque 128-byte descriptor, 64-byte aligned) per operand, passed as a __grid_constant__
+// kernel parameter.
+struct alignas(64) TmaDesc {
+    uint64_t opaque[16];
+};
+struct TmaOperands {
+    TmaDesc a, b;
+};
+
 struct UmmaArgs {
     uint32_t m, n, k;
+    uint32_t a_src, b_src;     // kSrc*: int8 CTA-pair kernel with tensor maps only
+    size_t b_ld;               // row stride (bytes) of a row-major B fetched through a tensor map
     const uint8_t *A;
     const uint8_t *B;
     uint32_t a_kblocks_total;  // blocks per row-tile in the A buffer
