@@ -236,8 +236,8 @@ ISSUE_RATE_INT8_TOPS = 2.0 * 128 * 192 * 32 / 102.5 * 148 * 1.965e9 / 1e12   # 4
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE run_gemm launch from the ncu captures summarised under
 # profiles/ (file named beside each figure): taken under ncu on an earlier run of the same kernels, NOT measured by
 # the run that prints the line.
-NCU_TRAFFIC = {"c3": (56.2e6, "profiles/gemm_ts_pair_w4a8_c3.txt"), "c4": (33.9e6, "profiles/gemm_pair_i8_c4.txt"),
-               "c5": (1419.1e6, "profiles/gemm_ts_pair_w4a16_c5.txt")}
+NCU_TRAFFIC = {"c3": (56.4e6, "profiles/gemm_ts_pair_w4a8_c3.txt"), "c4": (33.8e6, "profiles/gemm_pair_i8_c4.txt"),
+               "c5": (1561.0e6, "profiles/gemm_ts_pair_w4a16_c5.txt")}
 
 
 def algorithmic_bytes(cfg, n_local):
@@ -620,6 +620,55 @@ def bench_layout(torch, pkg, dev, peaks):
     out["quant_pack_qai8dxp_bf16"] = {"workload": f"tqt_run_quant_pack_qai8dxp_bf16 M={M} K={K}", "us": us, "bytes": nbytes,
                                       "gbs": nbytes / (us * 1e-6) / 1e9, "frac": nbytes / (us * 1e-6) / 1e9 / peaks["hbm"]}
     out["note"] = f"bytes in + bytes out per launch / CUDA-event time over rotating buffer sets (> 126 MB); frac of hbm_gbs of {peaks['source']}"
+    del acts, ap
+    out.update(bench_unpacked_and_conv(torch, pkg, dev, peaks, time_us))
+    return out
+
+
+def bench_unpacked_and_conv(torch, pkg, dev, peaks, time_us):
+    """C1's kernel type on row-major operands (tiled TMA loads into the tcgen05 CTA-pair kernel): the reference's own
+    CPU-runnable case (M=64, K=512, N=256) as a latency, and M=K=N=4096 as int8 TOPS; and one layer-sized int8
+    convolution through the packed channel-last wrapper (fused im2col + pack, then the requantising GEMM)."""
+    out = {}
+    uk = pkg.GemmClampI32I8I8()
+    for (M, K, N, sets, reps) in ((64, 512, 256, 8, 20), (4096, 4096, 4096, 6, 3)):
+        A = [torch.randint(-128, 128, (M, K), device=dev, dtype=torch.int8) for _ in range(sets)]
+        B = [torch.randint(-128, 128, (K, N), device=dev, dtype=torch.int8) for _ in range(sets)]
+        D = [torch.empty((M, N), device=dev, dtype=torch.int32) for _ in range(sets)]
+        us = time_us(lambda i: uk.run_gemm(M, N, K, A[i], K, 0, B[i], N, 0, None, N, D[i], N, -2**31, 2**31 - 1), sets, reps=reps)
+        rec = {"workload": f"gemm_clamp_i32_i8_i8 M={M} K={K} N={N}, row-major operands (A [m,k], B [k,n]) through tensor maps",
+               "us": us, "tops": 2.0 * M * N * K / (us * 1e-6) / 1e12, "kernel_family": pkg.debug_last_kernel()}
+        if M == 4096:
+            rec["frac"] = rec["tops"] / (2.0 * peaks["bf16"])
+            rec["note"] = "frac of 2 x bf16_tflops (burst); sets rotate through 302 MB"
+        else:
+            rec["note"] = "launch-latency bound: one tile on one CTA pair"
+        out["c1_i32_unpacked" if M == 64 else "i32_unpacked_4096"] = rec
+        del A, B, D
+    # 56 x 56 x 256 -> 256 channels, 3 x 3, pad 1 (M = 3136, K = 2304, N = 256), batch of 8 images as 8 groups of rows
+    ck = pkg.ConvI8(pkg.CONV_TYPES[0])
+    IC = OC = 256
+    cp = pkg.ConvParams.make(IC, OC, 1, (8, 56, 56), (1, 3, 3), pad=(0, 1, 1))
+    Mc, Kc = 8 * 56 * 56, 9 * IC
+    sets = 6
+    acts = [torch.randint(-128, 128, (8 * 56 * 56 * IC,), device=dev, dtype=torch.int8) for _ in range(sets)]
+    W = torch.randint(-127, 128, (OC, Kc), device=dev, dtype=torch.int8)
+    wp = torch.empty(ck.get_b_packed_size(OC, Kc), dtype=torch.uint8, device=dev)
+    ck.run_bt_pack(OC, Kc, Kc, Kc, 0, W, wp)
+    ap = [torch.empty(ck.get_a_im2colpack_size(Mc, Kc), dtype=torch.uint8, device=dev) for _ in range(sets)]
+    D = [torch.empty((Mc, OC), device=dev, dtype=torch.int8) for _ in range(sets)]
+    sb = torch.full((OC,), 0.004, device=dev, dtype=torch.float32)
+    bias = torch.zeros(OC, device=dev, dtype=torch.int32)
+    qp = pkg.QaI8QaI8QsI8CxParams(0.05, 0, sb.data_ptr(), OC, 2.0, 0)
+    us_col = time_us(lambda i: ck.run_im2colpack(0, acts[i], Kc, 0, ap[i], cp), sets)
+    us_all = time_us(lambda i: (ck.run_im2colpack(0, acts[i], Kc, 0, ap[i], cp),
+                                ck.run_conv(Mc, OC, Kc, ap[i], Kc, 0, wp, Kc, 0, None, OC, D[i], OC, bias, -128, 127, qp)), sets)
+    nbytes = acts[0].numel() + ap[0].numel()
+    out["conv_i8_channel_last_packed"] = {
+        "workload": "convcl_1xnbias_reqi32toi8_clamp_qai8_qai8p_qsi8cxp: 8 x 56 x 56 x 256 -> 256 channels, 3 x 3, pad 1 (M=25088, K=2304, N=256)",
+        "im2colpack_us": us_col, "im2colpack_gbs": nbytes / (us_col * 1e-6) / 1e9, "im2colpack_frac": nbytes / (us_col * 1e-6) / 1e9 / peaks["hbm"],
+        "conv_us": us_all, "tops": 2.0 * Mc * OC * Kc / (us_all * 1e-6) / 1e12,
+        "note": "im2colpack bytes = input tensor + packed matrix; conv = im2colpack + run_conv, int8 TOPS of the whole convolution"}
     return out
 
 
@@ -688,7 +737,7 @@ def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20
                              "note": "a kernel with the GEMV's launch shape that only reads the same bytes, same graph"},
             "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm"], "unit": "GB/s",
                          "frac": gbs / peaks["hbm"], "algorithmic_bytes": nbytes,
-                         "traffic": 8.698e6 if (K, N, M) == (4096, 4096, 1) else None,
+                         "traffic": 8.702e6 if (K, N, M) == (4096, 4096, 1) else None,
                          "traffic_source": ("ncu capture of an earlier run summarised in profiles/gemv_w4a8_c2.txt (one launch, dram "
                                             "read + write); not measured by this run") if (K, N, M) == (4096, 4096, 1) else None,
                          "note": f"CUDA-graph replay of {copies} back-to-back GEMVs over distinct weights; peak = hbm_gbs of {peaks['source']}"}}

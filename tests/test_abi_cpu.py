@@ -178,6 +178,14 @@ def test_conv_wrappers_without_gpu(pkg, tmp_path):
                        (pkg.CONV_TYPES[3], ("get_m_step get_n_step get_a_packed_offset get_b_im2colpack_offset get_c_offset get_bias_offset "
                                             "get_d_offset get_d_size get_a_packed_size get_b_im2colpack_size run_a_pack run_b_im2colpack run_conv"))):
         tables.append(f"    struct tqt_{t}_ukernel u{len(tables)} = {{" + ", ".join(f"tqt_{m}_{t}{S}" for m in members.split()) + "};")
+    for t, members in ((pkg.IGEMM_TYPES[0], "get_m_step get_n_step get_b_packed_offset get_c_offset get_bias_offset get_d_offset get_d_size "
+                                            "get_b_packed_size run_bt_pack run_igemm"),
+                       (pkg.IGEMM_TYPES[1], "get_m_step get_n_step get_b_offset get_c_offset get_bias_offset get_d_offset get_d_size run_igemm"),
+                       (pkg.IGEMM_TYPES[2], "get_m_step get_n_step get_a_offset get_c_offset get_bias_offset get_d_offset get_d_size run_igemm"),
+                       (pkg.IGEMM_TYPES[3], "get_m_step get_n_step get_a_packed_offset get_c_offset get_bias_offset get_d_offset get_d_size "
+                                            "get_a_packed_size run_a_pack run_igemm")):
+        tables.append(f"    struct tqt_{t}_ukernel u{len(tables)} = {{" + ", ".join(f"tqt_{m}_{t}{S}" for m in members.split()) + "};")
+    tables.append("    if (!(u4.run_igemm && u5.run_igemm && u6.run_igemm && u7.run_a_pack)) return 1;")
     src = tmp_path / "conv_tables.c"
     src.write_text('#include "tqt_b200_conv_i8_i8.h"\nint main(void) {\n' + "\n".join(tables) +
                    "\n    return (int)u0.get_m_step() + (u1.run_conv && u2.run_im2col && u3.run_b_im2colpack);\n}\n")

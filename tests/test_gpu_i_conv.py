@@ -130,6 +130,63 @@ def test_conv_requant(oracle, golden, idx, type_idx):
     assert cosine(deq, case["real"]) >= 0.999
 
 
+@pytest.mark.parametrize("type_idx", range(4))
+@pytest.mark.parametrize("idx", range(N_CASES))
+def test_igemm_requant(oracle, golden, idx, type_idx):
+    """The implicit-GEMM types: no im2col matrix; the whole output in one call and, for larger cases, as two calls that
+    split the output positions (the reference's m_idx / n_idx tile portions: D stays the base of the whole output)."""
+    p = pkg()
+    p.use_current_torch_stream()
+    geom, group_idx = conv_geometry_from_golden(golden[f"conv_{idx}_geom"])
+    uk = p.IgemmI8(p.IGEMM_TYPES[type_idx])
+    cf = uk.channel_first
+    case = conv_acceptance_case(oracle, geom, cf, group_idx)
+    col = oracle.im2col_i8(case["act"], geom, cf, group_idx)
+    rows, k, oc = geom.rows, geom.k, geom.output_channel // geom.groups
+    cp = _params(p, geom)
+    act, W, fused, s_w = to_dev(case["act"]), to_dev(case["W"]), to_dev(case["bias_fused"]), to_dev(case["scale_w"])
+    if uk.packed:
+        size = uk.get_a_packed_size(oc, k) if cf else uk.get_b_packed_size(oc, k)
+        wbuf = torch.zeros(size, dtype=torch.uint8, device=DEV)
+        (uk.run_a_pack if cf else uk.run_bt_pack)(oc, k, k, k, 0, W, wbuf)
+    else:
+        wbuf = W
+    if cf:
+        want = oracle.gemm_mx1bias_reqi32toi8(case["W"], col, case["scale_w"], case["scale_act"], case["scale_d"], case["zp_d"],
+                                              case["bias_fused"])
+        params = p.QaI8QsI8DxQaI8Params(s_w.data_ptr(), oc, case["scale_act"], case["zp_act"], case["scale_d"], case["zp_d"])
+        d = torch.full((oc, rows), 99, dtype=torch.int8, device=DEV)
+        splits = [(0, rows)] if rows < 8 else [(0, rows // 2), (rows // 2, rows - rows // 2)]
+        for p0, cnt in splits:
+            uk.run_igemm(oc, cnt, k, act, group_idx, p0, wbuf, k, d, rows, fused, -128, 127, cp, params)
+    else:
+        want = oracle.gemm_reqi32toi8(col, case["W"], True, case["scale_act"], case["scale_w"], case["scale_d"], case["zp_d"],
+                                      case["bias_fused"])
+        params = p.QaI8QaI8QsI8CxParams(case["scale_act"], case["zp_act"], s_w.data_ptr(), oc, case["scale_d"], case["zp_d"])
+        d = torch.full((rows, oc), 99, dtype=torch.int8, device=DEV)
+        splits = [(0, rows)] if rows < 8 else [(0, rows // 2), (rows // 2, rows - rows // 2)]
+        for p0, cnt in splits:
+            uk.run_igemm(cnt, oc, k, act, group_idx, p0, wbuf, k, d, oc, fused, -128, 127, cp, params)
+    sync_and_check()
+    got = d.cpu().numpy()
+    assert np.array_equal(got, want)
+    deq = (got.astype(np.float32) - np.float32(case["zp_d"])) * np.float32(case["scale_d"])
+    assert np.max(np.abs(deq - case["real"])) <= 1.0 and cosine(deq, case["real"]) >= 0.999
+
+
+def test_igemm_argument_checks():
+    p = pkg()
+    p.use_current_torch_stream()
+    uk = p.IgemmI8(p.IGEMM_TYPES[1])
+    cp = p.ConvParams.make(4, 8, 1, (1, 4, 4), (1, 3, 3))          # 2 x 2 = 4 output positions, K = 36
+    buf = torch.zeros(256, dtype=torch.int8, device=DEV)
+    qp = p.QaI8QaI8QsI8CxParams(0.1, 0, buf.data_ptr(), 8, 0.1, 0)
+    with pytest.raises(p.TqtError):
+        uk.run_igemm(4, 8, 36, buf, 0, 2, buf, 36, buf, 8, None, -128, 127, cp, qp)    # positions 2 .. 6 of 4
+    uk.run_igemm(4, 8, 36, buf, 0, 0, buf, 36, buf, 8, None, -128, 127, None, qp)       # null geometry: silent
+    uk.run_igemm(4, 8, 36, buf, 0, 0, buf, 36, buf, 8, None, -128, 127, cp, None)
+
+
 def test_conv_layer_sized(oracle):
     """A layer-sized channel-last convolution (56 x 56 x 64 -> 128 channels, 3 x 3, pad 1: M = 3136, K = 576) through the
     packed wrapper: 128-bit gather path and the CTA-pair GEMM, whole output against the oracle."""

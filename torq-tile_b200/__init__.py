@@ -527,6 +527,49 @@ class ConvI8(_UKernel):
         check("run_conv " + self.type_name)
 
 
+IGEMM_TYPES = ("igemmcl_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp", "igemmcl_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxt",
+               "igemmcf_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8", "igemmcf_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8")
+
+
+class IgemmI8(_UKernel):
+    """One of the int8 implicit-GEMM convolution types: run_igemm gathers the activation operand from the input tensor."""
+
+    def __init__(self, type_name: str):
+        self.type_name = type_name
+        self.channel_first = type_name.startswith("igemmcf")
+        self.packed = "qsi8cxp" in type_name or "qsi8dxp" in type_name
+        common = (("get_m_step", 0), ("get_n_step", 0), ("get_c_offset", 3), ("get_bias_offset", 1), ("get_d_offset", 3),
+                  ("get_d_size", 2))
+        if self.channel_first:
+            own = (("get_a_packed_offset", 4), ("get_a_packed_size", 2)) if self.packed else (("get_a_offset", 3),)
+            runs = ["run_a_pack"] if self.packed else []
+        else:
+            own = (("get_b_packed_offset", 4), ("get_b_packed_size", 2)) if self.packed else (("get_b_offset", 3),)
+            runs = ["run_bt_pack"] if self.packed else []
+        self.helpers_size = common + own
+        self.actions = [h[0] for h in self.helpers_size] + runs + ["run_igemm"]
+        self.params_cls = QaI8QsI8DxQaI8Params if self.channel_first else QaI8QaI8QsI8CxParams
+        super().__init__()
+
+    def run_a_pack(self, m, k, ldw, ldw_packed, k_idx, W, W_packed):
+        self._pack("run_a_pack", m, k, ldw, ldw_packed, k_idx, W, W_packed)
+
+    def run_bt_pack(self, n, k, ldw, ldw_packed, k_idx, W, W_packed):
+        self._pack("run_bt_pack", n, k, ldw, ldw_packed, k_idx, W, W_packed)
+
+    def run_igemm(self, m, n, k, inp, group_idx, pos_idx, weights, ldw, D, ldd, bias, clamp_min, clamp_max, conv_params,
+                  quant_params):
+        """pos_idx: first output position of the call (m_idx for channel-last, n_idx for channel-first)."""
+        f = self._sym("run_igemm")
+        f.argtypes = [_sz, _sz, _sz, _vp, _sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, C.c_int8, C.c_int8,
+                      C.POINTER(ConvParams), C.POINTER(self.params_cls)]
+        f.restype = None
+        f(m, n, k, _addr(inp), group_idx, pos_idx, 0, _addr(weights), ldw, 0, None, 0, _addr(D), ldd, _addr(bias),
+          int(clamp_min), int(clamp_max), None if conv_params is None else C.byref(conv_params),
+          None if quant_params is None else C.byref(quant_params))
+        check("run_igemm " + self.type_name)
+
+
 # ---- extensions ------------------------------------------------------------------------------------
 _TA_NAMES = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}
 
@@ -593,4 +636,4 @@ EXTENSION_SYMBOLS = (
 def all_ukernels():
     return [GemmClampI32I8I8(), GemmClampI32I8pI8p(), GemmReqI8(), GemmW4A8("f32"), GemmW4A8("f16"),
             GemmW4A8("bf16"), GemmW4A16("f16"), GemmW4A16("f32")] + [SiblingGemm(t) for t in SIBLING_TYPES] + \
-           [ConvI8(t) for t in CONV_TYPES]
+           [ConvI8(t) for t in CONV_TYPES] + [IgemmI8(t) for t in IGEMM_TYPES]

@@ -484,6 +484,13 @@ __global__ void __launch_bounds__(256) quant_qai8dx_kernel(size_t m, size_t k, c
     }
 }
 
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi)
+{
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
 // Warp-per-row variant for 16-bit inputs whose rows fit in registers (k <= 4096, k a multiple of 16,
 // 16-byte aligned rows): no block-wide synchronisation, 16 loads of 16 bytes in flight per lane, every
 // row read exactly once.  The per-element division x / s is done as Markstein's correction of
@@ -583,6 +590,8 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
     // (a bf16 row has the f32 exponent range; below about 2.9e-39 the reciprocal overflows) divide instead.
     // Uniform per row, so per warp.
     const bool plain_div = !(s > 7.8886091e-31f && s < 1.2676506e30f);   // outside [2^-100, 2^100]
+    const unsigned long long y2 = pack_f32x2(y, y), ns2 = pack_f32x2(-s, -s), magic2 = pack_f32x2(12582912.0f, 12582912.0f);
+    const int zc = zp - 0x4B400000;   // bits of 1.5 * 2^23
     const size_t tile = row >> 7;
     const uint32_t r = (uint32_t)(row & 127);
     const uint32_t out_chunks = PACKED ? (uint32_t)((k + 127) / 128) * 8u : nchunks;   // packed rows are zero-padded to the block width
@@ -596,21 +605,31 @@ __global__ void __launch_bounds__(256) quant_qai8dx_warp_kernel(size_t m, size_t
             for (uint32_t h = 0; h < 2; ++h) {
                 const uint32_t w[4] = {raw[i][h].x, raw[i][h].y, raw[i][h].z, raw[i][h].w};
                 int v[8];
+                if (plain_div) {
 #pragma unroll
-                for (uint32_t j = 0; j < 4; ++j) {
-                    float x2[2];
-                    widen(w[j], x2[0], x2[1]);
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        float x2[2];
+                        widen(w[j], x2[0], x2[1]);
+                        v[j * 2] = __float2int_rn(__fdiv_rn(x2[0], s)) + zp;
+                        v[j * 2 + 1] = __float2int_rn(__fdiv_rn(x2[1], s)) + zp;
+                    }
+                } else {
+                    // two elements per instruction (packed f32x2 arithmetic, each lane IEEE round-to-nearest): q0 = x * y,
+                    // e = fma(-q0, s, x), q = fma(e, y, q0); then q + 1.5 * 2^23 leaves rint(q) in the low mantissa bits
+                    // (|q| <= 255: the scale is the row's range over 255), so the conversion is an integer subtraction
+                    // folded into the zero point instead of a quarter-rate float-to-int instruction
 #pragma unroll
-                    for (uint32_t e2 = 0; e2 < 2; ++e2) {
-                        float q;
-                        if (plain_div) {
-                            q = __fdiv_rn(x2[e2], s);
-                        } else {
-                            const float q0 = __fmul_rn(x2[e2], y);
-                            const float err = __fmaf_rn(-q0, s, x2[e2]);
-                            q = __fmaf_rn(err, y, q0);
-                        }
-                        v[j * 2 + e2] = __float2int_rn(q) + zp;
+                    for (uint32_t j = 0; j < 4; ++j) {
+                        float x0, x1;
+                        widen(w[j], x0, x1);
+                        const unsigned long long X = pack_f32x2(x0, x1);
+                        unsigned long long q0, e, q, t;
+                        asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q0) : "l"(X), "l"(y2));
+                        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(e) : "l"(q0), "l"(ns2), "l"(X));
+                        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q) : "l"(e), "l"(y2), "l"(q0));
+                        asm("add.rn.f32x2 %0, %1, %2;" : "=l"(t) : "l"(q), "l"(magic2));
+                        v[j * 2] = (int)(uint32_t)t + zc;
+                        v[j * 2 + 1] = (int)(uint32_t)(t >> 32) + zc;
                     }
                 }
                 // saturate to int8 and pack four values per word: element 0 in the lowest byte

@@ -3,6 +3,7 @@
 // without tensor cores so that layout and epilogue code can be checked in isolation.  Operands
 // are fetched through small accessor structs, staged in shared memory as packed int8 words and
 // multiplied with dp4a.
+#include "conv_geom.cuh"
 #include "epilogues.cuh"
 
 namespace tqt {
@@ -46,6 +47,24 @@ struct RowMajorNib {  // [rows, k / 2] bytes, row stride in bytes; byte = (q_hi 
     {
         const uint32_t v = (p[r * ld_bytes + (k >> 1)] >> ((k & 1) * 4)) & 0xFu;
         return (int8_t)((int)v - 8);
+    }
+};
+
+// The im2col view of a convolution input as an operand: element (row = output position - pos0, k) is gathered from the
+// activation tensor on the fly (implicit GEMM: no im2col matrix exists anywhere).
+template <bool CF>
+struct Im2colI8 {
+    const int8_t *p;
+    ConvGeom g;
+    uint32_t pos0;   // output position of row 0 of this call
+    __device__ int8_t get(size_t r, size_t k) const
+    {
+        uint32_t od, oh, ow;
+        split_position(g, pos0 + (uint32_t)r, od, oh, ow);
+        KCursor<CF> cur;
+        cur.seek(g, (uint32_t)k);
+        size_t off;
+        return cur.source(g, od, oh, ow, off) ? p[off] : (int8_t)0;
     }
 };
 
@@ -192,6 +211,33 @@ static Result run_simt_layouts(const GemmCommon &g, Layout la, Layout lb, Epi ep
         return with_i8_layout(lb, g.B, g.ldb,
                               [&](auto b) { return run_simt<decltype(a), decltype(b), Epi, RSUM>(g, a, b, epi); }, b_block_bytes);
     });
+}
+
+// Implicit-GEMM convolutions (the igemm kernel types): the activation operand is the im2col view of `input`, the other
+// operand the weights in `wl` layout (Packed or RowMajor [rows, ld]).  Channel-last: A = im2col (rows = output positions
+// pos0 .. pos0 + m), B = weights [n, k], 1xN-bias requantisation.  Channel-first: A = weights [m, k], B = im2col
+// (columns = output positions pos0 .. pos0 + n), Mx1-bias requantisation.  g.D is the output cell of (row 0, column 0)
+// of this call.  Generic CUDA-core kernel.
+Result launch_igemm_cl_requant_i8(const GemmCommon &g, const ConvGeom &geom, uint32_t pos0, const void *input,
+                                  const RequantParams &p, int cmin, int cmax, Layout wl)
+{
+    if (g.m == 0 || g.n == 0) return Result{kOk, 0};
+    if (wl == Layout::KMajor) return Result{kUnsupported, 0};
+    EpiRequant epi{nullptr, 0, (const int32_t *)g.bias, (int8_t *)g.D, g.ldd, p.scale_a, p.scale_b,
+                   p.quant_channel_b, p.scale_d, p.zero_point_d, cmin, cmax};
+    Im2colI8<false> la{(const int8_t *)input, geom, pos0};
+    return with_i8_layout(wl, g.B, g.ldb, [&](auto b) { return run_simt<Im2colI8<false>, decltype(b), EpiRequant, false>(g, la, b, epi); });
+}
+
+Result launch_igemm_cf_requant_rows_i8(const GemmCommon &g, const ConvGeom &geom, uint32_t pos0, const void *input,
+                                       const RowRequantParams &p, int cmin, int cmax, Layout wl)
+{
+    if (g.m == 0 || g.n == 0) return Result{kOk, 0};
+    if (wl == Layout::KMajor) return Result{kUnsupported, 0};
+    EpiRequantRow epi{nullptr, 0, (const int32_t *)g.bias, (int8_t *)g.D, g.ldd, p.scale_a,
+                      p.quant_channel_a, p.scale_b, p.scale_d, p.zero_point_d, cmin, cmax};
+    Im2colI8<true> lb{(const int8_t *)input, geom, pos0};
+    return with_i8_layout(wl, g.A, g.lda, [&](auto a) { return run_simt<decltype(a), Im2colI8<true>, EpiRequantRow, false>(g, a, lb, epi); });
 }
 
 Result umma_gemm_requant_i8_layouts(const GemmCommon &g, const RequantParams &p, int cmin, int cmax, Layout la, Layout lb);

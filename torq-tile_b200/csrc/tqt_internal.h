@@ -150,6 +150,12 @@ Result launch_im2col_pack_i8(void *stream, const ConvGeom &g, bool channel_first
 // Gather into a plain matrix: [rows, k] for channel-last, [k, rows] for channel-first.
 Result launch_im2col_i8(void *stream, const ConvGeom &g, bool channel_first, const void *activation, void *matrix);
 
+// Implicit-GEMM convolutions: see kernels_simt.cu.
+Result launch_igemm_cl_requant_i8(const GemmCommon &g, const ConvGeom &geom, uint32_t pos0, const void *input,
+                                  const RequantParams &p, int clamp_min, int clamp_max, Layout weights);
+Result launch_igemm_cf_requant_rows_i8(const GemmCommon &g, const ConvGeom &geom, uint32_t pos0, const void *input,
+                                       const RowRequantParams &p, int clamp_min, int clamp_max, Layout weights);
+
 // Reads (and clears) the device-side watchdog word of the current device after synchronising
 // the stream.  0 = no fault.
 int read_device_fault(void *stream);
