@@ -98,6 +98,21 @@ def test_requant_reference_acceptance(oracle, path, m, n, k):
     assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("m,n,k", [(2560, 2176, 256), (4096, 4096, 128), (2560, 2304, 130), (300, 1100, 384)])
+def test_requant_split_tail_wave(oracle, m, n, k):
+    """Launches whose last wave of pair tiles is at most half full run its tiles as two one-block halves each
+    (90 tiles with an odd block count, so one half does not exist; 256 tiles; 90 whole; 10 tiles on a grid enlarged to 20
+    pairs): every output cell against the oracle."""
+    rng = np.random.default_rng(m + n + k)
+    A = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    W = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    sb = rng.uniform(0.001, 0.01, n).astype(np.float32)
+    bias = rng.integers(-1000, 1001, n).astype(np.int32)
+    want = oracle.gemm_reqi32toi8(A, W, True, 0.05, sb, 0.02 * np.sqrt(k), -5, bias)
+    got = run_requant(A, W, 0.05, sb, 0.02 * np.sqrt(k), -5, bias)
+    assert np.array_equal(got, want)
+
+
 def test_requant_options(oracle, path):
     rng = np.random.default_rng(8)
     m, n, k = 130, 260, 200

@@ -51,6 +51,53 @@ constexpr uint32_t kI8Stages = 6;
 constexpr uint32_t kI8Threads = 352;   // warp 0 producer (even K steps), warp 1 MMA / relay, warps 2..9 epilogue, warp 10 producer (odd K steps)
 constexpr uint32_t kI8Smem = 1024 + kI8Stages * 32768 + 8 * 3 * 128 * 4 + 256;
 
+// Work items of the int8 CTA-pair kernel.  Item w is a pair tile (256 x 256: two 128-column blocks of the N side), except
+// that the tiles of a last, at most half-full wave are split into two items of one block each (256 x 128): a one-block
+// MMA costs ~0.6 of a two-block one, so the tail wave takes 0.6 of a full wave's time instead of all of it, on twice as
+// many CTA pairs.  No reduction is involved: the halves are independent output columns.
+struct I8Work {
+    uint32_t pm;     // pair row-tile
+    uint32_t bn0;    // first 128-column block of the N side
+    uint32_t nblk;   // blocks: 2, or 1 (ragged last block, or half of a split tile)
+};
+
+struct I8Split {
+    uint32_t full;   // items below this index are whole tiles
+    uint32_t count;  // work items in all
+    bool split;
+};
+
+__device__ __forceinline__ I8Split i8_split(uint32_t num_tiles, uint32_t npairs, bool allow)
+{
+    I8Split sp;
+    sp.full = (num_tiles / npairs) * npairs;
+    const uint32_t rem = num_tiles - sp.full;
+    sp.split = allow && rem > 0 && 2u * rem <= npairs;
+    sp.count = sp.split ? sp.full + 2u * rem : num_tiles;
+    return sp;
+}
+
+// false: the item is empty (the second half of a tile whose second block lies beyond n); every role skips it alike
+__device__ __forceinline__ bool i8_work(uint32_t w, const I8Split &sp, uint32_t pmc, uint32_t tnc, uint32_t band, uint32_t nblocks,
+                                        bool b_whole, I8Work &o)
+{
+    uint32_t t = w, h = 2u;
+    if (sp.split && w >= sp.full) {
+        t = sp.full + ((w - sp.full) >> 1);
+        h = (w - sp.full) & 1u;
+    }
+    uint32_t tn;
+    tile_coords(t, pmc, tnc, band, o.pm, tn);
+    if (h == 2u) {
+        o.bn0 = tn * 2u;
+        o.nblk = b_whole ? 2u : min(2u, nblocks - tn * 2u);
+        return true;
+    }
+    o.bn0 = tn * 2u + h;
+    o.nblk = 1u;
+    return o.bn0 < nblocks;
+}
+
 // TMA = true: an operand whose args.a_src / args.b_src is not kSrcBlocks comes straight from the caller's row-major
 // matrix through a tiled TMA load (one 128 x 128-byte box per stage, 128-byte swizzle: the box lands in exactly the
 // layout a packed block has); cells outside the matrix read as zero, so ragged edges need no packing either.  A
@@ -81,6 +128,9 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
     const uint32_t nblocks = (args.n + 127) / 128, tnc = (nblocks + 1) / 2;
     const uint32_t num_tiles = pmc * tnc;
     const uint32_t KB = (args.k + 127) / 128;
+    // a B fetched by tiled TMA loads is always taken two blocks at a time (a box beyond the matrix is zeros); its tiles are not split
+    const bool b_whole = TMA && args.b_src != kSrcBlocks;
+    const I8Split sp = i8_split(num_tiles, npairs, !b_whole);
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; ++s) {
@@ -116,18 +166,18 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
         const uint32_t pw = warp == 0 ? 0u : 1u;
         uint32_t it = 0;
         bool ok = true;
-        for (uint32_t t = pair; t < num_tiles && ok; t += npairs) {
-            uint32_t pm, tn;
-            tile_coords(t, pmc, tnc, args.band_m, pm, tn);
-            const bool b_tma = TMA && args.b_src != kSrcBlocks, a_tma = TMA && args.a_src != kSrcBlocks;
-            const uint32_t nblk = b_tma ? 2u : min(2u, nblocks - tn * 2);   // a box beyond the matrix is zeros
+        for (uint32_t w = pair; w < sp.count && ok; w += npairs) {
+            I8Work wk;
+            if (!i8_work(w, sp, pmc, tnc, args.band_m, nblocks, b_whole, wk)) continue;
+            const uint32_t pm = wk.pm, nblk = wk.nblk;
+            const bool b_tma = b_whole, a_tma = TMA && args.a_src != kSrcBlocks;
             const uint32_t mtile = pm * 2 + rank;
             const bool a_valid = mtile < tiles_m;
             const uint32_t b_bytes = nblk == 2 ? 16384u : 8192u;
             const uint8_t *a_src = args.A + (size_t)mtile * args.a_kblocks_total * kI8BlockBytes;
             const size_t bbb = args.b_block_bytes;   // 16 KiB, or 16 KiB + the block's row sums
-            const uint8_t *b_src = nblk == 2 ? args.B + (size_t)(tn * 2 + rank) * args.b_kblocks_total * bbb
-                                             : args.B + (size_t)(tn * 2) * args.b_kblocks_total * bbb + rank * 8192u;
+            const uint8_t *b_src = nblk == 2 ? args.B + (size_t)(wk.bn0 + rank) * args.b_kblocks_total * bbb
+                                             : args.B + (size_t)wk.bn0 * args.b_kblocks_total * bbb + rank * 8192u;
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
                 if ((it & 1u) != pw) continue;
                 const uint32_t s = it % S, ph = (it / S) & 1u;
@@ -140,7 +190,7 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                 // two lanes issue one copy each in the same instruction
                 if (lane == 0) {
                     if (b_tma) {
-                        const int32_t rows0 = (int32_t)((tn * 2 + rank) * 128u), k0 = (int32_t)(kb * 128u);
+                        const int32_t rows0 = (int32_t)((wk.bn0 + rank) * 128u), k0 = (int32_t)(kb * 128u);
                         if (args.b_src == kSrcTmaMn)
                             ptx::tma_load_2d(ptx::smem_u32(sB + s * 16384), &maps->b, rows0, k0, BAR(kFull + s));
                         else
@@ -189,11 +239,10 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
             uint32_t it = 0, ti = 0, s = 0, ph = 0;
             bool ok = true, ready = false;
-            for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
-                uint32_t pm_unused, tn;
-                tile_coords(t, pmc, tnc, args.band_m, pm_unused, tn);
-                const uint32_t nblk = (TMA && args.b_src != kSrcBlocks) ? 2u : min(2u, nblocks - tn * 2);
-                const uint32_t idesc = nblk == 2 ? idesc256 : idesc128;
+            for (uint32_t w = pair; w < sp.count && ok; w += npairs) {
+                I8Work wk;
+                if (!i8_work(w, sp, pmc, tnc, args.band_m, nblocks, b_whole, wk)) continue;
+                const uint32_t idesc = wk.nblk == 2 ? idesc256 : idesc128;
                 const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
                 if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
                     ok = false;
@@ -220,6 +269,7 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                     s = s1;
                     ph = ph1;
                 }
+                ++ti;
             }
         }
         __syncwarp();
@@ -227,7 +277,9 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
         // ===================== relay (peer CTA): tells the leader that this CTA's stage has landed =====
         uint32_t it = 0;
         bool ok = true;
-        for (uint32_t t = pair; t < num_tiles && ok; t += npairs) {
+        for (uint32_t w = pair; w < sp.count && ok; w += npairs) {
+            I8Work wk;
+            if (!i8_work(w, sp, pmc, tnc, args.band_m, nblocks, b_whole, wk)) continue;
             for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
                 const uint32_t s = it % S, ph = (it / S) & 1u;
                 if (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull))) {
@@ -244,12 +296,15 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
         int32_t *sCol = sColAll + (warp - 2u) * 384u;
         uint32_t ti = 0;
         bool ok = true;
-        for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
-            uint32_t pm, tn;
-            tile_coords(t, pmc, tnc, args.band_m, pm, tn);
+        for (uint32_t w = pair; w < sp.count && ok; w += npairs) {
+            I8Work wk;
+            if (!i8_work(w, sp, pmc, tnc, args.band_m, nblocks, b_whole, wk)) continue;
+            const uint32_t pm = wk.pm;
             const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
-            const uint32_t n0 = tn * 256u + half * 128u;
-            const uint32_t ncols = args.n > n0 ? min(128u, args.n - n0) : 0u;
+            ++ti;
+            // this warp's column half exists when the item has two blocks (or is the first of one)
+            const uint32_t n0 = (wk.bn0 + half) * 128u;
+            const uint32_t ncols = (half < wk.nblk && args.n > n0) ? min(128u, args.n - n0) : 0u;
             const size_t mrow = (size_t)(pm * 2 + rank) * 128u + quad * 32u + lane;
             const bool row_ok = mrow < args.m;
             __syncwarp();
@@ -268,7 +323,7 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
             float row_sa = 0.0f;
             int32_t row_zp = 0;
             if constexpr (EK == EpiKind::DxCx) {
-                const uint32_t blk = tn * 2u + half;   // this warp's 128 columns are one 128-row block tile of B
+                const uint32_t blk = wk.bn0 + half;   // this warp's 128 columns are one 128-row block tile of B
                 for (uint32_t c = lane; c < 128u; c += 32u) {
                     const bool cok = c < ncols;
                     int32_t rsum = 0;
@@ -1094,9 +1149,18 @@ static Result launch_grid(Kern kern, const UmmaArgs &a, uint32_t num_tiles, bool
     return Result{kOk, 0};
 }
 
-Result pair_gemm_i8_dxcx(const UmmaArgs &a, Dtype td, cudaStream_t st)
+// Pair tiles of an int8 x int8 launch, as the number of CTA pairs worth launching: a problem with so few tiles that
+// twice as many pairs still fit the GPU runs as half tiles (see I8Work), which the kernel derives from its grid size.
+static uint32_t i8_launch_items(const UmmaArgs &a, bool b_whole)
 {
     const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
+    const uint32_t max_pairs = (uint32_t)sm_count_cached() / 2;
+    return (!b_whole && 2u * tiles <= max_pairs) ? 2u * tiles : tiles;
+}
+
+Result pair_gemm_i8_dxcx(const UmmaArgs &a, Dtype td, cudaStream_t st)
+{
+    const uint32_t tiles = i8_launch_items(a, false);
     static bool set_f32[64] = {false}, set_f16[64] = {false};
     if (td == Dtype::F32)
         return launch_grid(gemm_pair_i8_kernel<EpiKind::DxCx, Dtype::F32>, a, tiles, true, kI8Threads, kI8Smem, st, set_f32);
@@ -1105,14 +1169,14 @@ Result pair_gemm_i8_dxcx(const UmmaArgs &a, Dtype td, cudaStream_t st)
 
 Result pair_gemm_i8_rows(const UmmaArgs &a, cudaStream_t st)
 {
-    const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
+    const uint32_t tiles = i8_launch_items(a, false);
     static bool set_row[64] = {false};
     return launch_grid(gemm_pair_i8_kernel<EpiKind::Req8Row>, a, tiles, true, kI8Threads, kI8Smem, st, set_row);
 }
 
 Result pair_gemm_i8(const UmmaArgs &a, bool requant, cudaStream_t st)
 {
-    const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
+    const uint32_t tiles = i8_launch_items(a, false);
     static bool set_s32[64] = {false}, set_req[64] = {false};
     note_kernel(kKernelPairBlocks);
     if (requant) return launch_grid(gemm_pair_i8_kernel<EpiKind::Req8>, a, tiles, true, kI8Threads, kI8Smem, st, set_req);
@@ -1168,7 +1232,7 @@ Result pair_gemm_i8_tma(const UmmaArgs &a_in, EpiKind ek, Dtype td, size_t lda, 
     if (a.a_src == kSrcTmaK && !encode_i8_map(&maps.a, a.A, a.k, a.m, lda)) return Result{kUnsupported, 0};
     if (a.b_src == kSrcTmaK && !encode_i8_map(&maps.b, a.B, a.k, a.n, ldb)) return Result{kUnsupported, 0};
     if (a.b_src == kSrcTmaMn && !encode_i8_map(&maps.b, a.B, a.n, a.k, ldb)) return Result{kUnsupported, 0};
-    const uint32_t tiles = (((a.m + 127) / 128 + 1) / 2) * ((((a.n + 127) / 128) + 1) / 2);
+    const uint32_t tiles = i8_launch_items(a, a.b_src != kSrcBlocks);
     static bool set_s32[64] = {false}, set_req[64] = {false}, set_row[64] = {false}, set_f32[64] = {false}, set_f16[64] = {false};
     note_kernel(kKernelPairTma);
     switch (ek) {
