@@ -730,7 +730,34 @@ def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20
     us_read = _graph_time_us(torch, stream, reads, copies, reps)
     pkg.set_stream(torch.cuda.current_stream().cuda_stream)
     gbs = nbytes / (us * 1e-6) / 1e9
-    return {"metric": "w4a8_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "us_per_gemv": us,
+    phases = None
+    if M == 1:
+        # clock64 phase stamps of the dp4a GEMV (thread 0 of every CTA), one buffer per launch of the same chain: where a
+        # GEMV's time goes when its predecessor is still running (the stamped graph is not the timed one)
+        lib.tqt_cuda_debug_set_timing_buffer.argtypes = [ctypes.c_void_p]
+        bufs = [torch.zeros(148 * 16, dtype=torch.int64, device=dev) for _ in layers]
+
+        def stamped():
+            for L, b in zip(layers, bufs):
+                lib.tqt_cuda_debug_set_timing_buffer(b.data_ptr())
+                L.gemm(M)
+            lib.tqt_cuda_debug_set_timing_buffer(None)
+
+        _graph_time_us(torch, stream, stamped, copies, 2)
+        pkg.set_stream(torch.cuda.current_stream().cuda_stream)
+        rows = []
+        for b in bufs[8:]:
+            t = b.cpu().numpy().reshape(148, 16)[:, :6].astype("float64")
+            t = t[t[:, 5] > 0]
+            if len(t):
+                rows.append((t[:, 1:] - t[:, :-1]).mean(0))
+        if rows:
+            import numpy as _np
+            d = _np.median(_np.array(rows), axis=0)
+            phases = {"unit": "SM cycles, mean over the CTAs of a launch, median over launches 9..48 of the chain",
+                      "entry_to_loads_issued": d[0], "griddepcontrol_wait": d[1], "k_loop_after_wait": d[2], "combine": d[3],
+                      "epilogue_store": d[4], "total": float(d.sum())}
+    return {"metric": "w4a8_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "us_per_gemv": us, "phases": phases,
             "workload": f"gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp decode M={M} K={K} N={N}",
             "bytes_per_gemv": nbytes, "gpu_launches": reps * copies,
             "read_ceiling": {"gbs": rd / (us_read * 1e-6) / 1e9, "us": us_read,

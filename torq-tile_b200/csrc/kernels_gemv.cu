@@ -30,6 +30,7 @@
 namespace tqt {
 
 int sm_count_cached();
+long long *timing_buffer();   // kernels_umma.cu
 
 constexpr uint32_t kGemvThreads = 256;
 constexpr uint32_t kGemvWarpRows = 8;   // output columns per warp
@@ -50,7 +51,15 @@ struct GemvArgs {
     const float *scale_b;
     float cmin, cmax;
     int pdl;
+    long long *dbg;   // diagnostic (tqt_cuda_debug_set_timing_buffer): thread 0 of CTAs 0..147 stores clock64 phase stamps, 16 slots per CTA
 };
+
+// Phase stamps of the dp4a GEMV (cycles of the CTA's SM clock): 0 kernel entry, 1 first set's weight loads issued,
+// 2 griddepcontrol.wait returned, 3 K loop done (activations fetched, dp4a chain), 4 partial sums combined, 5 output stored.
+__device__ __forceinline__ void gemv_stamp(const GemvArgs &args, int slot)
+{
+    if (args.dbg && threadIdx.x == 0 && blockIdx.x < 148u) args.dbg[blockIdx.x * 16u + slot] = clock64();
+}
 
 // 128-bit streaming load: read-only path, do not keep the line in L1.
 __device__ __forceinline__ uint4 ldg_stream(const void *p)
@@ -95,6 +104,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
     const uint32_t groups = (args.n + kGemvWarpRows - 1) / kGemvWarpRows;
     const uint32_t sgroups = (groups + G - 1) / G;                 // sets of G groups: the unit a CTA takes
 
+    gemv_stamp(args, 0);
     if (args.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     constexpr size_t kWStep = (size_t)S * kI4CxBlockBytes;
@@ -143,8 +153,10 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
         }
     };
     load_column_constants(sg);
+    gemv_stamp(args, 1);
     // everything else may have been produced by the preceding kernel
     if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+    gemv_stamp(args, 2);
 
     float sa[MR];
     int32_t zp[MR];
@@ -210,6 +222,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
             if (t0 + CH < T) load_chunk(t0 + CH);
         }
 
+        gemv_stamp(args, 3);
         // request the next set's first chunk before combining this one: the registers are free
         const uint32_t cur = sg;
         const uint32_t next = sg + gridDim.x;
@@ -240,6 +253,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
             }
         }
         __syncthreads();
+        gemv_stamp(args, 4);
 
         if (finisher) {
 #pragma unroll
@@ -267,6 +281,7 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
                 }
             }
         }
+        gemv_stamp(args, 5);
         if (next >= sgroups) break;
         sg = next;
         load_column_constants(sg);
@@ -275,25 +290,23 @@ __global__ void __launch_bounds__(kGemvThreads, gemv_min_ctas<MR, G>()) gemv_w4a
 }
 
 // ======================================================================================================
-// GEMV for 1 <= m <= 16 on mma.sync (m16n8k32, s8 x s8 -> s32), weights streamed through registers.
+// GEMV for 2 <= m <= 16 on mma.sync (m16n8k32, s8 x s8 -> s32), weights streamed through registers.
 // The tensor cores here are a convenience, not a throughput need: the 16-row A fragment is exactly a decode
-// batch, so one kernel serves every m <= 16 at nearly the cost of m = 1, and the activations are fetched once
-// per CTA (staged in shared memory after the wait for the predecessor) instead of once per lane and row.
+// batch, so one kernel serves every m <= 16 at nearly the cost of m = 2.
 //
-// A CTA owns a set of 8 G consecutive output columns (G = 2 or 4 groups of 8); warp w takes K blocks w, w+8, ...
+// A CTA owns a set of 8 G consecutive output columns (G = 1 or 2 groups of 8); warp w takes K blocks w, w+8, ...
 // Lane (g, t) = (lane / 4, lane % 4) streams, per group and K block, the 16 bytes of weight row g that hold
 // logical segment t (physical position t ^ ((g >> 1) & 3): a warp-wide load still covers 512 contiguous
 // bytes), and supplies, for MMA step j, b0 = 16 q[col g][32 t + 4 j ..] and b1 = 16 q[col g][32 t + 16 + 4 j ..]
-// (the two masks of word j).  The A fragment takes words j of activation chunks 2t / 2t+1 of rows g / g+8: any
-// consistent permutation of k is a valid contraction order, and integer sums are exact.  The column sums of the
-// weights (the zero-point correction) are accumulated from the same words with dp4a against ones, so the row-sum
-// tails of the packed blocks are not read.  The eight warps are combined through shared
-// memory; warp 0 runs the epilogue (reference: src/gemm/gemm_i8_i4/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp/
-// ..._4x1vl_rvv.cpp:118-177).  No mbarrier, no scratch memory.
+// (the two masks of word j).  The A fragment takes words j of activation chunks 2t / 2t+1 of rows g / g+8, loaded
+// straight from the packed activation rows after the wait for the predecessor: any consistent permutation of k is a
+// valid contraction order, and integer sums are exact.  The column sums of the weights (the zero-point correction)
+// are accumulated from the same words with dp4a against ones, so the row-sum tails of the packed blocks are not
+// read.  The eight warps are combined through shared memory; warp 0 runs the epilogue (reference:
+// src/gemm/gemm_i8_i4/gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp/..._4x1vl_rvv.cpp:118-177).  No mbarrier, no scratch
+// memory, no staging of weights or activations in shared memory (both were slower in a chain of GEMVs).
 //
-// All weight loads of a CTA's first set are requested before griddepcontrol.wait.  With G = 4 a decode-sized
-// launch (N = 4096: 128 CTAs of 256 threads) takes under half of the register file, so the next GEMV of a chain
-// is resident with its weights in flight while this one runs its post-wait tail.
+// All weight loads of a CTA's first set are requested before griddepcontrol.wait.
 // ======================================================================================================
 constexpr uint32_t kGvRedInts = 5u * 32u;   // per warp and group: [acc0..3, column sum][lane]
 
@@ -308,7 +321,7 @@ __device__ __forceinline__ void mma_s8_16832(int32_t (&d)[4], uint32_t a0, uint3
 template <int G>
 constexpr int gemv_mma_min_ctas() { return 2; }
 
-// Dynamic shared memory: [m rows][K blocks][128 B] activations (as they lie in the packed blocks) | [7 warps][G][reduce].
+// Static shared memory: [7 warps][G][reduce].
 // R16: the launch has more than 8 activation rows (fragment rows g + 8 exist); their fragments are then fetched
 // two K blocks at a time to stay inside the register budget.
 template <int G, bool R16, Dtype TD>
@@ -623,6 +636,7 @@ Result gemv_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin,
     a.scale_b = p.scale_b;
     a.cmin = cmin;
     a.cmax = cmax;
+    a.dbg = timing_buffer();
     cudaStream_t st = (cudaStream_t)g.stream;
     switch (td) {
         case Dtype::F32: return launch_gemv_m<Dtype::F32>(a, st);
