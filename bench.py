@@ -645,6 +645,24 @@ def bench_unpacked_and_conv(torch, pkg, dev, peaks, time_us):
             rec["note"] = "launch-latency bound: one tile on one CTA pair"
         out["c1_i32_unpacked" if M == 64 else "i32_unpacked_4096"] = rec
         del A, B, D
+    # the W4A8 prefill shape with both operands left in the caller's layouts (A int8 [m, k], B nibbles [n, k / 2]): tiled TMA
+    # loads into the tensor-memory kernel, converters decode the reference's unpacked nibble order
+    M, K, N, _ = CONFIGS["c3"]
+    us_w = pkg.SiblingGemm("gemm_1xnbias_clamp_bf16_qai8dx_qsi4cxt")
+    sets = 5
+    A = [torch.randint(-128, 128, (M, K), device=dev, dtype=torch.int8) for _ in range(sets)]
+    B = [torch.randint(0, 256, (N, K // 2), device=dev, dtype=torch.uint8) for _ in range(sets)]
+    D = [torch.empty((M, N), device=dev, dtype=torch.bfloat16) for _ in range(sets)]
+    sa = torch.full((M,), 0.02, device=dev, dtype=torch.float32)
+    zp = torch.zeros(M, device=dev, dtype=torch.int32)
+    sb = torch.full((N,), 0.004, device=dev, dtype=torch.float32)
+    wp = pkg.QaI8DxQsI4CxParams(sa.data_ptr(), zp.data_ptr(), sb.data_ptr())
+    us = time_us(lambda i: us_w.run_gemm(M, N, K, A[i], K, 0, B[i], K, 0, None, N, D[i], N, None, -65504.0, 65504.0, wp), sets)
+    out["w4a8_unpacked_c3"] = {"workload": f"gemm_1xnbias_clamp_bf16_qai8dx_qsi4cxt M={M} K={K} N={N}, row-major operands through tensor maps",
+                               "us": us, "tops": 2.0 * M * N * K / (us * 1e-6) / 1e12, "kernel_family": pkg.debug_last_kernel(),
+                               "frac": 2.0 * M * N * K / (us * 1e-6) / 1e12 / (2.0 * peaks["bf16"]),
+                               "note": "frac of 2 x bf16_tflops (burst); sets rotate through 480 MB"}
+    del A, B, D
     # 56 x 56 x 256 -> 256 channels, 3 x 3, pad 1 (M = 3136, K = 2304, N = 256), batch of 8 images as 8 groups of rows
     ck = pkg.ConvI8(pkg.CONV_TYPES[0])
     IC = OC = 256

@@ -1,11 +1,13 @@
 /*
  * The remaining kernel types of the three quantised GEMM families: the unpacked ("t" layouts) and
  * otherwise-packed siblings of the types in tqt_b200_gemm_i8_i8.h, tqt_b200_gemm_i8_i4.h and
- * tqt_b200_gemm_f16_i4.h.  Same contraction, different operand layout or epilogue.  Types with an unpacked
- * operand run on the generic CUDA-core kernel (any alignment, any layout); the fully packed ones (mx1bias
- * ..._qsi8dxp_qai8p, ..._qai8dxp_qsi8cxp) on the tcgen05 CTA-pair kernel.  The packed B of the qai8dxp_qsi8cxp
- * types is opaque like every packed buffer: 16 KiB blocks followed by 128 int16 partial row sums each
- * (get_b_packed_size / get_b_packed_offset account for it).
+ * tqt_b200_gemm_f16_i4.h.  Same contraction, different operand layout or epilogue.  The fully packed types (mx1bias
+ * ..._qsi8dxp_qai8p, ..._qai8dxp_qsi8cxp) run on the tcgen05 CTA-pair kernel.  Types with a row-major ("unpacked")
+ * operand run on the same tensor-core kernels, each stage fetched from the caller's matrix by tiled TMA loads, when
+ * that operand's base address and row stride (in bytes) are multiples of 16; any other call runs on a generic
+ * CUDA-core kernel (any alignment, any layout, much slower).  The packed B of the qai8dxp_qsi8cxp types is opaque
+ * like every packed buffer: 16 KiB blocks followed by 128 int16 partial row sums each (get_b_packed_size /
+ * get_b_packed_offset account for it).
  *
  * Reference variants replaced (paths under src/gemm/):
  *   gemm_i8_i4/gemm_1xnbias_clamp_{f32,f16,bf16}_qai8dx_qsi4cxt/tqt_gemm_..._4x1vl_rvv.h

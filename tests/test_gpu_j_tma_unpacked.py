@@ -7,12 +7,12 @@ import numpy as np
 import pytest
 import torch
 
-from oracle.tqo import TD_F16, TD_F32
-from tqt_testlib import DEV, bits16, pkg, sync_and_check, to_dev
+from oracle.tqo import TD_BF16, TD_F16, TD_F32
+from tqt_testlib import DEV, FMAX, bits16, cosine, f16_bits_to_f32, pkg, rel_err, sync_and_check, to_dev
 
 pytestmark = pytest.mark.gpu
 
-SIMT, PAIR_BLOCKS, PAIR_TMA = 1, 2, 3
+SIMT, PAIR_BLOCKS, PAIR_TMA, TS_TMA = 1, 2, 3, 4
 # (m, n, k, lda - k, ldb - rows): ragged in every dimension, odd block counts (a whole box beyond the matrix),
 # several K blocks, padding columns behind k / n that hold other data
 SHAPES = [(64, 256, 512, 0, 0), (5, 7, 16, 0, 9), (130, 257, 194, 14, 15), (33, 140, 1026, 6, 4), (300, 520, 640, 0, 8),
@@ -132,6 +132,77 @@ def test_dynamic_activation_float_out_unpacked(oracle, td, m, n, k, pa, pb):
     got = d.cpu().numpy() if td == "f32" else bits16(d)
     assert np.array_equal(got, want)
     assert p.debug_last_kernel() == (PAIR_TMA if _aligned(k + pa) and _aligned(k + pb) else SIMT)
+
+
+# (m, n, k, lda - k, ldb - k): k even; the nibble matrix has ldb / 2 bytes per row
+W4_SHAPES = [(5, 7, 16, 0, 16), (64, 96, 128, 0, 0), (130, 257, 194, 14, 30), (33, 140, 1026, 6, 4), (300, 520, 640, 16, 32),
+             (200, 260, 96, 0, 0), (450, 390, 1100, 20, 20)]
+
+
+@pytest.mark.parametrize("td", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("m,n,k,pa,pb", W4_SHAPES)
+def test_w4a8_unpacked(oracle, td, m, n, k, pa, pb):
+    """gemm_1xnbias_clamp_{f32,f16,bf16}_qai8dx_qsi4cxt: A int8 [m, lda], B nibbles [n, ldb / 2 bytes] in the reference's
+    unpacked encoding; tiled TMA loads feed the tensor-memory kernel, whose converters decode that nibble order and add
+    up the row sums.  Bit-exact like the packed types."""
+    p = pkg()
+    p.use_current_torch_stream()
+    rng = np.random.default_rng(m * 31 + n + k)
+    A_full, A = _padded(rng, m, k, pa)
+    nib, sb = oracle.quantize_b_per_channel_sym_int4(rng.normal(0, 0.02, (n, k)).astype(np.float32))
+    nib_full = rng.integers(0, 256, (n, (k + pb) // 2), dtype=np.uint8)
+    nib_full[:, :k // 2] = nib
+    sa = rng.uniform(0.01, 0.05, m).astype(np.float32)
+    zp = rng.integers(-30, 30, m).astype(np.int32)
+    tdt = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}[td]
+    tdi = {"f32": TD_F32, "f16": TD_F16, "bf16": TD_BF16}[td]
+    bias_d = to_dev(rng.normal(0, 0.1, n).astype(np.float32)).to(tdt)
+    bias_o = bias_d.cpu().numpy() if td == "f32" else bits16(bias_d)
+    c_d = to_dev(rng.normal(0, 1, (m, n)).astype(np.float32)).to(tdt) if m % 2 else None
+    c_o = None if c_d is None else (c_d.cpu().numpy() if td == "f32" else bits16(c_d))
+    clamp = (-FMAX, FMAX) if td == "f32" else (-65504.0, 65504.0)
+    want = oracle.gemm_w4a8(A, nib, sa, zp, sb, tdi, c_o, bias_o, clamp)
+    uk = p.SiblingGemm(f"gemm_1xnbias_clamp_{td}_qai8dx_qsi4cxt")
+    sa_d, zp_d, sb_d = to_dev(sa), to_dev(zp), to_dev(sb)
+    d = torch.full((m, n), 7.0, dtype=tdt, device=DEV)
+    params = p.QaI8DxQsI4CxParams(sa_d.data_ptr(), zp_d.data_ptr(), sb_d.data_ptr())
+    uk.run_gemm(m, n, k, to_dev(A_full), k + pa, 0, to_dev(nib_full), k + pb, 0, c_d, n, d, n, bias_d, clamp[0], clamp[1], params)
+    sync_and_check()
+    got = d.cpu().numpy() if td == "f32" else bits16(d)
+    assert np.array_equal(got, want)
+    tma = _aligned(k + pa) and _aligned((k + pb) // 2)
+    assert p.debug_last_kernel() == (TS_TMA if tma else SIMT)
+
+
+@pytest.mark.parametrize("td", ["f16", "f32"])
+@pytest.mark.parametrize("m,n,k,bl,pa,pb", [(5, 7, 16, 2, 0, 16), (64, 96, 128, 32, 0, 0), (130, 257, 192, 64, 8, 64),
+                                            (33, 140, 1024, 128, 0, 0), (300, 390, 640, 32, 24, 32), (200, 130, 200, 8, 0, 24)])
+def test_w4a16_unpacked(oracle, td, m, n, k, bl, pa, pb):
+    """gemm_1xnbias_clamp_{f16,f32}_f16_qsi4c2t: A f16 [m, lda], B nibbles [n, ldb / 2 bytes], scale_b f16 [n, k / bl]."""
+    p = pkg()
+    p.use_current_torch_stream()
+    rng = np.random.default_rng(m + n + k + bl)
+    A_full = rng.normal(0, 1, (m, k + pa)).astype(np.float16)
+    A = np.ascontiguousarray(A_full[:, :k])
+    W = rng.normal(0, 0.02, (n, k)).astype(np.float16)
+    nib, sc = oracle.quantize_fp16_to_int4(W.view(np.uint16), bl)
+    nib_full = rng.integers(0, 256, (n, (k + pb) // 2), dtype=np.uint8)
+    nib_full[:, :k // 2] = nib
+    bias = rng.normal(0, 0.1, n).astype(np.float16 if td == "f16" else np.float32)
+    bias_o = bias.view(np.uint16) if td == "f16" else bias
+    clamp = (-65504.0, 65504.0) if td == "f16" else (-FMAX, FMAX)
+    want = oracle.gemm_w4a16(A.view(np.uint16), nib, sc, bl, TD_F16 if td == "f16" else TD_F32, None, bias_o, clamp)
+    uk = p.SiblingGemm(f"gemm_1xnbias_clamp_{td}_f16_qsi4c2t")
+    d = torch.full((m, n), 7.0, dtype=torch.float16 if td == "f16" else torch.float32, device=DEV)
+    uk.run_gemm(m, n, k, to_dev(A_full.view(np.uint16)), k + pa, 0, to_dev(nib_full), k + pb, 0, None, n, d, n, to_dev(bias_o),
+                clamp[0], clamp[1], bl=bl, scale_b=to_dev(sc), ldsb=k // bl)
+    sync_and_check()
+    got = d.float().cpu().numpy()
+    ref = f16_bits_to_f32(want) if td == "f16" else want
+    assert rel_err(got, ref) < 2e-2
+    assert np.max(np.abs(got - ref)) <= 1.0 and cosine(got, ref) >= 0.9999
+    tma = _aligned(2 * (k + pa)) and _aligned((k + pb) // 2)
+    assert p.debug_last_kernel() == (TS_TMA if tma else SIMT)
 
 
 def test_unaligned_base_falls_back(oracle):

@@ -522,9 +522,30 @@ struct TsCfg {
 // REPL: the epilogue also stores into the output replicas (fused all-gather).  A separate instantiation: with the
 // replica stores compiled into the common kernel, even as a branch never taken, every launch ran 10 % slower
 // (code size: the strip loop is unrolled 32 times).
-template <TsKind KD, Dtype TD, bool PAIR, bool WIDE, bool REPL>
-__device__ __forceinline__ void ts_body(const UmmaArgs &args)
+// The two 4-bit values (k = 2 t, 2 t + 1 of an 8-k word) as the low nibbles of the two halves of a word.  Packed qsi4c2
+// blocks order a word's nibbles (k0,k2,k4,k6,k1,k3,k5,k7) so that one shift and mask does it; row-major weights hold them
+// in k order.
+template <bool SEQUENTIAL>
+__device__ __forceinline__ uint32_t nib_pair(uint32_t w, uint32_t t)
 {
+    if (SEQUENTIAL) {
+        const uint32_t x = w >> (8u * t);
+        return (x & 0xFu) | ((x << 12) & 0x000F0000u);
+    }
+    return (w >> (4u * t)) & 0x000F000Fu;
+}
+
+// UNP (CTA pairs, 192-row tiles only): the operands stay in the caller's row-major layouts and every stage is fetched by
+// tiled TMA loads through the two tensor maps in `maps`: activations int8 / f16 [m, lda] as boxes of 128 bytes x 96 rows
+// with the 128-byte swizzle (what a slice of a packed block looks like), weights as nibbles [n, ldb / 2 bytes] in the
+// reference's unpacked encoding (byte = (q_hi + 8) << 4 | (q_lo + 8), consecutive k in consecutive nibbles) as boxes of
+// 64 bytes x 128 rows with the 64-byte swizzle, which puts 16-byte segment s of row r at position s ^ ((r >> 1) & 3)
+// like a packed block.  The converters decode that nibble order and add up the row sums themselves (the packed
+// blocks carry them in their tails); cells outside the matrices arrive as zero bytes.
+template <TsKind KD, Dtype TD, bool PAIR, bool WIDE, bool REPL, bool UNP = false>
+__device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands *maps = nullptr)
+{
+    static_assert(!UNP || (PAIR && !WIDE && !REPL), "row-major operands: CTA pairs with 192-row tiles only");
     using Cfg = TsCfg<KD, PAIR, WIDE>;
     using OutT = typename TdTraits<TD>::type;
     constexpr bool kF16 = Cfg::kF16;
@@ -650,6 +671,20 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                     // W4A8: every step brings its own 128-k block of nibbles; W4A16: the group's single block rides on step 0
                     const bool nib_now = nib_valid && (!kF16 || h == 0);
                     const uint32_t nib_bytes = kF16 ? 8192u : 8448u;
+                    if constexpr (UNP) {
+                        // boxes always count in full, cells beyond the matrices included
+                        if (lane == 0) ptx::mbar_arrive_expect_tx(BAR(kFull + s), kActBytes + (nib_now ? 8192u : 0u));
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (nib_now)   // 64 bytes of nibbles = 128 k: x counts bytes of the row
+                                ptx::tma_load_2d(ptx::smem_u32(sNib + gs * Cfg::kNibGroupBytes + (kF16 ? 0u : h * 8192u)), &maps->b,
+                                                 (int32_t)((kF16 ? g : ks) * 64u), (int32_t)(nb * 128u), BAR(kFull + s));
+                        } else if (lane == 1) {
+                            ptx::tma_load_2d(ptx::smem_u32(sAct + s * kActBytes), &maps->a, (int32_t)(ks * 128u), (int32_t)a0, BAR(kFull + s));
+                        }
+                        __syncwarp();
+                        continue;
+                    }
                     if (lane == 0) ptx::mbar_arrive_expect_tx(BAR(kFull + s), act_tx + (nib_now ? nib_bytes : 0u));
                     __syncwarp();
                     // three lanes issue one bulk copy each in the same instruction
@@ -869,7 +904,33 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                     continue;
                 }
                 uint32_t regs[32];
-                if constexpr (!kF16) {
+                if constexpr (!kF16 && UNP) {
+                    // Row-major nibbles: word j of segment seg holds k = 32 seg + 8 j .. + 7, low nibble first, as u = q + 8.
+                    // L / H = the even / odd k as bytes 16 u; two byte permutes put them in k order and 16 u - 128 = 16 q
+                    // is an exclusive-or with 0x80 (no carries: 16 u <= 240).  sum u = dp4a of the nibble bytes with ones.
+                    const uint8_t *nrowp = sNib + gs * Cfg::kNibGroupBytes + h * 8192u + row * 64u;
+                    const uint32_t kv = min(128u, args.k - (g * 2u + h) * 128u);   // k values of this step that exist
+                    int32_t usum = 0;
+#pragma unroll
+                    for (uint32_t seg = 0; seg < 4; ++seg) {
+                        const uint4 w = *reinterpret_cast<const uint4 *>(nrowp + ((seg ^ swz_in) << 4));
+                        uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+                        for (uint32_t j = 0; j < 4; ++j) {
+                            if (kv < 128u) {   // the ragged last step: nibbles beyond k (zero bytes from the copy) become u = 8, q = 0
+                                const uint32_t k0 = seg * 32u + j * 8u;
+                                const uint32_t nv = kv > k0 ? min(8u, kv - k0) : 0u;
+                                const uint32_t mask = nv >= 8u ? 0xffffffffu : ((1u << (4u * nv)) - 1u);
+                                ws[j] = (ws[j] & mask) | (0x88888888u & ~mask);
+                            }
+                            const uint32_t lo = (ws[j] << 4) & 0xF0F0F0F0u, hi = ws[j] & 0xF0F0F0F0u;
+                            regs[seg * 8 + 2 * j] = __byte_perm(lo, hi, 0x5140) ^ 0x80808080u;       // k = 32 seg + 8 j .. + 3
+                            regs[seg * 8 + 2 * j + 1] = __byte_perm(lo, hi, 0x7362) ^ 0x80808080u;   // k = 32 seg + 8 j + 4 .. + 7
+                            usum = __dp4a((int)((lo >> 4) + (hi >> 4)), 0x01010101, usum);
+                        }
+                    }
+                    rsum += usum - 8 * 128;   // sum q = sum u - 8 per nibble (the masked ones hold u = 8)
+                } else if constexpr (!kF16) {
                     const uint8_t *blk = sNib + gs * Cfg::kNibGroupBytes + h * 8448u;
                     const uint8_t *nrowp = blk + row * 64u;
 #pragma unroll
@@ -903,7 +964,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                                 const __half2 sc2 = __half2half2(sc8[sg * 4 + wi]);
 #pragma unroll
                                 for (uint32_t tt = 0; tt < 4; ++tt) {
-                                    const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
+                                    const uint32_t bits = nib_pair<UNP>(ws[wi], tt) | 0x64006400u;
                                     const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032), sc2);
                                     regs[sg * 16 + wi * 4 + tt] = *reinterpret_cast<const uint32_t *>(&v);
                                 }
@@ -922,7 +983,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args)
                                     const uint32_t kk = kbase + sg * 32u + wi * 8u + 2 * tt;
                                     const __half2 sc2 = (n_ok && kk < args.k) ? __half2half2(__ldg(srow + kk / args.bl))
                                                                               : __float2half2_rn(0.0f);
-                                    const uint32_t bits = ((ws[wi] >> (4 * tt)) & 0x000F000Fu) | 0x64006400u;
+                                    const uint32_t bits = nib_pair<UNP>(ws[wi], tt) | 0x64006400u;
                                     const __half2 v = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&bits), k1032), sc2);
                                     regs[sg * 16 + wi * 4 + tt] = *reinterpret_cast<const uint32_t *>(&v);
                                 }
@@ -1102,6 +1163,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1) gemm_
     ts_body<KD, TD, true, WIDE, REPL>(args);
 }
 
+// Row-major operands: the tensor maps travel as a kernel parameter.
+template <TsKind KD, Dtype TD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
+    gemm_ts_pair_tma_kernel(const UmmaArgs args, const __grid_constant__ TmaOperands maps)
+{
+    ts_body<KD, TD, true, false, false, true>(args, &maps);
+}
+
 // Same kernel on one CTA (cta_group::1): the CTA stages all 192 activation rows itself.
 template <TsKind KD, Dtype TD>
 __global__ void __launch_bounds__(kTsThreads, 1) gemm_ts_kernel(const UmmaArgs args)
@@ -1205,7 +1274,10 @@ static EncodeTiledFn encode_tiled_fn()
 
 // int8 matrix [outer, inner] with `inner` contiguous and rows `stride` bytes apart, read in boxes of 128 x 128 bytes
 // with the 128-byte swizzle.  The base and the stride must be multiples of 16 bytes.
-static bool encode_i8_map(TmaDesc *out, const void *base, size_t inner, size_t outer, size_t stride)
+// A byte matrix [outer, inner bytes] with rows `stride` bytes apart, read in boxes of box_inner bytes x box_outer rows;
+// box_inner 128 takes the 128-byte swizzle, 64 the 64-byte one.
+static bool encode_byte_map(TmaDesc *out, const void *base, size_t inner, size_t outer, size_t stride, uint32_t box_inner,
+                            uint32_t box_outer)
 {
     static_assert(sizeof(CUtensorMap) == sizeof(TmaDesc), "tensor map size");
     EncodeTiledFn fn = encode_tiled_fn();
@@ -1214,11 +1286,16 @@ static bool encode_i8_map(TmaDesc *out, const void *base, size_t inner, size_t o
         return false;
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {stride};
-    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     return fn(reinterpret_cast<CUtensorMap *>(out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box,
-              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, box_inner == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool encode_i8_map(TmaDesc *out, const void *base, size_t inner, size_t outer, size_t stride)
+{
+    return encode_byte_map(out, base, inner, outer, stride, 128, 128);
 }
 
 // int8 x int8 with at least one operand in the caller's row-major layout.  a.a_src / a.b_src say how each operand is
@@ -1292,6 +1369,40 @@ Result ts_gemm_w4a16(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st)
 {
     if (td == Dtype::F16) return launch_ts<TsKind::W4A16, Dtype::F16>(a, pair, st);
     return launch_ts<TsKind::W4A16, Dtype::F32>(a, pair, st);
+}
+
+// int4 weights with row-major operands (the reference's unpacked "t" kernel types): activations [m, lda] of a_elem bytes
+// per element, weights as nibbles [n, ldb / 2 bytes].  kUnsupported when a tensor map cannot describe an operand.
+template <TsKind KD, Dtype TD>
+static Result launch_ts_tma(const UmmaArgs &a_in, const TmaOperands &maps, cudaStream_t st)
+{
+    UmmaArgs a = a_in;
+    a.mt = kTsMT;
+    a.pdl = 0;
+    const uint32_t nblocks = (a.n + 127) / 128;
+    const uint32_t tiles = ((a.m + kTsMT - 1) / kTsMT) * ((nblocks + 1) / 2);
+    static bool set_attr[64] = {false};
+    note_kernel(kKernelTsTma);
+    return launch_grid(gemm_ts_pair_tma_kernel<KD, TD>, a, tiles, true, kTsThreads, TsCfg<KD, true, false>::kSmem, st, set_attr, maps);
+}
+
+Result ts_gemm_unpacked(const UmmaArgs &a, bool w4a16, Dtype td, size_t lda, size_t ldb, cudaStream_t st)
+{
+    TmaOperands maps{};
+    const size_t a_elem = w4a16 ? 2 : 1;
+    constexpr uint32_t kActRowsPair = kTsMT / 2;
+    if (!encode_byte_map(&maps.a, a.A, (size_t)a.k * a_elem, a.m, lda * a_elem, 128, kActRowsPair)) return Result{kUnsupported, 0};
+    if ((a.k & 1u) || (ldb & 1u) || !encode_byte_map(&maps.b, a.B, a.k / 2, a.n, ldb / 2, 64, 128)) return Result{kUnsupported, 0};
+    if (w4a16) {
+        if (td == Dtype::F16) return launch_ts_tma<TsKind::W4A16, Dtype::F16>(a, maps, st);
+        if (td == Dtype::F32) return launch_ts_tma<TsKind::W4A16, Dtype::F32>(a, maps, st);
+        return Result{kUnsupported, 0};
+    }
+    switch (td) {
+        case Dtype::F32: return launch_ts_tma<TsKind::W4A8, Dtype::F32>(a, maps, st);
+        case Dtype::F16: return launch_ts_tma<TsKind::W4A8, Dtype::F16>(a, maps, st);
+        default: return launch_ts_tma<TsKind::W4A8, Dtype::BF16>(a, maps, st);
+    }
 }
 
 }  // namespace tqt

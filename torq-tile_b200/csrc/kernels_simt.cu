@@ -311,8 +311,18 @@ static Result simt_w4a8_unpacked_t(const GemmCommon &g, const W4A8Params &p, flo
     return run_simt<RowMajorI8, RowMajorNib, EpiW4A8<TD>, true>(g, la, lb, epi);
 }
 
+Result umma_gemm_w4a8_unpacked(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax);
+Result umma_gemm_w4a16_unpacked(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td, float cmin,
+                                float cmax);
+
 Result launch_gemm_w4a8_unpacked(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
 {
+    // operands whose base addresses and row strides are multiples of 16 bytes: tiled TMA loads into the tensor-core
+    // kernel (TQT_B200_PATH=simt keeps the generic kernel, which also takes everything else)
+    if (g.m && g.n && g.k && env_path() != Path::Simt) {
+        Result r = umma_gemm_w4a8_unpacked(g, p, td, cmin, cmax);
+        if (r.status != kUnsupported) return r;
+    }
     switch (td) {
         case Dtype::F32: return simt_w4a8_unpacked_t<Dtype::F32>(g, p, cmin, cmax);
         case Dtype::F16: return simt_w4a8_unpacked_t<Dtype::F16>(g, p, cmin, cmax);
@@ -361,7 +371,12 @@ Result simt_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size
                        float cmax)
 {
     if (g.m == 0 || g.n == 0) return Result{kOk, 0};
+    if (g.k && env_path() != Path::Simt) {   // tensor cores through tiled TMA loads, where tensor maps can describe the operands
+        Result r = umma_gemm_w4a16_unpacked(g, bl, scale_b, ldsb, td, cmin, cmax);
+        if (r.status != kUnsupported) return r;
+    }
     if (g.m > 65535 || g.n_replicas) return Result{kUnsupported, 0};
+    note_kernel(kKernelSimt);
     dim3 grid((unsigned)ceil_div(g.n, 128), (unsigned)g.m);
     cudaStream_t st = (cudaStream_t)g.stream;
     if (td == Dtype::F16)

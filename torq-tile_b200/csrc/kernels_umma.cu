@@ -791,4 +791,34 @@ Result umma_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size
     return launch_umma<BMode::I4C2, EpiKind::W4A16, Dtype::F32>(a, st);
 }
 
+// ---- int4 weights with row-major operands: tiled TMA loads into the CTA-pair tensor-memory kernel ----------------
+Result ts_gemm_unpacked(const UmmaArgs &a, bool w4a16, Dtype td, size_t lda, size_t ldb, cudaStream_t st);
+
+Result umma_gemm_w4a8_unpacked(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax)
+{
+    UmmaArgs a{};
+    if (!fill_common(a, g, td == Dtype::F32 ? 4 : 2, 128, 128) || a.n_replicas || g.k > 65536) return Result{kUnsupported, 0};
+    a.scale_a = p.scale_a;
+    a.zp_a = p.zp_a;
+    a.scale_b = p.scale_b;
+    a.cmin_f = cmin;
+    a.cmax_f = cmax;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k / 2);
+    return ts_gemm_unpacked(a, false, td, g.lda, g.ldb, (cudaStream_t)g.stream);
+}
+
+Result umma_gemm_w4a16_unpacked(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td, float cmin,
+                                float cmax)
+{
+    UmmaArgs a{};
+    if (td == Dtype::BF16 || !fill_common(a, g, td == Dtype::F32 ? 4 : 2, 64, 128) || a.n_replicas) return Result{kUnsupported, 0};
+    a.scale_blk = (const __half *)scale_b;
+    a.ldsb = ldsb;
+    a.bl = (uint32_t)bl;
+    a.cmin_f = cmin;
+    a.cmax_f = cmax;
+    a.band_m = choose_band(g.m * g.k * 2, g.n * g.k / 2);
+    return ts_gemm_unpacked(a, true, td, g.lda, g.ldb, (cudaStream_t)g.stream);
+}
+
 }  // namespace tqt

@@ -178,7 +178,7 @@ Result stream_read(const void *src, size_t bytes, void *sink, void *stream);
 // tensor-memory kernel.
 Path env_path();
 // Diagnostic for tests: which kernel family the most recent int8 x int8 launch of the process used (kKernel*).
-enum : int { kKernelNone = 0, kKernelSimt = 1, kKernelPairBlocks = 2, kKernelPairTma = 3 };
+enum : int { kKernelNone = 0, kKernelSimt = 1, kKernelPairBlocks = 2, kKernelPairTma = 3, kKernelTsTma = 4 };
 void note_kernel(int family);
 int last_kernel();
 int umma_variant();
