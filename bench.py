@@ -645,6 +645,22 @@ def bench_unpacked_and_conv(torch, pkg, dev, peaks, time_us):
             rec["note"] = "launch-latency bound: one tile on one CTA pair"
         out["c1_i32_unpacked" if M == 64 else "i32_unpacked_4096"] = rec
         del A, B, D
+    # unquantised bf16 GEMM (packed operands) at 4096^3: kind::f16 MMAs, f32 accumulators, bf16 output
+    fk = pkg.FloatGemm("gemm_1xnbias_clamp_bf16_bf16p_bf16p")
+    Mf = Kf = Nf = 4096
+    sets = 6
+    ap = [torch.empty(fk.get_a_packed_size(Mf, Kf), dtype=torch.uint8, device=dev) for _ in range(sets)]
+    bp = [torch.empty(fk.get_b_packed_size(Nf, Kf), dtype=torch.uint8, device=dev) for _ in range(sets)]
+    for i in range(sets):
+        fk.run_a_pack(Mf, Kf, Kf, Kf, 0, torch.randn((Mf, Kf), device=dev).to(torch.bfloat16), ap[i])
+        fk.run_bt_pack(Nf, Kf, Kf, Kf, 0, torch.randn((Nf, Kf), device=dev).to(torch.bfloat16), bp[i])
+    D = [torch.empty((Mf, Nf), device=dev, dtype=torch.bfloat16) for _ in range(sets)]
+    us = time_us(lambda i: fk.run_gemm(Mf, Nf, Kf, ap[i], Kf, 0, bp[i], Kf, 0, None, Nf, D[i], Nf, None, -3.0e38, 3.0e38), sets)
+    tf = 2.0 * Mf * Nf * Kf / (us * 1e-6) / 1e12
+    out["bf16_gemm_4096"] = {"workload": "gemm_1xnbias_clamp_bf16_bf16p_bf16p M=K=N=4096 (unquantised, packed operands)", "us": us,
+                             "tflops": tf, "frac": tf / peaks["bf16"], "kernel_family": pkg.debug_last_kernel(),
+                             "note": "frac of bf16_tflops (burst); sets rotate through 600 MB"}
+    del ap, bp, D
     # the W4A8 prefill shape with both operands left in the caller's layouts (A int8 [m, k], B nibbles [n, k / 2]): tiled TMA
     # loads into the tensor-memory kernel, converters decode the reference's unpacked nibble order
     M, K, N, _ = CONFIGS["c3"]

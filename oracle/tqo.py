@@ -75,6 +75,8 @@ class Oracle:
                                                _vp, _vp, _vp, _sz, C.c_float, C.c_float, C.c_int]
 
         lib.tqo_im2col_i8.argtypes = [C.c_int, _sz, _vp, _vp, _vp]
+        lib.tqo_gemm_float.argtypes = [C.c_int, C.c_int, _sz, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int, _vp, _sz, _vp, _sz, _vp,
+                                       C.c_int, C.c_float, C.c_float]
         lib.tqo_fill_uniform_f32.argtypes = [_vp, _sz, C.c_float, C.c_float, C.c_uint32]
         lib.tqo_fill_uniform_i8.argtypes = [_vp, _sz, C.c_int, C.c_int, C.c_uint32]
         lib.tqo_fill_uniform_i32.argtypes = [_vp, _sz, C.c_int32, C.c_int32, C.c_uint32]
@@ -97,6 +99,17 @@ class Oracle:
         a = np.empty(shape, np.float32)
         self.lib.tqo_fill_normal_f32(_ptr(a), a.size, float(mean), float(sigma), int(seed))
         return a
+
+    def gemm_float(self, ta, td, A, B, b_transposed, Cm=None, bias=None, bias_per_row=False,
+                   clamp=(-3.4028234663852886e38, 3.4028234663852886e38)):
+        """Unquantised GEMM: A [m, k], B [n, k] (b_transposed) or [k, n], as float32 arrays (ta / td TD_F32) or uint16
+        bit patterns; C, bias and the result in the output type td."""
+        m, k = A.shape
+        n = B.shape[0] if b_transposed else B.shape[1]
+        D = np.empty((m, n), np.float32 if td == TD_F32 else np.uint16)
+        self.lib.tqo_gemm_float(ta, td, m, n, k, _ptr(A), A.shape[1], _ptr(B), B.shape[1], int(b_transposed), _ptr(Cm), n,
+                                _ptr(D), n, _ptr(bias), int(bias_per_row), float(clamp[0]), float(clamp[1]))
+        return D
 
     def im2col_i8(self, activation, geom, channel_first, group_idx=0):
         """``geom``: ConvGeometry.  Returns [M, K] (channel-last) or [K, N] (channel-first)."""
@@ -275,6 +288,25 @@ class Reference:
             lib.ref_w4a8_quantize_b_per_channel_sym_int4.argtypes = [_vp, _sz, _sz, _vp, _vp]
             lib.ref_w4a8_gemm.argtypes = [_sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_float,
                                           C.c_float, C.c_int]
+
+    def has_float(self) -> bool:
+        return self.lib is not None and hasattr(self.lib, "ref_gemm_float")
+
+    def gemm_float(self, ta, td, A, B, b_transposed, Cm=None, bias=None, bias_per_row=False,
+                   clamp=(-3.4028234663852886e38, 3.4028234663852886e38)):
+        """reference_gemm<TA, TD> of the reference (same argument conventions as Oracle.gemm_float)."""
+        m, k = A.shape
+        n = B.shape[0] if b_transposed else B.shape[1]
+        D = np.empty((m, n), np.float32 if td == TD_F32 else np.uint16)
+        f = self.lib.ref_gemm_float
+        f.argtypes = [C.c_int, C.c_int, _sz, _sz, _sz, _vp, _sz, _vp, _sz, C.c_int, _vp, _sz, _vp, _sz, _vp, C.c_int,
+                      C.c_float, C.c_float]
+        f.restype = C.c_int
+        rc = f(ta, td, m, n, k, _ptr(A), A.shape[1], _ptr(B), B.shape[1], int(b_transposed), _ptr(Cm), n, _ptr(D), n,
+               _ptr(bias), int(bias_per_row), float(clamp[0]), float(clamp[1]))
+        if rc != 0:
+            raise ValueError("the reference does not instantiate this type combination")
+        return D
 
     def has_conv(self) -> bool:
         return self.lib is not None and hasattr(self.lib, "ref_im2col_i8")

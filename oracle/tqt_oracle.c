@@ -643,3 +643,34 @@ void tqo_im2col_i8(int channel_first, size_t group_idx, const int8_t *act, int8_
         }
     }
 }
+
+/* ------------------------------------------------------------------------- */
+/* Unquantised GEMM families (f32 / f16 / bf16 operands).                     */
+/* Follows test/common/reference_gemm.cpp:11-61: f32 accumulation in k order  */
+/* (separate multiply and add), + C, + bias (per column, or per row for the   */
+/* mx1bias types), clamp in f32, one narrowing to the output type.            */
+/* ta / td: TQO_TD_*; b_transposed: B is [n, ldb], else [k, ldb].             */
+/* ------------------------------------------------------------------------- */
+void tqo_gemm_float(int ta, int td, size_t m, size_t n, size_t k, const void *A, size_t lda,
+                    const void *B, size_t ldb, int b_transposed, const void *C, size_t ldc,
+                    void *D, size_t ldd, const void *bias, int bias_per_row, float clamp_min,
+                    float clamp_max)
+{
+#pragma omp parallel for schedule(static)
+    for (ptrdiff_t i = 0; i < (ptrdiff_t)m; ++i) {
+        for (size_t j = 0; j < n; ++j) {
+            float acc = 0.0f;
+            for (size_t p = 0; p < k; ++p) {
+                const float a = td_load(A, (size_t)i * lda + p, ta);
+                const float b = b_transposed ? td_load(B, j * ldb + p, ta) : td_load(B, p * ldb + j, ta);
+                const float prod = a * b;
+                acc = acc + prod;
+            }
+            if (C) acc += td_load(C, (size_t)i * ldc + j, td);
+            if (bias) acc += td_load(bias, bias_per_row ? (size_t)i : j, td);
+            acc = fmaxf(acc, clamp_min);
+            acc = fminf(acc, clamp_max);
+            td_store(D, (size_t)i * ldd + j, td, acc);
+        }
+    }
+}

@@ -183,6 +183,38 @@ def main():
         out[f"conv_{idx}_cl"] = ref.im2col_i8(act, geom, False, group_idx)
         out[f"conv_{idx}_cf"] = ref.im2col_i8(act, geom, True, group_idx)
     out["conv_cases"] = np.array([len(CONV_CASES)], np.int64)
+    # ---- unquantised GEMM families: reference_gemm<TA, TD> on the suite's shapes and options
+    # (test/gemm/test_gemm_f32_f32_rvv.cpp:30-49; inputs U(-1,1) seed 42 for A then B, seed 43 for C then bias,
+    # test/common/gemm_test_runner.h:326-365), both B layouts, column and row bias ----
+    tname = {TD_F32: "f32", TD_F16: "f16", TD_BF16: "bf16"}
+    npdt = {TD_F32: np.float32, TD_F16: np.float16, TD_BF16: "bf16"}
+    # (m, n, k, bias, c, clamp)
+    fl_cases = [(32, 32, 32, 0, 0, None), (5, 11, 10, 0, 0, None), (17, 19, 23, 0, 0, None), (60, 61, 127, 0, 0, None),
+                (31, 35, 63, 1, 0, None), (32, 32, 32, 0, 0, (-100.0, 150.0)), (31, 35, 63, 0, 1, None),
+                (60, 61, 127, 1, 1, (-100.0, 150.0)), (31, 35, 63, 1, 1, (-1.5, 2.0))]
+    for ta, td in ((TD_F32, TD_F32), (TD_F16, TD_F16), (TD_BF16, TD_BF16), (TD_BF16, TD_F32), (TD_BF16, TD_F16)):
+        for idx, (m, n, k, has_bias, has_c, clamp) in enumerate(fl_cases):
+            tag = f"fl_{tname[ta]}_{tname[td]}_{idx}"
+            AB = ref.fill_uniform((1, m * k + n * k), npdt[ta], -1.0, 1.0, 42).reshape(-1)
+            A, B = AB[:m * k].reshape(m, k).copy(), AB[m * k:].reshape(n, k).copy()
+            CB = ref.fill_uniform((1, m * n + max(m, n)), npdt[td], -1.0, 1.0, 43).reshape(-1)
+            Cm = CB[:m * n].reshape(m, n).copy() if has_c else None
+            bias_n = CB[m * n:m * n + n].copy() if has_bias else None
+            bias_m = CB[m * n:m * n + m].copy() if has_bias else None
+            bits = lambda x: None if x is None else (x.view(np.uint16) if x.dtype == np.float16 else x)
+            A_, B_ = bits(A), bits(B)
+            Bn_ = np.ascontiguousarray(B_.T)
+            cl = clamp if clamp else (-FMAX, FMAX)
+            out[tag + "_A"], out[tag + "_B"] = A_, B_
+            if has_c:
+                out[tag + "_C"] = bits(Cm)
+            if has_bias:
+                out[tag + "_bias"] = bits(CB[m * n:].copy())
+            out[tag + "_Dt"] = ref.gemm_float(ta, td, A_, B_, True, bits(Cm), bits(bias_n), False, cl)
+            out[tag + "_Dn"] = ref.gemm_float(ta, td, A_, Bn_, False, bits(Cm), bits(bias_n), False, cl)
+            out[tag + "_Dr"] = ref.gemm_float(ta, td, A_, B_, True, bits(Cm), bits(bias_m), True, cl)
+    out["fl_cases"] = np.array([(m, n, k, b, c, 0 if cl is None else 1, 0.0 if cl is None else cl[0], 0.0 if cl is None else cl[1])
+                                for m, n, k, b, c, cl in fl_cases], np.float64)
     path = os.path.join(HERE, "ref_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes,", len(out), "arrays")

@@ -25,7 +25,7 @@ def _declared_symbols():
     import subprocess
     names = set()
     for h in ("tqt_b200_common.h", "tqt_b200_gemm_i8_i8.h", "tqt_b200_gemm_i8_i4.h", "tqt_b200_gemm_f16_i4.h", "tqt_b200_gemm_siblings.h",
-              "tqt_b200_conv_i8_i8.h", "tqt_b200_ext.h"):
+              "tqt_b200_conv_i8_i8.h", "tqt_b200_gemm_float.h", "tqt_b200_ext.h"):
         out = subprocess.check_output(["/usr/bin/g++", "-E", "-P", "-x", "c++", os.path.join(ROOT, "include", h)], text=True)
         names |= set(re.findall(r"\b(tqt_[a-z0-9_]+?)\s*\(", out))
     return {n for n in names if not n.endswith("_t")}

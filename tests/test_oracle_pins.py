@@ -358,3 +358,32 @@ def test_im2col_live_reference_when_built(oracle):
         g = int(rng.integers(0, groups))
         for cf in (False, True):
             assert np.array_equal(oracle.im2col_i8(act, geom, cf, g), ref.im2col_i8(act, geom, cf, g))
+
+
+_FL_TYPES = (("f32", "f32"), ("f16", "f16"), ("bf16", "bf16"), ("bf16", "f32"), ("bf16", "f16"))
+_FL_TD = {"f32": TD_F32, "f16": TD_F16, "bf16": TD_BF16}
+
+
+def test_float_gemm_golden(oracle, golden):
+    """The unquantised GEMM restatement against the reference's reference_gemm<TA, TD> (test/common/reference_gemm.cpp:
+    11-88, compiled by oracle/Makefile ref) for the five type combinations it instantiates, on the float suites' shapes
+    with their bias / C / clamp options, B as [n, k] and [k, n], bias per column and per row: bit for bit."""
+    checked = 0
+    for ta, td in _FL_TYPES:
+        for idx, (m, n, k, has_bias, has_c, has_clamp, lo, hi) in enumerate(golden["fl_cases"]):
+            m, n, k = int(m), int(n), int(k)
+            tag = f"fl_{ta}_{td}_{idx}"
+            A, B = golden[tag + "_A"], golden[tag + "_B"]
+            Cm = golden[tag + "_C"] if has_c else None
+            bias = golden[tag + "_bias"] if has_bias else None
+            clamp = (lo, hi) if has_clamp else (-FMAX, FMAX)
+            bits = lambda x: x.view(np.uint32) if x.dtype == np.float32 else x
+            got = oracle.gemm_float(_FL_TD[ta], _FL_TD[td], A, B, True, Cm, None if bias is None else bias[:n].copy(), False, clamp)
+            assert np.array_equal(bits(got), bits(golden[tag + "_Dt"])), tag
+            got = oracle.gemm_float(_FL_TD[ta], _FL_TD[td], A, np.ascontiguousarray(B.T), False, Cm,
+                                    None if bias is None else bias[:n].copy(), False, clamp)
+            assert np.array_equal(bits(got), bits(golden[tag + "_Dn"])), tag
+            got = oracle.gemm_float(_FL_TD[ta], _FL_TD[td], A, B, True, Cm, None if bias is None else bias[:m].copy(), True, clamp)
+            assert np.array_equal(bits(got), bits(golden[tag + "_Dr"])), tag
+            checked += 3
+    assert checked == 5 * 9 * 3

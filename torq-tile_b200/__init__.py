@@ -527,6 +527,65 @@ class ConvI8(_UKernel):
         check("run_conv " + self.type_name)
 
 
+FLOAT_TYPES = (
+    [f"gemm_1xnbias_clamp_{t}_{t}_{t}{s}" for t in ("f32", "f16", "bf16") for s in ("", "p", "t")]
+    + [f"gemm_1xnbias_clamp_{t}_{t}p_{t}p" for t in ("f32", "f16", "bf16")]
+    + [f"gemm_mx1bias_clamp_{t}_{t}_{t}" for t in ("f32", "f16")] + [f"gemm_mx1bias_clamp_{t}_{t}p_{t}p" for t in ("f32", "f16")]
+    + [f"gemm_1xnbias_clamp_{td}_bf16{a}_bf16{b}" for td in ("f16", "f32") for a, b in (("", ""), ("", "t"), ("p", "p"))]
+)
+
+
+class FloatGemm(_UKernel):
+    """One of the unquantised GEMM kernel types (include/tqt_b200_gemm_float.h): gemm_<bias>_clamp_<TD>_<TA>[p]_<TB>[p|t]."""
+
+    def __init__(self, type_name: str):
+        self.type_name = type_name
+        parts = type_name.split("_")            # gemm, <bias>, clamp, TD, TA[p], TB[p|t]
+        self.bias_per_row = parts[1] == "mx1bias"
+        self.td = parts[3]
+        self.ta = parts[4].rstrip("p")
+        self.a_packed = parts[4].endswith("p")
+        self.b_packed = parts[5].endswith("p")
+        self.b_transposed = parts[5].endswith("t")
+        common = (("get_m_step", 0), ("get_n_step", 0), ("get_c_offset", 3), ("get_bias_offset", 1), ("get_d_offset", 3),
+                  ("get_d_size", 2))
+        own, packs = (), []
+        if self.a_packed:
+            own += (("get_a_packed_offset", 4), ("get_a_packed_size", 2))
+            packs.append("run_a_pack")
+        else:
+            own += (("get_a_offset", 3),)
+        if self.b_packed:
+            own += (("get_b_packed_offset", 4), ("get_b_packed_size", 2))
+            packs += ["run_b_pack", "run_bt_pack"]
+        else:
+            own += (("get_b_offset", 3),)
+        self.helpers_size = common + own
+        self.actions = [h[0] for h in self.helpers_size] + packs + ["run_gemm"]
+        super().__init__()
+
+    def run_a_pack(self, m, k, lda, lda_packed, k_idx, A, A_packed):
+        self._pack("run_a_pack", m, k, lda, lda_packed, k_idx, A, A_packed)
+
+    def run_b_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_b_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def run_bt_pack(self, n, k, ldb, ldb_packed, k_idx, B, B_packed):
+        self._pack("run_bt_pack", n, k, ldb, ldb_packed, k_idx, B, B_packed)
+
+    def run_gemm(self, m, n, k, A, lda, k_idx_a, B, ldb, k_idx_b, Cm, ldc, D, ldd, bias, clamp_min, clamp_max):
+        f = self._sym("run_gemm")
+        f.argtypes = [_sz, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _sz, _vp, _sz, _vp, _sz, _vp, C.c_float, C.c_float]
+        f.restype = None
+        if self.td == "f32":
+            lo, hi = C.c_float(clamp_min), C.c_float(clamp_max)
+        else:
+            cv = f16_bits if self.td == "f16" else bf16_bits
+            lo, hi = half_arg(cv(clamp_min)), half_arg(cv(clamp_max))
+        f(m, n, k, _addr(A), lda, k_idx_a, _addr(B), ldb, k_idx_b, _addr(Cm), ldc, _addr(D), ldd, _addr(bias), lo, hi)
+        check("run_gemm " + self.type_name)
+
+
 IGEMM_TYPES = ("igemmcl_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxp", "igemmcl_1xnbias_reqi32toi8_clamp_qai8_qai8_qsi8cxt",
                "igemmcf_mx1bias_reqi32toi8_clamp_qai8_qsi8dx_qai8", "igemmcf_mx1bias_reqi32toi8_clamp_qai8_qsi8dxp_qai8")
 
@@ -636,4 +695,4 @@ EXTENSION_SYMBOLS = (
 def all_ukernels():
     return [GemmClampI32I8I8(), GemmClampI32I8pI8p(), GemmReqI8(), GemmW4A8("f32"), GemmW4A8("f16"),
             GemmW4A8("bf16"), GemmW4A16("f16"), GemmW4A16("f32")] + [SiblingGemm(t) for t in SIBLING_TYPES] + \
-           [ConvI8(t) for t in CONV_TYPES] + [IgemmI8(t) for t in IGEMM_TYPES]
+           [ConvI8(t) for t in CONV_TYPES] + [IgemmI8(t) for t in IGEMM_TYPES] + [FloatGemm(t) for t in FLOAT_TYPES]

@@ -5,6 +5,7 @@
 #include "../../include/tqt_b200_conv_i8_i8.h"
 #include "../../include/tqt_b200_ext.h"
 #include "../../include/tqt_b200_gemm_f16_i4.h"
+#include "../../include/tqt_b200_gemm_float.h"
 #include "../../include/tqt_b200_gemm_i8_i4.h"
 #include "../../include/tqt_b200_gemm_i8_i8.h"
 #include "../../include/tqt_b200_gemm_siblings.h"
@@ -500,6 +501,7 @@ void tqt_cuda_set_output_replicas(const void *local_base, size_t local_bytes, vo
 
 #include "abi_siblings.inc"
 #include "abi_conv.inc"
+#include "abi_float.inc"
 
 int tqt_cuda_debug_last_kernel(void) { return last_kernel(); }
 

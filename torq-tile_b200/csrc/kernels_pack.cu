@@ -154,11 +154,16 @@ static Result pack_rows_impl(void *stream, size_t rows, size_t k, size_t ld_src,
             pack_rows_kernel<1, true><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
         else
             pack_rows_kernel<1, false><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
-    } else {
+    } else if (elem_size == 2) {
         if (transposed_src)
             pack_rows_kernel<2, true><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
         else
             pack_rows_kernel<2, false><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
+    } else {
+        if (transposed_src)
+            pack_rows_kernel<4, true><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
+        else
+            pack_rows_kernel<4, false><<<grid, threads, 0, st>>>(rows, k, ld_src, kblocks_total, s, d, kblocks, chunks, block_bytes);
     }
     return check_launch();
 }

@@ -127,7 +127,9 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
     const uint32_t tiles_m = (args.m + 127) / 128, pmc = (tiles_m + 1) / 2;
     const uint32_t nblocks = (args.n + 127) / 128, tnc = (nblocks + 1) / 2;
     const uint32_t num_tiles = pmc * tnc;
-    const uint32_t KB = (args.k + 127) / 128;
+    constexpr bool kFloat = EK == EpiKind::Float;   // 16-bit floating-point operands (kind::f16), f32 accumulators
+    constexpr uint32_t kElem = kFloat ? 2u : 1u;
+    const uint32_t KB = (args.k * kElem + 127) / 128;   // K blocks of 128 bytes per row
     // a B fetched by tiled TMA loads is always taken two blocks at a time (a box beyond the matrix is zeros); its tiles are not split
     const bool b_whole = TMA && args.b_src != kSrcBlocks;
     const I8Split sp = i8_split(num_tiles, npairs, !b_whole);
@@ -232,8 +234,10 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
         // latency of the test (~200 cycles even on a long-completed phase) off the critical path.
         if (lane == 0) {
             const bool b_mn = TMA && args.b_src == kSrcTmaMn;
-            const uint32_t idesc256 = ptx::make_idesc(2u, 1u, 1u, 256, 256) | (b_mn ? ptx::kIdescBMajorMn : 0u);
-            const uint32_t idesc128 = ptx::make_idesc(2u, 1u, 1u, 256, 128);
+            const uint32_t ffmt = args.in_bf16 ? 1u : 0u;
+            const uint32_t idesc256 = kFloat ? ptx::make_idesc(1u, ffmt, ffmt, 256, 256)
+                                             : (ptx::make_idesc(2u, 1u, 1u, 256, 256) | (b_mn ? ptx::kIdescBMajorMn : 0u));
+            const uint32_t idesc128 = kFloat ? ptx::make_idesc(1u, ffmt, ffmt, 256, 128) : ptx::make_idesc(2u, 1u, 1u, 256, 128);
             const uint64_t a_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sA)), b_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sB));
             const uint32_t a_lo0 = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
@@ -256,7 +260,9 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                         break;
                     }
                     ptx::tc_fence_after();
-                    if (b_mn)
+                    if constexpr (kFloat)
+                        ptx::mma_f16_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
+                    else if (b_mn)
                         ptx::mma_i8_ss_pair_group4<256>(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
                     else
                         ptx::mma_i8_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);   // 16 KiB stages = 1024 units
@@ -357,6 +363,16 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                     row_zp = args.zp_a[mrow];
                 }
             }
+            // unquantised GEMM: bias per column (staged as float bits) or per row (this thread's constant)
+            float row_bias_f = 0.0f;
+            if constexpr (EK == EpiKind::Float) {
+                for (uint32_t c = lane; c < 128u; c += 32u) {
+                    float bv = 0.0f;
+                    if (c < ncols && args.bias && !args.bias_per_row) bv = TdTraits<TD>::load(args.bias, n0 + c);
+                    sCol[256 + c] = __float_as_int(bv);
+                }
+                if (row_ok && args.bias && args.bias_per_row) row_bias_f = TdTraits<TD>::load(args.bias, mrow);
+            }
             // per-row requantisation (Mx1 bias types): this thread's row has one multiplier, shift and bias
             int32_t row_mult = 0, row_rsh = 0, row_bias = 0;
             if constexpr (EK == EpiKind::Req8Row) {
@@ -386,7 +402,7 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                     const uint32_t c0 = ch * 32u;
                     const uint32_t nvalid = min(32u, ncols - c0);
                     alignas(16) OutT out[32];
-                    if constexpr (EK != EpiKind::DxCx) {
+                    if constexpr (EK != EpiKind::DxCx && EK != EpiKind::Float) {
                         // the optional C operand: one uniform branch per strip, so the loop below has none
                         if (args.C) {
                             const int32_t *crow = static_cast<const int32_t *>(args.C) + mrow * args.ldc + n0 + c0;
@@ -401,6 +417,14 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                         if constexpr (EK == EpiKind::S32) {
                             const int32_t v = (int32_t)r[j];
                             out[j] = max(args.cmin_i, min(args.cmax_i, v));
+                        } else if constexpr (EK == EpiKind::Float) {
+                            // + C, + bias, clamp in f32, one narrowing (test/common/reference_gemm.cpp:38-57); nothing is
+                            // added where the caller passed no C / no bias (x + 0 would turn -0 into +0)
+                            float v = __uint_as_float(r[j]);
+                            if (args.C && j < nvalid) v = __fadd_rn(v, TdTraits<TD>::load(args.C, mrow * args.ldc + n0 + c));
+                            if (has_bias) v = __fadd_rn(v, args.bias_per_row ? row_bias_f : __int_as_float(sCol[256 + c]));
+                            v = fminf(fmaxf(v, args.cmin_f), args.cmax_f);
+                            out[j] = cvt_out<OutT>(v);
                         } else if constexpr (EK == EpiKind::DxCx) {
                             // acc - zp_a * rowsum(b), then r = (float)acc * (scale_b * scale_a); f32: + bias, clamp;
                             // f16: narrow first, then add the bias and clamp in f16 (as EpiDxCx in epilogues.cuh)
@@ -1325,6 +1349,26 @@ Result pair_gemm_i8_tma(const UmmaArgs &a_in, EpiKind ek, Dtype td, size_t lda, 
         case EpiKind::Req8Row:
             return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::Req8Row>, a, tiles, true, kI8Threads, kI8Smem, st, set_row, maps);
         default: return Result{kUnsupported, 0};
+    }
+}
+
+// Unquantised f16 / bf16 GEMM: the same kernel with kind::f16 MMAs and the float epilogue.  Operands packed (128-row blocks
+// of 64 elements per row) or row-major [rows, k] through tensor maps.
+Result pair_gemm_f16(const UmmaArgs &a_in, bool bf16, Dtype td, bool bias_per_row, size_t lda, size_t ldb, cudaStream_t st)
+{
+    UmmaArgs a = a_in;
+    a.in_bf16 = bf16 ? 1 : 0;
+    a.bias_per_row = bias_per_row ? 1 : 0;
+    TmaOperands maps{};
+    if (a.a_src == kSrcTmaK && !encode_i8_map(&maps.a, a.A, (size_t)a.k * 2, a.m, lda * 2)) return Result{kUnsupported, 0};
+    if (a.b_src == kSrcTmaK && !encode_i8_map(&maps.b, a.B, (size_t)a.k * 2, a.n, ldb * 2)) return Result{kUnsupported, 0};
+    const uint32_t tiles = i8_launch_items(a, a.b_src != kSrcBlocks);
+    static bool set_f32[64] = {false}, set_f16[64] = {false}, set_bf16[64] = {false};
+    note_kernel(a.a_src == kSrcBlocks && a.b_src == kSrcBlocks ? kKernelPairBlocks : kKernelPairTma);
+    switch (td) {
+        case Dtype::F32: return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::Float, Dtype::F32>, a, tiles, true, kI8Threads, kI8Smem, st, set_f32, maps);
+        case Dtype::F16: return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::Float, Dtype::F16>, a, tiles, true, kI8Threads, kI8Smem, st, set_f16, maps);
+        default: return launch_grid(gemm_pair_i8_tma_kernel<EpiKind::Float, Dtype::BF16>, a, tiles, true, kI8Threads, kI8Smem, st, set_bf16, maps);
     }
 }
 

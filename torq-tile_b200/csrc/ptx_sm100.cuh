@@ -421,6 +421,34 @@ __device__ __forceinline__ void mma_i8_ss_pair_group4(uint32_t d_tmem, uint32_t 
         : "memory");
 }
 
+// The same block for 16-bit floating-point operands (kind::f16: f16 or bf16 by the instruction descriptor, f32
+// accumulation, K = 16 per instruction = 32 bytes, so the descriptors step as for int8).
+template <uint32_t BSTEP = 2>
+__device__ __forceinline__ void mma_f16_ss_pair_group4(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                       uint32_t idesc, uint32_t accum_first)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, pt;\n\t"
+        ".reg .b32 la, lb;\n\t"
+        ".reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "setp.eq.b32 pt, 0, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\t mov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t"
+        "add.u32 la, %1, 2;\n\t add.u32 lb, %3, %7;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "add.u32 la, %1, 4;\n\t add.u32 lb, %3, %8;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "add.u32 la, %1, 6;\n\t add.u32 lb, %3, %9;\n\t mov.b64 da, {la, %2};\n\t mov.b64 db, {lb, %4};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, pt;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accum_first), "n"(BSTEP), "n"(2 * BSTEP),
+          "n"(3 * BSTEP)
+        : "memory");
+}
+
 // A group of eight TS MMAs (two K steps of four K slices) in one instruction block, to keep the issuing
 // thread's instruction count per MMA at its minimum (the thread is the bottleneck of the mainloop).  MMA q = 4 h + j
 // takes its M-side operand at a_tmem + 8 q, its N-side descriptor at desc + h * stage16 + 2 j (only the low word of

@@ -150,6 +150,11 @@ Result launch_im2col_pack_i8(void *stream, const ConvGeom &g, bool channel_first
 // Gather into a plain matrix: [rows, k] for channel-last, [k, rows] for channel-first.
 Result launch_im2col_i8(void *stream, const ConvGeom &g, bool channel_first, const void *activation, void *matrix);
 
+// Unquantised GEMM (kernels_float.cu, kernels_pair.cu): operands of type ta in layouts la / lb (A never KMajor), C, bias
+// and D of type td, bias per column or per row.
+Result launch_gemm_float(const GemmCommon &g, Dtype ta, Dtype td, float clamp_min, float clamp_max, Layout la, Layout lb,
+                         bool bias_per_row);
+
 // Implicit-GEMM convolutions: see kernels_simt.cu.
 Result launch_igemm_cl_requant_i8(const GemmCommon &g, const ConvGeom &geom, uint32_t pos0, const void *input,
                                   const RequantParams &p, int clamp_min, int clamp_max, Layout weights);

@@ -6,7 +6,7 @@
 namespace tqt {
 
 enum class BMode : int { I8 = 0, I4Cx = 1, I4C2 = 2 };
-enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3, Req8Row = 4, DxCx = 5 };
+enum class EpiKind : int { S32 = 0, Req8 = 1, W4A8 = 2, W4A16 = 3, Req8Row = 4, DxCx = 5, Float = 6 };
 
 // How the int8 CTA-pair kernel fetches an operand: packed 16 KiB blocks by untiled bulk copies, or boxes of the caller's
 // row-major matrix by tiled TMA loads (K-major: k contiguous; MN-major, B only: n contiguous).
@@ -25,6 +25,8 @@ struct UmmaArgs {
     uint32_t m, n, k;
     uint32_t a_src, b_src;     // kSrc*: int8 CTA-pair kernel with tensor maps only
     size_t b_ld;               // row stride (bytes) of a row-major B fetched through a tensor map
+    int in_bf16;               // unquantised 16-bit GEMM: operands are bf16 (else f16)
+    int bias_per_row;          // unquantised GEMM: bias indexed by output row (mx1bias types)
     const uint8_t *A;
     const uint8_t *B;
     uint32_t a_kblocks_total;  // blocks per row-tile in the A buffer
@@ -94,6 +96,8 @@ template <Dtype TD>
 struct OutType<EpiKind::Req8Row, TD> { using type = int8_t; };
 template <Dtype TD>
 struct OutType<EpiKind::DxCx, TD> { using type = typename TdTraits<TD>::type; };
+template <Dtype TD>
+struct OutType<EpiKind::Float, TD> { using type = typename TdTraits<TD>::type; };
 template <Dtype TD>
 struct OutType<EpiKind::W4A8, TD> { using type = typename TdTraits<TD>::type; };
 template <Dtype TD>
