@@ -83,8 +83,8 @@ def test_float_gemm(oracle, type_idx, m, n, k, has_bias, has_c, clamp):
     sync_and_check()
     got = d.cpu().numpy() if td == "f32" else bits16(d)
     fam = p.debug_last_kernel()
-    tensor_ok = ta != "f32" and (uk.b_packed or uk.b_transposed)
-    aligned = (uk.a_packed or (2 * k) % 16 == 0) and (uk.b_packed or (2 * k) % 16 == 0)
+    tensor_ok = ta != "f32"
+    aligned = (uk.a_packed or (2 * k) % 16 == 0) and (uk.b_packed or (2 * (k if uk.b_transposed else n)) % 16 == 0)
     if not tensor_ok or not aligned:
         assert fam == SIMT
         assert np.array_equal(got.view(np.uint32) if td == "f32" else got, want.view(np.uint32) if td == "f32" else want)

@@ -193,10 +193,16 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                 if (lane == 0) {
                     if (b_tma) {
                         const int32_t rows0 = (int32_t)((wk.bn0 + rank) * 128u), k0 = (int32_t)(kb * 128u);
-                        if (args.b_src == kSrcTmaMn)
-                            ptx::tma_load_2d(ptx::smem_u32(sB + s * 16384), &maps->b, rows0, k0, BAR(kFull + s));
-                        else
+                        if (args.b_src == kSrcTmaMn) {
+                            // B stored [k, n]: x runs along n.  int8: one box of 128 columns x 128 k rows; 16-bit types: the
+                            // first of two boxes of 64 columns (128 bytes) x 64 k rows (lane 2 issues the second)
+                            if constexpr (kFloat)
+                                ptx::tma_load_2d(ptx::smem_u32(sB + s * 16384), &maps->b, rows0 * 2, (int32_t)(kb * 64u), BAR(kFull + s));
+                            else
+                                ptx::tma_load_2d(ptx::smem_u32(sB + s * 16384), &maps->b, rows0, k0, BAR(kFull + s));
+                        } else {
                             ptx::tma_load_2d(ptx::smem_u32(sB + s * 16384), &maps->b, k0, rows0, BAR(kFull + s));
+                        }
                     } else {
                         ptx::bulk_g2s(ptx::smem_u32(sB + s * 16384), b_src + (size_t)kb * bbb, b_bytes, BAR(kFull + s));
                     }
@@ -206,6 +212,9 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                                          BAR(kFull + s));
                     else
                         ptx::bulk_g2s(ptx::smem_u32(sA + s * 16384), a_src + (size_t)kb * kI8BlockBytes, 16384u, BAR(kFull + s));
+                } else if (kFloat && lane == 2 && b_tma && args.b_src == kSrcTmaMn) {
+                    const int32_t cols1 = (int32_t)(((wk.bn0 + rank) * 128u + 64u) * 2u);   // the second 64 columns, in bytes
+                    ptx::tma_load_2d(ptx::smem_u32(sB + s * 16384 + 8192), &maps->b, cols1, (int32_t)(kb * 64u), BAR(kFull + s));
                 }
                 __syncwarp();
             }
@@ -235,10 +244,13 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
         if (lane == 0) {
             const bool b_mn = TMA && args.b_src == kSrcTmaMn;
             const uint32_t ffmt = args.in_bf16 ? 1u : 0u;
-            const uint32_t idesc256 = kFloat ? ptx::make_idesc(1u, ffmt, ffmt, 256, 256)
-                                             : (ptx::make_idesc(2u, 1u, 1u, 256, 256) | (b_mn ? ptx::kIdescBMajorMn : 0u));
+            const uint32_t idesc256 = (kFloat ? ptx::make_idesc(1u, ffmt, ffmt, 256, 256) : ptx::make_idesc(2u, 1u, 1u, 256, 256)) |
+                                      (b_mn ? ptx::kIdescBMajorMn : 0u);
             const uint32_t idesc128 = kFloat ? ptx::make_idesc(1u, ffmt, ffmt, 256, 128) : ptx::make_idesc(2u, 1u, 1u, 256, 128);
-            const uint64_t a_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sA)), b_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sB));
+            // a 16-bit MN-major stage is two column groups of 64 (128 bytes wide, 64 k rows each) 8 KiB apart
+            const uint64_t a_desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sA)),
+                           b_desc0 = (kFloat && b_mn) ? ptx::make_desc_sw128(ptx::smem_u32(sB), 8192u, 1024u)
+                                                      : ptx::make_desc_k_sw128(ptx::smem_u32(sB));
             const uint32_t a_lo0 = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
             uint32_t it = 0, ti = 0, s = 0, ph = 0;
@@ -260,9 +272,12 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                         break;
                     }
                     ptx::tc_fence_after();
-                    if constexpr (kFloat)
-                        ptx::mma_f16_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
-                    else if (b_mn)
+                    if constexpr (kFloat) {
+                        if (b_mn)   // K slices of 16 rows of 128 bytes
+                            ptx::mma_f16_ss_pair_group4<128>(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
+                        else
+                            ptx::mma_f16_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
+                    } else if (b_mn)
                         ptx::mma_i8_ss_pair_group4<256>(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
                     else
                         ptx::mma_i8_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);   // 16 KiB stages = 1024 units
@@ -1362,6 +1377,7 @@ Result pair_gemm_f16(const UmmaArgs &a_in, bool bf16, Dtype td, bool bias_per_ro
     TmaOperands maps{};
     if (a.a_src == kSrcTmaK && !encode_i8_map(&maps.a, a.A, (size_t)a.k * 2, a.m, lda * 2)) return Result{kUnsupported, 0};
     if (a.b_src == kSrcTmaK && !encode_i8_map(&maps.b, a.B, (size_t)a.k * 2, a.n, ldb * 2)) return Result{kUnsupported, 0};
+    if (a.b_src == kSrcTmaMn && !encode_byte_map(&maps.b, a.B, (size_t)a.n * 2, a.k, ldb * 2, 128, 64)) return Result{kUnsupported, 0};
     const uint32_t tiles = i8_launch_items(a, a.b_src != kSrcBlocks);
     static bool set_f32[64] = {false}, set_f16[64] = {false}, set_bf16[64] = {false};
     note_kernel(a.a_src == kSrcBlocks && a.b_src == kSrcBlocks ? kKernelPairBlocks : kKernelPairTma);

@@ -827,10 +827,10 @@ Result pair_gemm_f16(const UmmaArgs &a, bool bf16, Dtype td, bool bias_per_row, 
 Result umma_gemm_float(const GemmCommon &g, Dtype ta, Dtype td, float cmin, float cmax, Layout la, Layout lb, bool bias_per_row)
 {
     UmmaArgs a{};
-    if (ta == Dtype::F32 || lb == Layout::KMajor) return Result{kUnsupported, 0};   // B [k, n] of 16-bit types: generic kernel
+    if (ta == Dtype::F32) return Result{kUnsupported, 0};
     if (!fill_common(a, g, td == Dtype::F32 ? 4 : 2, 64, 64) || a.n_replicas) return Result{kUnsupported, 0};
     a.a_src = la == Layout::Packed ? kSrcBlocks : kSrcTmaK;
-    a.b_src = lb == Layout::Packed ? kSrcBlocks : kSrcTmaK;
+    a.b_src = lb == Layout::Packed ? kSrcBlocks : lb == Layout::RowMajor ? kSrcTmaK : kSrcTmaMn;
     a.cmin_f = cmin;
     a.cmax_f = cmax;
     a.band_m = choose_band(g.m * g.k * 2, g.n * g.k * 2);

@@ -228,6 +228,14 @@ __device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t smem_addr)
 // [4,6) D format (0 f16, 1 f32, 2 s32); [7,10) A format; [10,13) B format; bit 15 / 16: A / B operand MN-major;
 // [17,23) N>>3; [24,29) M>>4.
 // kind::i8 formats: 0 = u8, 1 = s8.  kind::f16 formats: 0 = f16, 1 = bf16.
+// The same descriptor with explicit byte offsets: lbo between 128-byte-wide groups along the operand's M / N dimension
+// (MN-major operands wider than one group), sbo between groups of 8 rows.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo)
+{
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo >> 4) & 0x3FFFu) << 16) | ((uint64_t)((sbo >> 4) & 0x3FFFu) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+
 constexpr uint32_t kIdescBMajorMn = 1u << 16;   // N-side operand MN-major (its rows run along K in shared memory)
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t d_fmt, uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n)
 {
