@@ -590,17 +590,17 @@ def bench_layout(torch, pkg, dev, peaks):
     out = {}
 
     def time_us(fn, sets, reps=3):
-        for i in range(sets):
-            fn(i)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for r in range(reps):
+        """us per launch of fn(i), i over the rotating sets, replayed as one CUDA graph (no host launch cost in the figure)."""
+        stream = torch.cuda.Stream()
+
+        def all_sets():
+            pkg.use_current_torch_stream()
             for i in range(sets):
                 fn(i)
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) * 1e3 / (reps * sets)
+
+        us = _graph_time_us(torch, stream, all_sets, sets, max(reps, 3))
+        pkg.use_current_torch_stream()
+        return us
 
     sets = 6
     nibs = [torch.randint(0, 256, (N, K // 2), device=dev, dtype=torch.uint8) for _ in range(sets)]

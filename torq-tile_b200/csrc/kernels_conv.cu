@@ -64,6 +64,41 @@ __global__ void __launch_bounds__(256) im2col_pack_i8_kernel(ConvGeom g, const i
     }
 }
 
+// Channel-last inputs whose channel counts are multiples of 16: thread (row, chunk c) walks the K blocks of its row,
+// carrying the kernel-window cursor forward by 128 columns per step instead of dividing the column index down again, so a
+// 16-byte chunk costs a bounds test, a 128-bit load and a 128-bit store.  A warp still writes four rows x 128 contiguous bytes.
+__global__ void __launch_bounds__(256) im2col_pack_cl16_kernel(ConvGeom g, const int8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                                               size_t kblocks, size_t kblocks_total, size_t total_threads)
+{
+    for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total_threads; idx += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t c = (uint32_t)(idx & 7);
+        const size_t row = idx >> 3;               // rows of all tiles, padding rows of the last tile included
+        const uint32_t r = (uint32_t)(row & 127);
+        uint8_t *out = dst + (row >> 7) * kblocks_total * kI8BlockBytes + sw128_byte(r, c * 16);
+        const bool row_ok = row < g.rows;
+        uint32_t od = 0, oh = 0, ow = 0;
+        KCursor<false> cur;
+        cur.kd = cur.kh = cur.kw = cur.ic = 0;
+        if (row_ok) {
+            split_position(g, (uint32_t)row, od, oh, ow);
+            cur.seek(g, c * 16u);
+        }
+        uint32_t k0 = c * 16u;
+        for (size_t kb = 0; kb < kblocks; ++kb, k0 += 128u, out += kI8BlockBytes) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            size_t off;
+            if (row_ok && k0 < g.k && cur.source(g, od, oh, ow, off)) v = *reinterpret_cast<const uint4 *>(src + off);
+            *reinterpret_cast<uint4 *>(out) = v;
+            // 128 columns on: whole kernel taps are skipped a channel run at a time
+            cur.ic += 128u;
+            while (cur.ic >= g.ic_pg) {
+                cur.ic -= g.ic_pg;
+                if (++cur.kw == g.ker[2]) { cur.kw = 0; if (++cur.kh == g.ker[1]) { cur.kh = 0; ++cur.kd; } }
+            }
+        }
+    }
+}
+
 // Plain im2col matrix: channel-last [rows, k] (consecutive threads along k = along the input's channels), channel-first
 // [k, rows] (consecutive threads along the output positions).
 template <bool CF>
@@ -108,8 +143,14 @@ Result launch_im2col_pack_i8(void *stream, const ConvGeom &g, bool channel_first
                                                                      kblocks_total, chunks, 0);
     } else {
         const int vec_ok = g.ic_pg % 16 == 0 && g.c_total % 16 == 0 && (reinterpret_cast<uintptr_t>(activation) & 15) == 0;
-        im2col_pack_i8_kernel<false><<<grid_for(chunks), 256, 0, st>>>(g, (const int8_t *)activation, (uint8_t *)packed, kblocks,
-                                                                      kblocks_total, chunks, vec_ok);
+        if (vec_ok) {
+            const size_t threads = ceil_div(g.rows, 128) * 128 * 8;
+            im2col_pack_cl16_kernel<<<grid_for(threads), 256, 0, st>>>(g, (const int8_t *)activation, (uint8_t *)packed, kblocks,
+                                                                      kblocks_total, threads);
+        } else {
+            im2col_pack_i8_kernel<false><<<grid_for(chunks), 256, 0, st>>>(g, (const int8_t *)activation, (uint8_t *)packed, kblocks,
+                                                                          kblocks_total, chunks, 0);
+        }
     }
     return conv_check_launch();
 }
