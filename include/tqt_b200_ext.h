@@ -29,6 +29,29 @@ void tqt_run_quant_pack_qai8dxp_f16_128x128_sm100a(size_t m, size_t k, const voi
                                                    float *scale_a, int32_t *zero_point_a);
 void tqt_run_quant_pack_qai8dxp_bf16_128x128_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_packed,
                                                     float *scale_a, int32_t *zero_point_a);
+/* Quantise + GEMM in one call: the activations A (a_type 0 = f32, 1 = f16, 2 = bf16; [m, lda]) are quantised into the
+ * caller's A_packed / scale_a / zero_point_a buffers (sized as for tqt_run_quant_pack_qai8dxp_*) and the W4A8 GEMM of
+ * the same output type runs on them: D = clamp((A_q x B) * scale_a * scale_b + C + bias).  For 16-bit activations with
+ * k <= 4096 and more than 16 rows this is ONE cooperative launch (the GEMM kernel quantises its own activations, one
+ * row per warp, and crosses a grid-wide barrier before its mainloop); other shapes run the two kernels back to back.
+ * Results are those of the two separate calls, bit for bit.  The grid barrier uses a file-scope device array of the
+ * library: do not run two of these calls at the same time on one device (calls on one stream never do).  No
+ * counterpart in the reference, whose callers quantise on the host. */
+void tqt_run_quant_gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp_128x128_sm100a(
+    size_t m, size_t n, size_t k, const void *A, size_t lda, int a_type, void *A_packed, float *scale_a,
+    int32_t *zero_point_a, const void *B_packed, size_t ldb, const void *C, size_t ldc, void *D, size_t ldd,
+    const void *bias, float clamp_min, float clamp_max, const float *scale_b);
+#if !defined(TQT_B200_NO_HALF_TYPES)
+void tqt_run_quant_gemm_1xnbias_clamp_f16_qai8dxp_qsi4cxp_128x128_sm100a(
+    size_t m, size_t n, size_t k, const void *A, size_t lda, int a_type, void *A_packed, float *scale_a,
+    int32_t *zero_point_a, const void *B_packed, size_t ldb, const void *C, size_t ldc, void *D, size_t ldd,
+    const void *bias, float16_t clamp_min, float16_t clamp_max, const float *scale_b);
+void tqt_run_quant_gemm_1xnbias_clamp_bf16_qai8dxp_qsi4cxp_128x128_sm100a(
+    size_t m, size_t n, size_t k, const void *A, size_t lda, int a_type, void *A_packed, float *scale_a,
+    int32_t *zero_point_a, const void *B_packed, size_t ldb, const void *C, size_t ldc, void *D, size_t ldd,
+    const void *bias, bfloat16_t clamp_min, bfloat16_t clamp_max, const float *scale_b);
+#endif
+
 /* Same quantiser with a plain row-major int8 result [m,k] (ldq in elements), for the unpacked
  * (qai8dx) kernel types and for inspection. */
 void tqt_run_quant_qai8dx_f32_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_q, size_t ldq,

@@ -163,7 +163,7 @@ def test_quantiser_strided_rows(oracle):
 
 
 @pytest.mark.parametrize("ta", ["f16", "bf16"])
-@pytest.mark.parametrize("m,k", [(256, 4096), (40, 1024), (33, 16), (128, 4080)])
+@pytest.mark.parametrize("m,k", [(256, 4096), (40, 1024), (33, 16), (128, 4080), (45, 2064), (50, 1040), (37, 3088), (20000, 1024)])
 def test_quantiser_rows_in_registers_exact_division(oracle, m, k, ta):
     """Many 16-bit rows with k <= 4096 take the warp-per-row kernel, which divides by the row scale
     through a corrected reciprocal.  Values are planted next to the rounding boundaries (quotients

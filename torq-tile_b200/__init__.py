@@ -646,6 +646,27 @@ def quant_pack_qai8dxp(A, A_packed, scale_a, zero_point_a, m=None, k=None, lda=N
     check("quant_pack_qai8dxp")
 
 
+_A_TYPE = {"f32": 0, "f16": 1, "bf16": 2}
+
+
+def quant_gemm_w4a8(td, m, n, k, A, lda, A_packed, scale_a, zero_point_a, B_packed, ldb, Cm, ldc, D, ldd, bias, clamp_min,
+                    clamp_max, scale_b):
+    """tqt_run_quant_gemm_1xnbias_clamp_<td>_qai8dxp_qsi4cxp: quantise the activations A (f32 / f16 / bf16 tensor) and run
+    the W4A8 GEMM on them; one cooperative launch where the library has a fused form for the shape."""
+    f = getattr(lib(), f"tqt_run_quant_gemm_1xnbias_clamp_{td}_qai8dxp_qsi4cxp_{VARIANT}")
+    f.argtypes = [_sz, _sz, _sz, _vp, _sz, C.c_int, _vp, _vp, _vp, _vp, _sz, _vp, _sz, _vp, _sz, _vp, C.c_float, C.c_float, _vp]
+    f.restype = None
+    a_type = _A_TYPE[_TA_NAMES[str(A.dtype).replace("torch.", "")]]
+    if td == "f32":
+        lo, hi = C.c_float(clamp_min), C.c_float(clamp_max)
+    else:
+        cv = f16_bits if td == "f16" else bf16_bits
+        lo, hi = half_arg(cv(clamp_min)), half_arg(cv(clamp_max))
+    f(m, n, k, _addr(A), lda, a_type, _addr(A_packed), _addr(scale_a), _addr(zero_point_a), _addr(B_packed), ldb, _addr(Cm), ldc,
+      _addr(D), ldd, _addr(bias), lo, hi, _addr(scale_b))
+    check("quant_gemm_w4a8")
+
+
 def quant_qai8dx(A, A_q, scale_a, zero_point_a):
     """Same quantiser with a plain row-major int8 result."""
     ta = _TA_NAMES[str(A.dtype).replace("torch.", "")]
@@ -687,6 +708,7 @@ EXTENSION_SYMBOLS = (
      "tqt_cuda_debug_stream_read", "tqt_cuda_set_output_replicas", "tqt_cuda_debug_set_path", "tqt_cuda_debug_inject_wait_failure",
      "tqt_cuda_debug_last_kernel"]
     + [f"tqt_run_quant_pack_qai8dxp_{t}_{VARIANT}" for t in ("f32", "f16", "bf16")]
+    + [f"tqt_run_quant_gemm_1xnbias_clamp_{t}_qai8dxp_qsi4cxp_{VARIANT}" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_quant_qai8dx_{t}_sm100a" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_{n}_{VARIANT}" for n in ("a_unpack_i8", "a_unpack_f16", "bt_unpack_qsi4cxp", "bt_unpack_qsi4c2p")]
 )

@@ -135,6 +135,30 @@ void run_quant(size_t m, size_t k, const void *A, size_t lda, void *out, size_t 
     set_result(launch_quant_qai8dx(t_stream, m, k, A, lda, ta, out, ldq, packed, scale_a, zp_a));
 }
 
+// Quantise the activations and run the W4A8 GEMM: one cooperative launch where the shape allows (the GEMM kernel
+// quantises its own activations before its mainloop), else the quantiser and the GEMM as two launches.
+void run_quant_w4a8(size_t m, size_t n, size_t k, const void *A, size_t lda, int a_type, void *A_packed, float *scale_a,
+                    int32_t *zp_a, const void *B_packed, size_t ldb, const void *C, size_t ldc, void *D, size_t ldd,
+                    const void *bias, float cmin, float cmax, const float *scale_b, Dtype td)
+{
+    if (a_type < 0 || a_type > 2 || (k & 1)) return set_invalid();
+    if (m && n && (!A || !A_packed || !scale_a || !zp_a || !B_packed || !D || !scale_b)) return set_invalid();
+    if (m == 0 || n == 0) return set_ok();
+    if (ldb < k) ldb = k;
+    if (!replicas_cover(m, n, D, ldd, td == Dtype::F32 ? 4 : 2)) return set_invalid();
+    const Dtype ta = (Dtype)a_type;
+    note_kernel(kKernelNone);
+    GemmCommon g = common(m, n, k, A_packed, k, B_packed, ldb, C, ldc, D, ldd, bias);
+    W4A8Params p{scale_a, zp_a, scale_b};
+    if (ta != Dtype::F32 && env_path() == Path::Auto && m > 16) {
+        Result r = umma_gemm_w4a8_fusedq(g, p, td, cmin, cmax, A, lda, ta == Dtype::BF16);
+        if (r.status != kUnsupported) return set_result(r);
+    }
+    Result q = launch_quant_qai8dx(t_stream, m, k, A, lda, ta, A_packed, 0, true, scale_a, zp_a);
+    if (q.status != kOk) return set_result(q);
+    set_result(launch_gemm_w4a8(g, p, td, cmin, cmax, env_path()));
+}
+
 }  // namespace
 
 extern "C" {
@@ -414,6 +438,19 @@ void tqt_run_quant_pack_qai8dxp_bf16_128x128_sm100a(size_t m, size_t k, const vo
 {
     run_quant(m, k, A, lda, A_packed, 0, true, scale_a, zero_point_a, Dtype::BF16);
 }
+#define TQT_DEFINE_QUANT_GEMM(TDNAME, TDTYPE, TDENUM)                                                                  \
+    void tqt_run_quant_gemm_1xnbias_clamp_##TDNAME##_qai8dxp_qsi4cxp_128x128_sm100a(                                   \
+        size_t m, size_t n, size_t k, const void *A, size_t lda, int a_type, void *A_packed, float *scale_a,           \
+        int32_t *zero_point_a, const void *B_packed, size_t ldb, const void *C, size_t ldc, void *D, size_t ldd,       \
+        const void *bias, TDTYPE clamp_min, TDTYPE clamp_max, const float *scale_b)                                    \
+    {                                                                                                                  \
+        run_quant_w4a8(m, n, k, A, lda, a_type, A_packed, scale_a, zero_point_a, B_packed, ldb, C, ldc, D, ldd, bias,  \
+                       (float)clamp_min, (float)clamp_max, scale_b, TDENUM);                                           \
+    }
+TQT_DEFINE_QUANT_GEMM(f32, float, Dtype::F32)
+TQT_DEFINE_QUANT_GEMM(f16, float16_t, Dtype::F16)
+TQT_DEFINE_QUANT_GEMM(bf16, bfloat16_t, Dtype::BF16)
+
 void tqt_run_quant_qai8dx_f32_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_q, size_t ldq,
                                      float *scale_a, int32_t *zero_point_a)
 {

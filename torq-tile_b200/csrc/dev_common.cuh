@@ -26,7 +26,8 @@ enum FaultCode : unsigned int {
     kFaultEpilogueWait = 0x400,   // epilogue waited for an accumulator
     kFaultConverterWait = 0x500,  // int4 converter waited for data or a free buffer
     kFaultGemvWait = 0x600,       // GEMV waited for its bulk copies
-    kFaultDrainWait = 0x700       // producer waited for its own copies while bailing out
+    kFaultDrainWait = 0x700,      // producer waited for its own copies while bailing out
+    kFaultGridBarrier = 0x800     // a CTA waited at the grid-wide barrier of the fused quantiser
 };
 
 // ---- packed-layout index arithmetic -------------------------------------------------------------

@@ -31,6 +31,7 @@
 
 #include "epilogues.cuh"
 #include "ptx_sm100.cuh"
+#include "quant_row.cuh"
 #include "umma_args.cuh"
 
 namespace tqt {
@@ -581,10 +582,51 @@ __device__ __forceinline__ uint32_t nib_pair(uint32_t w, uint32_t t)
 // 64 bytes x 128 rows with the 64-byte swizzle, which puts 16-byte segment s of row r at position s ^ ((r >> 1) & 3)
 // like a packed block.  The converters decode that nibble order and add up the row sums themselves (the packed
 // blocks carry them in their tails); cells outside the matrices arrive as zero bytes.
-template <TsKind KD, Dtype TD, bool PAIR, bool WIDE, bool REPL, bool UNP = false>
+// Grid-wide barrier for a launch whose CTAs are all resident (a cooperative launch): sense reversal on two words of
+// device memory, [arrivals, generation].  Thread 0 of every CTA arrives; the last arrival clears the count and advances
+// the generation, the others poll the generation with a bounded wait.  Returns false when the wait ran out (the
+// caller then skips its work and tears down).  Writes made before the barrier by any thread of any CTA are visible to
+// every thread after it, to bulk copies too (fence.proxy.async).
+__device__ __forceinline__ bool grid_barrier(unsigned int *sync, unsigned int nblocks, volatile int *sAbort, unsigned int *fault)
+{
+    __syncthreads();
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) {
+        int ok = 1;
+        unsigned int gen;
+        asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(gen) : "l"(sync + 1) : "memory");
+        __threadfence();
+        if (atomicAdd(sync, 1u) == nblocks - 1u) {
+            atomicExch(sync, 0u);
+            __threadfence();
+            atomicAdd(sync + 1, 1u);
+        } else {
+            const long long t0 = clock64();
+            unsigned int now;
+            while (true) {
+                asm volatile("ld.acquire.gpu.u32 %0, [%1];" : "=r"(now) : "l"(sync + 1) : "memory");
+                if (now != gen) break;
+                if (clock64() - t0 > ptx::wait_limit(sAbort)) {
+                    if (fault) atomicCAS(fault, 0u, (unsigned)kFaultGridBarrier);
+                    ok = 0;
+                    break;
+                }
+                __nanosleep(32);
+            }
+        }
+        __threadfence();
+        s_ok = ok;
+    }
+    __syncthreads();
+    asm volatile("fence.proxy.async;" ::: "memory");
+    return s_ok != 0;
+}
+
+template <TsKind KD, Dtype TD, bool PAIR, bool WIDE, bool REPL, bool UNP = false, bool FUSEQ = false>
 __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands *maps = nullptr)
 {
     static_assert(!UNP || (PAIR && !WIDE && !REPL), "row-major operands: CTA pairs with 192-row tiles only");
+    static_assert(!FUSEQ || (KD == TsKind::W4A8 && PAIR && !WIDE && !REPL && !UNP), "fused quantiser: W4A8 CTA pairs, 192-row tiles");
     using Cfg = TsCfg<KD, PAIR, WIDE>;
     using OutT = typename TdTraits<TD>::type;
     constexpr bool kF16 = Cfg::kF16;
@@ -662,8 +704,28 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
     const uint32_t hint_mma = (args.inject & 16u) ? 0u : ptx::kTryWaitSuspendNs;
     const uint32_t hint_conv = (args.inject & 32u) ? 0u : ptx::kTryWaitSuspendNs;
     bool conv_failed = false;   // a converter warp whose waits ran out does not help with the epilogue
+    bool run_roles = true;
+    if constexpr (FUSEQ) {
+        // Phase 0: every warp of the grid quantises rows of the activations into the packed A operand this kernel is
+        // about to read (one row per warp at a time), then all CTAs meet at a grid-wide barrier.
+        // rows are dealt round-robin over the CTAs first, so that few rows still spread over every SM
+        const uint32_t gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * (kTsThreads / 32u);
+        uint8_t *a_out = const_cast<uint8_t *>(args.A);
+        float *sa_out = const_cast<float *>(args.scale_a);
+        int32_t *zp_out = const_cast<int32_t *>(args.zp_a);
+        for (size_t row = gw; row < args.m; row += nw) {
+            if (args.q_bf16)
+                quant_row_warp<Dtype::BF16, true>(row, args.k, args.q_in, args.q_lda, a_out, 0, args.a_kblocks_total, sa_out, zp_out, lane);
+            else
+                quant_row_warp<Dtype::F16, true>(row, args.k, args.q_in, args.q_lda, a_out, 0, args.a_kblocks_total, sa_out, zp_out, lane);
+        }
+        asm volatile("fence.proxy.async;" ::: "memory");   // the packed rows are read by bulk copies after the barrier
+        run_roles = grid_barrier(args.grid_sync, gridDim.x, sAbort, args.fault);
+    }
 
-    if (warp == 0 || warp == 18) {
+    if (!run_roles) {
+        // the grid barrier ran out: nothing was started, fall through to the teardown
+    } else if (warp == 0 || warp == 18) {
         // ===================== producers (both CTAs) =====================
         // The issue of a bulk copy costs its warp a few hundred cycles whatever its size (measured: one
         // warp sustains one set of copies per ~400-500 cycles, n warps n times that, up to ~72 B/clk per
@@ -1060,7 +1122,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         conv_failed = !ok;
     }
 
-    if (warp >= 2 && warp < 18 && !conv_failed) {
+    if (run_roles && warp >= 2 && warp < 18 && !conv_failed) {
         // ===================== epilogue (8 warps per CTA): D^T, lane = output channel ==================
         // The converter warps, idle once the last K step of their last tile is in tensor memory, come here
         // too and take the upper half of that tile's column strips: the epilogue of the last tile overlaps no
@@ -1117,8 +1179,13 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                 float sa_l = 0.0f;
                 int32_t zp_l = 0;
                 if constexpr (!kF16) {
-                    sa_l = lane < nvalid ? __ldg(args.scale_a + m0 + c0 + lane) : 0.0f;
-                    zp_l = lane < nvalid ? __ldg(args.zp_a + m0 + c0 + lane) : 0;
+                    if constexpr (FUSEQ) {   // written by this launch's phase 0: coherent loads
+                        sa_l = lane < nvalid ? args.scale_a[m0 + c0 + lane] : 0.0f;
+                        zp_l = lane < nvalid ? args.zp_a[m0 + c0 + lane] : 0;
+                    } else {
+                        sa_l = lane < nvalid ? __ldg(args.scale_a + m0 + c0 + lane) : 0.0f;
+                        zp_l = lane < nvalid ? __ldg(args.zp_a + m0 + c0 + lane) : 0;
+                    }
                 }
                 __syncwarp();
                 OutT *dcol = static_cast<OutT *>(args.D) + (size_t)(m0 + c0) * args.ldd + n;
@@ -1200,6 +1267,13 @@ template <TsKind KD, Dtype TD, bool WIDE, bool REPL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1) gemm_ts_pair_kernel(const UmmaArgs args)
 {
     ts_body<KD, TD, true, WIDE, REPL>(args);
+}
+
+// W4A8 with the activation quantiser in front of the mainloop (one launch; needs every CTA resident: cooperative launch).
+template <Dtype TD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1) gemm_ts_pair_fusedq_kernel(const UmmaArgs args)
+{
+    ts_body<TsKind::W4A8, TD, true, false, false, false, true>(args);
 }
 
 // Row-major operands: the tensor maps travel as a kernel parameter.
@@ -1429,6 +1503,82 @@ Result ts_gemm_w4a16(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st)
 {
     if (td == Dtype::F16) return launch_ts<TsKind::W4A16, Dtype::F16>(a, pair, st);
     return launch_ts<TsKind::W4A16, Dtype::F32>(a, pair, st);
+}
+
+// ---- W4A8 with the activation quantiser fused in front (one cooperative launch) -----------------------------------
+// The grid barrier's two words live in a file-scope device array (the library allocates nothing); its address is looked
+// up once per device.  Two fused launches must not run at the same time on one device (they would share the barrier):
+// launches on one stream never do.
+static __device__ __align__(256) unsigned int g_fused_sync[64];
+
+static unsigned int *fused_sync_ptr()
+{
+    static unsigned int *cache[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    unsigned int *p = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+    if (!p) {
+        void *addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_fused_sync) != cudaSuccess) return nullptr;
+        p = static_cast<unsigned int *>(addr);
+        __atomic_store_n(&cache[dev], p, __ATOMIC_RELEASE);
+    }
+    return p;
+}
+
+template <Dtype TD>
+static Result launch_fusedq(const UmmaArgs &a, uint32_t tiles, cudaStream_t st)
+{
+    auto kern = gemm_ts_pair_fusedq_kernel<TD>;
+    constexpr uint32_t smem = TsCfg<TsKind::W4A8, true, false>::kSmem;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return Result{kLaunchFailed, (int)e};
+        attr_set[dev] = true;
+    }
+    const uint32_t max_pairs = (uint32_t)sm_count_cached() / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (tiles < max_pairs ? tiles : max_pairs), 1, 1);
+    cfg.blockDim = dim3(kTsThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;   // every CTA resident: the kernel's CTAs wait on one another
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return Result{kUnsupported, (int)e};   // the caller falls back to two launches
+    }
+    note_kernel(kKernelTsFusedQuant);
+    return Result{kOk, 0};
+}
+
+// kUnsupported: the caller runs the quantiser and the GEMM as two launches.
+Result ts_gemm_w4a8_fusedq(const UmmaArgs &a_in, Dtype td, const void *q_in, size_t q_lda, bool q_bf16, cudaStream_t st)
+{
+    UmmaArgs a = a_in;
+    const uint32_t nblocks = (a.n + 127) / 128, tnc = (nblocks + 1) / 2, pairs = (uint32_t)sm_count_cached() / 2;
+    const uint32_t t192 = ((a.m + kTsMT - 1) / kTsMT) * tnc, t256 = ((a.m + kTsMTWide - 1) / kTsMTWide) * tnc;
+    if (t192 > pairs && t256 <= pairs) return Result{kUnsupported, 0};   // the single-wave wide tile has no fused form
+    if (a.n_replicas || a.k > 4096 || a.k % 16 || q_lda % 8 || (reinterpret_cast<uintptr_t>(q_in) & 15)) return Result{kUnsupported, 0};
+    a.mt = kTsMT;
+    a.pdl = 0;
+    a.q_in = q_in;
+    a.q_lda = q_lda;
+    a.q_bf16 = q_bf16 ? 1 : 0;
+    a.grid_sync = fused_sync_ptr();
+    if (!a.grid_sync) return Result{kUnsupported, 0};
+    switch (td) {
+        case Dtype::F32: return launch_fusedq<Dtype::F32>(a, t192, st);
+        case Dtype::F16: return launch_fusedq<Dtype::F16>(a, t192, st);
+        default: return launch_fusedq<Dtype::BF16>(a, t192, st);
+    }
 }
 
 // int4 weights with row-major operands (the reference's unpacked "t" kernel types): activations [m, lda] of a_elem bytes

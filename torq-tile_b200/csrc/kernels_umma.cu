@@ -821,6 +821,23 @@ Result umma_gemm_w4a16_unpacked(const GemmCommon &g, size_t bl, const void *scal
     return ts_gemm_unpacked(a, true, td, g.lda, g.ldb, (cudaStream_t)g.stream);
 }
 
+// ---- W4A8 with the activation quantiser fused in front ----------------------------------------------------------
+Result ts_gemm_w4a8_fusedq(const UmmaArgs &a, Dtype td, const void *q_in, size_t q_lda, bool q_bf16, cudaStream_t st);
+
+Result umma_gemm_w4a8_fusedq(const GemmCommon &g, const W4A8Params &p, Dtype td, float cmin, float cmax, const void *q_in,
+                             size_t q_lda, bool q_bf16)
+{
+    UmmaArgs a{};
+    if (!fill_common(a, g, td == Dtype::F32 ? 4 : 2, 128, 128) || a.n_replicas || umma_variant() != 0) return Result{kUnsupported, 0};
+    a.scale_a = p.scale_a;
+    a.zp_a = p.zp_a;
+    a.scale_b = p.scale_b;
+    a.cmin_f = cmin;
+    a.cmax_f = cmax;
+    a.band_m = choose_band(g.m * g.k, g.n * g.k / 2);
+    return ts_gemm_w4a8_fusedq(a, td, q_in, q_lda, q_bf16, (cudaStream_t)g.stream);
+}
+
 // ---- unquantised f16 / bf16 GEMM on the CTA-pair kernel ---------------------------------------------------------
 Result pair_gemm_f16(const UmmaArgs &a, bool bf16, Dtype td, bool bias_per_row, size_t lda, size_t ldb, cudaStream_t st);
 

@@ -150,6 +150,11 @@ Result launch_im2col_pack_i8(void *stream, const ConvGeom &g, bool channel_first
 // Gather into a plain matrix: [rows, k] for channel-last, [k, rows] for channel-first.
 Result launch_im2col_i8(void *stream, const ConvGeom &g, bool channel_first, const void *activation, void *matrix);
 
+// W4A8 GEMM that quantises its own activations (16-bit [m, q_lda]) into g.A, p.scale_a, p.zp_a before its mainloop: one
+// cooperative launch.  kUnsupported when the shape has no fused form (the caller then launches quantiser and GEMM).
+Result umma_gemm_w4a8_fusedq(const GemmCommon &g, const W4A8Params &p, Dtype td, float clamp_min, float clamp_max,
+                             const void *q_in, size_t q_lda, bool q_bf16);
+
 // Unquantised GEMM (kernels_float.cu, kernels_pair.cu): operands of type ta in layouts la / lb (A never KMajor), C, bias
 // and D of type td, bias per column or per row.
 Result launch_gemm_float(const GemmCommon &g, Dtype ta, Dtype td, float clamp_min, float clamp_max, Layout la, Layout lb,
@@ -183,7 +188,7 @@ Result stream_read(const void *src, size_t bytes, void *sink, void *stream);
 // tensor-memory kernel.
 Path env_path();
 // Diagnostic for tests: which kernel family the most recent int8 x int8 launch of the process used (kKernel*).
-enum : int { kKernelNone = 0, kKernelSimt = 1, kKernelPairBlocks = 2, kKernelPairTma = 3, kKernelTsTma = 4 };
+enum : int { kKernelNone = 0, kKernelSimt = 1, kKernelPairBlocks = 2, kKernelPairTma = 3, kKernelTsTma = 4, kKernelTsFusedQuant = 5 };
 void note_kernel(int family);
 int last_kernel();
 int umma_variant();

@@ -25,6 +25,13 @@ struct UmmaArgs {
     uint32_t m, n, k;
     uint32_t a_src, b_src;     // kSrc*: int8 CTA-pair kernel with tensor maps only
     size_t b_ld;               // row stride (bytes) of a row-major B fetched through a tensor map
+    // fused activation quantiser (W4A8, CTA pairs): the kernel first quantises q_rows rows of q_in (16-bit, row stride
+    // q_lda elements) into its own packed A operand, scale_a and zp_a, one row per warp, and crosses a grid-wide
+    // barrier on grid_sync ([arrivals, generation], a per-device static) before its mainloop roles start
+    const void *q_in;
+    size_t q_lda;
+    int q_bf16;
+    unsigned int *grid_sync;
     int in_bf16;               // unquantised 16-bit GEMM: operands are bf16 (else f16)
     int bias_per_row;          // unquantised GEMM: bias indexed by output row (mx1bias types)
     const uint8_t *A;

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from . import (GemmReqI8, GemmW4A8, GemmW4A16, QaI8DxQsI4CxParams, QaI8QaI8QsI8CxParams, quant_pack_qai8dxp,
+from . import (GemmReqI8, GemmW4A8, GemmW4A16, QaI8DxQsI4CxParams, QaI8QaI8QsI8CxParams, quant_gemm_w4a8, quant_pack_qai8dxp,
                use_current_torch_stream)
 
 _TORCH_TD = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
@@ -40,7 +40,7 @@ class _HostPipelined:
         needs to issue it (column shards on several GPUs).  The result is the workspace's output tensor,
         available as ``.out`` on the callable.  A must stay alive and in place."""
         m = A.shape[0]
-        key = ("captured", A.data_ptr(), m, bool(gemm_only))
+        key = ("captured", A.data_ptr(), m, bool(gemm_only), bool(getattr(self, "fuse_quant", False)))
         fn = self._ws.get(key)
         if fn is None:
             self.prepare(A)          # allocates the workspace, leaves a valid packed A for a GEMM-only graph
@@ -48,9 +48,10 @@ class _HostPipelined:
             torch.cuda.current_stream().synchronize()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
-                if not gemm_only:
-                    self.prepare(A)
-                self.gemm(m)
+                if gemm_only:
+                    self.gemm(m)
+                else:
+                    self.step(A)
 
             def fn():
                 g.replay()
@@ -59,6 +60,11 @@ class _HostPipelined:
             fn.graph = g
             self._ws[key] = fn
         return fn
+
+    def step(self, A):
+        """prepare(A) + gemm: what one call of the operator enqueues."""
+        self.prepare(A)
+        return self.gemm(A.shape[0])
 
     def _pipe(self, m, chunks, in_dtype):
         key = ("pipe", m, chunks)
@@ -144,6 +150,7 @@ class W4A8Linear(_HostPipelined):
 
     def __init__(self, nib, scale_b, k, out_dtype="bf16", bias=None, clamp=None):
         self.uk = GemmW4A8(out_dtype)
+        self.out_name = out_dtype
         self.td = self.out_dtype = _TORCH_TD[out_dtype]
         self.n, self.k = nib.shape[0], k
         dev = nib.device
@@ -186,9 +193,23 @@ class W4A8Linear(_HostPipelined):
 
     prepare = quantize
 
+    #: quantise + GEMM as ONE cooperative launch where the library has a fused form for the shape (16-bit activations,
+    #: k <= 4096, more than 16 rows); the entry point runs the two kernels back to back otherwise
+    fuse_quant = False
+
+    def step(self, A, Cm=None):
+        if not self.fuse_quant:
+            self.quantize(A)
+            return self.gemm(A.shape[0], Cm)
+        m = A.shape[0]
+        ws = self.workspace(m)
+        use_current_torch_stream()
+        quant_gemm_w4a8(self.out_name, m, self.n, self.k, A, A.stride(0), ws["a_packed"], ws["scale_a"], ws["zp_a"], self.b_packed,
+                        self.k, Cm, self.n, ws["out"], ws["out"].stride(0), self.bias, self.clamp[0], self.clamp[1], self.scale_b)
+        return ws["out"]
+
     def __call__(self, A, Cm=None):
-        self.quantize(A)
-        return self.gemm(A.shape[0], Cm)
+        return self.step(A, Cm)
 
 
 class W8A8RequantLinear(_HostPipelined):
