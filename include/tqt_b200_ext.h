@@ -51,6 +51,21 @@ void tqt_run_quant_gemm_1xnbias_clamp_bf16_qai8dxp_qsi4cxp_128x128_sm100a(
     int32_t *zero_point_a, const void *B_packed, size_t ldb, const void *C, size_t ldc, void *D, size_t ldd,
     const void *bias, bfloat16_t clamp_min, bfloat16_t clamp_max, const float *scale_b);
 #endif
+/* Quantise + GEMM for callers that cannot allocate device memory and have no workspace to pass: a plug-in inside a
+ * serving process whose memory pool already owns the whole GPU (cudaMalloc fails there), or inside a loop that cannot
+ * afford cudaMalloc's device-wide synchronisation.  Same arithmetic as the call above with f32 output, but the packed
+ * activations, scales and zero points live in a static device array of the library (8 MiB + 64 KiB, held by every GPU
+ * that loads the library until the process exits); the call allocates nothing.
+ *   Limit: m <= 8192 and tqt_get_a_packed_size_gemm_1xnbias_clamp_f32_qai8dxp_qsi4cxp_128x128_sm100a(m, k) <= 8 MiB
+ *   (e.g. 2048 x 4096).  Larger calls launch nothing and leave status TQT_CUDA_UNSUPPORTED.
+ *   The first call on each device looks the array's address up (with that device current): make that call before any
+ *   stream capture.
+ *   All calls on a device share the array: calls that overlap on the GPU (different streams) race; calls on one stream
+ *   do not.  The array keeps the last call's contents; nothing in it has to be cleared between calls.
+ * No counterpart in the reference, whose callers own every buffer. */
+void tqt_run_quant_gemm_static_1xnbias_clamp_f32_qai8dxp_qsi4cxp_128x128_sm100a(
+    size_t m, size_t n, size_t k, const void *A, size_t lda, int a_type, const void *B_packed, size_t ldb, const void *C,
+    size_t ldc, void *D, size_t ldd, const void *bias, float clamp_min, float clamp_max, const float *scale_b);
 
 /* Same quantiser with a plain row-major int8 result [m,k] (ldq in elements), for the unpacked
  * (qai8dx) kernel types and for inspection. */

@@ -667,6 +667,19 @@ def quant_gemm_w4a8(td, m, n, k, A, lda, A_packed, scale_a, zero_point_a, B_pack
     check("quant_gemm_w4a8")
 
 
+def quant_gemm_w4a8_static(m, n, k, A, lda, B_packed, ldb, Cm, ldc, D, ldd, bias, clamp_min, clamp_max, scale_b):
+    """tqt_run_quant_gemm_static_1xnbias_clamp_f32_qai8dxp_qsi4cxp: quantise + W4A8 GEMM (f32 output) for callers that
+    cannot allocate: the intermediates live in a static device array of the library.  Status UNSUPPORTED (raised by
+    ``check``) when the call exceeds the array."""
+    f = getattr(lib(), f"tqt_run_quant_gemm_static_1xnbias_clamp_f32_qai8dxp_qsi4cxp_{VARIANT}")
+    f.argtypes = [_sz, _sz, _sz, _vp, _sz, C.c_int, _vp, _sz, _vp, _sz, _vp, _sz, _vp, C.c_float, C.c_float, _vp]
+    f.restype = None
+    a_type = _A_TYPE[_TA_NAMES[str(A.dtype).replace("torch.", "")]]
+    f(m, n, k, _addr(A), lda, a_type, _addr(B_packed), ldb, _addr(Cm), ldc, _addr(D), ldd, _addr(bias), clamp_min, clamp_max,
+      _addr(scale_b))
+    check("quant_gemm_w4a8_static")
+
+
 def quant_qai8dx(A, A_q, scale_a, zero_point_a):
     """Same quantiser with a plain row-major int8 result."""
     ta = _TA_NAMES[str(A.dtype).replace("torch.", "")]
@@ -709,6 +722,7 @@ EXTENSION_SYMBOLS = (
      "tqt_cuda_debug_last_kernel"]
     + [f"tqt_run_quant_pack_qai8dxp_{t}_{VARIANT}" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_quant_gemm_1xnbias_clamp_{t}_qai8dxp_qsi4cxp_{VARIANT}" for t in ("f32", "f16", "bf16")]
+    + [f"tqt_run_quant_gemm_static_1xnbias_clamp_f32_qai8dxp_qsi4cxp_{VARIANT}"]
     + [f"tqt_run_quant_qai8dx_{t}_sm100a" for t in ("f32", "f16", "bf16")]
     + [f"tqt_run_{n}_{VARIANT}" for n in ("a_unpack_i8", "a_unpack_f16", "bt_unpack_qsi4cxp", "bt_unpack_qsi4c2p")]
 )

@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libtorq_tile_b200.so")
 OBJ = os.path.join(HERE, "build")
 
-CU_SOURCES = ["kernels_pack.cu", "kernels_simt.cu", "kernels_umma.cu", "kernels_pair.cu", "kernels_gemv.cu", "kernels_conv.cu", "kernels_float.cu"]
+CU_SOURCES = ["kernels_pack.cu", "kernels_simt.cu", "kernels_umma.cu", "kernels_pair.cu", "kernels_gemv.cu", "kernels_conv.cu", "kernels_float.cu", "static_scratch.cu"]
 CXX_SOURCES = ["abi.cpp", "dispatch.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--threads", "4"]

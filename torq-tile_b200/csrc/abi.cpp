@@ -451,6 +451,20 @@ TQT_DEFINE_QUANT_GEMM(f32, float, Dtype::F32)
 TQT_DEFINE_QUANT_GEMM(f16, float16_t, Dtype::F16)
 TQT_DEFINE_QUANT_GEMM(bf16, bfloat16_t, Dtype::BF16)
 
+// The variant that allocates nothing and takes no workspace: static_scratch.cu.
+void tqt_run_quant_gemm_static_1xnbias_clamp_f32_qai8dxp_qsi4cxp_128x128_sm100a(
+    size_t m, size_t n, size_t k, const void *A, size_t lda, int a_type, const void *B_packed, size_t ldb, const void *C,
+    size_t ldc, void *D, size_t ldd, const void *bias, float clamp_min, float clamp_max, const float *scale_b)
+{
+    if (a_type < 0 || a_type > 2 || (k & 1)) return set_invalid();
+    if (m && n && (!A || !B_packed || !D || !scale_b)) return set_invalid();
+    if (m == 0 || n == 0) return set_ok();
+    if (ldb < k) ldb = k;
+    if (!replicas_cover(m, n, D, ldd, 4)) return set_invalid();
+    GemmCommon g = common(m, n, k, nullptr, k, B_packed, ldb, C, ldc, D, ldd, bias);
+    set_result(quant_gemm_w4a8_static(g, A, lda, (Dtype)a_type, scale_b, Dtype::F32, clamp_min, clamp_max));
+}
+
 void tqt_run_quant_qai8dx_f32_sm100a(size_t m, size_t k, const void *A, size_t lda, void *A_q, size_t ldq,
                                      float *scale_a, int32_t *zero_point_a)
 {

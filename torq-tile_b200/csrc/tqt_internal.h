@@ -96,6 +96,11 @@ struct W4A8Params {
 Result launch_gemm_w4a8(const GemmCommon &g, const W4A8Params &p, Dtype td, float clamp_min, float clamp_max,
                         Path path);
 
+// Quantise + W4A8 GEMM with the intermediates in the library's own static device array (static_scratch.cu); g.A / g.lda
+// are filled in by the callee.  kUnsupported when the call exceeds the array.
+Result quant_gemm_w4a8_static(GemmCommon g, const void *A, size_t lda, Dtype ta, const float *scale_b, Dtype td,
+                              float clamp_min, float clamp_max);
+
 // W4A16 block-quant; A f16 packed, B qsi4c2 packed; td F16 or F32.
 Result launch_gemm_w4a16(const GemmCommon &g, size_t bl, const void *scale_b, size_t ldsb, Dtype td,
                          float clamp_min, float clamp_max, Path path);
