@@ -531,7 +531,7 @@ enum class TsKind : int { W4A8 = 0, W4A16 = 1 };
 
 constexpr uint32_t kTsMT = 192;            // activation rows per tile (MMA N) by default; 96 per CTA in a pair
 constexpr uint32_t kTsMTWide = 256;        // CTA pairs, launches of at most one tile per pair: one accumulator of 256 columns
-constexpr uint32_t kTsThreads = 608;       // warp 0 producer (step 0 of each group), 1 MMA, 2..9 epilogue, 10..17 converters, 18 producer (step 1)
+constexpr uint32_t kTsThreads = 640;       // warp 0 producer (step 0 of each group), 1 MMA, 2..9 epilogue, 10..17 converters, 18 producer (step 1), 19 second MMA issuer (CTA pairs)
 constexpr uint32_t kTsT = 4;               // tensor-memory operand stages (4 x 32 columns)
 
 // WIDE (CTA pairs only): 256 activation rows per tile on one accumulator, for launches of at most one tile per pair.
@@ -646,6 +646,10 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                        kRsumFull = kTmemFull + 4, kRsumEmpty = kTmemFull + 6;
     uint32_t *sTmemBase = reinterpret_cast<uint32_t *>(bars + kTmemFull + 8);
     volatile int *sAbort = reinterpret_cast<volatile int *>(sTmemBase + 1);
+    // CTA pairs issue their MMAs from two threads that take the groups in turn (warp 1 the even ones, warp 19 the odd
+    // ones): sIssued counts the groups issued so far and hands the turn over
+    constexpr bool kDual = PAIR;
+    volatile uint32_t *sIssued = reinterpret_cast<volatile uint32_t *>(sTmemBase + 3);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;
@@ -666,13 +670,14 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         for (uint32_t g = 0; g < NG; ++g) ptx::mbar_init(BAR(kGroupDone + g), 1);
         for (uint32_t s = 0; s < 2; ++s) ptx::mbar_init(BAR(kConvFull + s), PAIR ? 16 : 8);   // per group slot: 8 converter warps per CTA
         for (uint32_t e = 0; e < 2; ++e) {
-            ptx::mbar_init(BAR(kTmemFull + e), 1);
+            ptx::mbar_init(BAR(kTmemFull + e), kDual ? 2 : 1);   // one commit per issuing thread
             ptx::mbar_init(BAR(kTmemEmpty + e), PAIR ? 16 : 8);
             ptx::mbar_init(BAR(kRsumFull + e), 8);   // 8 converter warps
             ptx::mbar_init(BAR(kRsumEmpty + e), 8);
         }
         sAbort[0] = 0;
         sAbort[1] = (int)args.wait_shift;
+        *sIssued = 0u;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -823,37 +828,54 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                 }
             }
         }
-    } else if (warp == 1) {
-        // ===================== MMA issuer (one thread of the leader CTA; the rest of the warp idles) ==========
-        // The issuing thread is the bottleneck of the mainloop, not the tensor pipe: a group of eight MMAs occupies
-        // the pipe for ~820 cycles (M256 x N192 x K32: 102.5 each), and the thread has to wait, fence, issue and
-        // commit inside that time.  Measured on this loop: each wait-plus-fence costs ~200-300 cycles even on a
-        // barrier that completed long ago, four MMA issues ~320, a commit ~160.  So the loop does one wait per
-        // GROUP (both steps' converters arrive on one barrier), issues the eight MMAs back to back from
-        // precomputed descriptors, and nothing else; one thread runs it, so no warp-wide reconvergence either.
-        if (rank == 0 && lane == 0) {
+    } else if (warp == 1 || warp == 19) {
+        // ===================== MMA issuers (one thread each, leader CTA; the rest of the warps idle) ==========
+        // A group of eight MMAs occupies the tensor pipe for ~820 cycles (M256 x N192 x K32: 102.5 each).  One thread
+        // that waits for the operands, fences, issues the eight MMAs and commits needs longer than that per group
+        // (measured with clock64 stamps: wait + fence 150-450 cycles even on a barrier that completed long ago, the
+        // eight issues 500-880 because they block once the pipe's queue is full, the commit 120-240) and the queue
+        // does not hold enough MMAs to cover its other work, so the pipe ran dry for a part of every group.  CTA pairs
+        // therefore issue from two threads in different SM sub-partitions that take the groups in turn: while one
+        // commits and waits for its next group's operands the other is already issuing.  The turn is handed over through
+        // a counter in shared memory, so the MMAs enter the pipe in group order (the first MMA of a tile overwrites the
+        // accumulator, and floating-point accumulation stays in one order).  Each thread commits its own groups; the
+        // accumulator-full barrier takes one commit from each.
+        const uint32_t who = warp == 1 ? 0u : 1u;
+        if (rank == 0 && lane == 0 && (kDual || who == 0u)) {
             const uint32_t idesc = kF16 ? ptx::make_idesc(1u, 0u, 0u, PAIR ? 256 : 128, mt)
                                         : ptx::make_idesc(2u, 1u, 1u, PAIR ? 256 : 128, mt);
             const uint64_t desc0 = ptx::make_desc_k_sw128(ptx::smem_u32(sAct));
             const uint32_t desc0_lo = (uint32_t)desc0, desc0_hi = (uint32_t)(desc0 >> 32);
             constexpr uint32_t kDescStage = kActBytes >> 4;   // descriptor address field counts 16-byte units
-            uint32_t Gc = 0, ti = 0, gs = 0;
+            constexpr uint32_t kStride = kDual ? 2u : 1u;     // this thread takes every kStride-th group
+            const uint32_t peer_tmem_full = (PAIR && kDual) ? ptx::mapa(BAR(kTmemFull), 1) : 0u;
+            uint32_t ti = 0, G0 = 0;   // G0 = groups of the tiles before this one
             bool ok = true;
-            // Whether the next group's operands are ready is tested one group ahead: the test is issued after the
+            // Whether this thread's next group's operands are ready is tested one group ahead: the test is issued after the
             // current group's MMAs and its result read after the commit, so its latency (~150-250 cycles even on a phase
             // that completed long ago) is off the issuing thread's critical path.  A phase seen complete stays
             // complete: the converters can only arrive for it again after the MMAs that are about to be issued.
             bool ready = false;
-            for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
+            for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti, G0 += ngroups) {
                 const uint32_t acc = ti & 1u, pha = (ti >> 1) & 1u;
                 if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kTmemEmpty + acc), pha ^ 1u, sAbort, args.fault, kFaultMmaWaitTmem))) {
                     ok = false;
                     break;
                 }
                 const uint32_t d_tmem = tmem_base + acc * mt;
-                for (uint32_t g = 0; g < ngroups; ++g, ++Gc) {
-                    const uint32_t slot = Gc & 1u;
-                    const bool tr = trace && Gc < 64u;   // diagnostic trace: first 64 groups of pair 0
+                const uint32_t g_first = kDual ? ((G0 & 1u) ^ who) : 0u;
+                if (g_first >= ngroups) {
+                    // a one-group tile that is the other thread's: only keep the accumulator-full barrier's count
+                    // (the wait above paces this: the barrier's previous phase has been consumed)
+                    if constexpr (PAIR && kDual) {
+                        ptx::mbar_arrive(BAR(kTmemFull + acc));
+                        ptx::mbar_arrive_cluster(peer_tmem_full + acc * 8u);
+                    }
+                    continue;
+                }
+                for (uint32_t g = g_first; g < ngroups; g += kStride) {
+                    const uint32_t Gc = G0 + g, slot = Gc & 1u, gs = Gc % NG;
+                    const bool tr = trace && who == 0u && Gc < 64u;   // diagnostic trace: first 64 groups of pair 0
                     if (tr) trace[Gc * 8 + 0] = clock64();
                     // all converter warps of both steps have written operand stages 2 slot, 2 slot + 1 (which also
                     // means the activation rows of the two shared-memory stages have landed, in both CTAs of a pair)
@@ -864,6 +886,21 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     }
                     if (tr) trace[Gc * 8 + 4] = trace[Gc * 8 + 5] = clock64();
                     ptx::tc_fence_after();
+                    if constexpr (kDual) {
+                        // this thread's turn: the other one has issued group Gc - 1
+                        if (*sIssued != Gc) {
+                            const long long t0 = clock64();
+                            while (*sIssued != Gc) {
+                                if (*sAbort || clock64() - t0 > ptx::wait_limit(sAbort)) {
+                                    if (!*sAbort && args.fault) atomicCAS(args.fault, 0u, (unsigned)kFaultMmaWaitFull);
+                                    *sAbort = 1;
+                                    ok = false;
+                                    break;
+                                }
+                            }
+                            if (!ok) break;
+                        }
+                    }
                     if (tr) trace[Gc * 8 + 1] = clock64();
                     const uint32_t two = (ksteps - g * 2u) >= 2u ? 1u : 0u;
                     const uint32_t dlo = desc0_lo + gs * 2u * kDescStage, a_t = tmem_a + slot * 64u;
@@ -874,20 +911,25 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                         if constexpr (PAIR) ptx::mma_i8_ts_pair_group8(d_tmem, a_t, dlo, desc0_hi, kDescStage, idesc, g, two);
                         else ptx::mma_i8_ts_group8(d_tmem, a_t, dlo, desc0_hi, kDescStage, idesc, g, two);
                     }
+                    if constexpr (kDual) {
+                        asm volatile("" ::: "memory");
+                        *sIssued = Gc + 1u;
+                    }
                     if (tr) trace[Gc * 8 + 2] = clock64();
-                    // the next group's barrier (the other slot; same parity formula with Gc + 1): tested between the MMAs
-                    // and the commit, read at the top of the next iteration
-                    const bool next_ready = ptx::mbar_test_wait(BAR(kConvFull + (slot ^ 1u)), ((Gc + 1u) >> 1) & 1u);
+                    // this thread's next group's barrier (same parity formula with Gc + kStride): tested between the
+                    // MMAs and the commit, read at the top of the next iteration
+                    const uint32_t Gn = Gc + kStride;
+                    const bool next_ready = ptx::mbar_test_wait(BAR(kConvFull + (Gn & 1u)), (Gn >> 1) & 1u);
+                    const bool last_mine = g + kStride >= ngroups;
                     if constexpr (PAIR) {
                         ptx::tc_commit_pair(BAR(kGroupDone + gs), 3);
-                        if (g == ngroups - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
+                        if (last_mine) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
                     } else {
                         ptx::tc_commit(BAR(kGroupDone + gs));
-                        if (g == ngroups - 1) ptx::tc_commit(BAR(kTmemFull + acc));
+                        if (last_mine) ptx::tc_commit(BAR(kTmemFull + acc));
                     }
                     if (tr) trace[Gc * 8 + 3] = clock64();
                     ready = next_ready;
-                    gs = gs + 1u == NG ? 0u : gs + 1u;
                 }
             }
         }
@@ -921,6 +963,12 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         };
         uint32_t Gc = 0, ti = 0;
         bool ok = true;
+        // A wait on an mbarrier costs 150-300 cycles even when its phase completed long ago, and a converter warp has two
+        // per step (its shared-memory stage has landed; the MMAs that read its tensor-memory stage are done).  Both are
+        // therefore tested ahead of their use, so that the test's latency runs under the expansion: the next step's
+        // stage at the end of the current step, the tensor-memory stage at the top of the step.  A phase seen complete
+        // stays complete until this warp's own announcement lets the pipeline advance.
+        bool full_ready = false;
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
             uint32_t tm_unused, tn;
             tile_coords(t, tmc, tnc, args.band_m, tm_unused, tn);
@@ -974,7 +1022,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                 // requested during the previous step of this warp (or are requested here, for a tile's first step)
                 __half sc8[8];
                 if constexpr (kF16) load_scales(g * 2 + h, step_valid, sc8);
-                if (!TQT_PTIMED(0, ptx::mbar_wait(BAR(kFull + s), phs, sAbort, args.fault, kFaultConverterWait))) {
+                const uint32_t Gp = Gc - 2u;
+                const bool done_ready = Gc < 2u || ptx::mbar_test_wait(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u);
+                if (!full_ready && !TQT_PTIMED(0, ptx::mbar_wait(BAR(kFull + s), phs, sAbort, args.fault, kFaultConverterWait))) {
                     ok = false;
                     break;
                 }
@@ -987,6 +1037,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                 if (!step_valid) {   // empty step of an odd tile: keep the barrier in step, nothing to convert
                     // like a real step, it may only be announced once the group that used this operand stage
                     // before is done: otherwise two announcements could fall into one phase of the barrier
+                    full_ready = false;   // the next step's stage has not been tested
                     if (Gc >= 2u) {
                         const uint32_t Gp = Gc - 2u;
                         if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
@@ -1093,9 +1144,12 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     }
                 }
                 if (ctr) ctr[1] = clock64();
+                {
+                    const uint32_t Gn = Gc + 1u;
+                    full_ready = ptx::mbar_test_wait(BAR(kFull + (Gn % NG) * 2u + h), (Gn / NG) & 1u);
+                }
                 // the MMAs of the group two groups back read this tensor-memory stage: they must be done
-                if (Gc >= 2u) {
-                    const uint32_t Gp = Gc - 2u;
+                if (!done_ready) {
                     if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
                                                               kFaultConverterWait, hint_conv))) {
                         ok = false;
