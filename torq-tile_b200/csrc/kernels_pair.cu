@@ -36,9 +36,17 @@
 
 namespace tqt {
 
+// Role timing (cycles spent in each role's waits) and the per-group clock64 traces exist only in builds with
+// -DTQT_B200_DIAG: the timed form of a wait duplicates its polling loop, and the kernels' hot loops are sensitive to code
+// size (a few predicated diagnostic branches in the converter loop cost the C3 GEMM 8 %).
+#ifdef TQT_B200_DIAG
+#define TQT_DIAG_ON(args) ((args).dbg != nullptr)
+#else
+#define TQT_DIAG_ON(args) false
+#endif
 #define TQT_PTIMED(slot, call)                                  \
     ([&]() -> bool {                                            \
-        if (!args.dbg) return (call);                           \
+        if (!TQT_DIAG_ON(args)) return (call);                  \
         const long long _t0 = clock64();                        \
         const bool _r = (call);                                 \
         wcyc[slot] += clock64() - _t0;                          \
@@ -159,7 +167,7 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
     ptx::tc_fence_after();
     const uint32_t tmem_base = *sTmemBase;
     long long wcyc[3] = {0, 0, 0};
-    const long long t_role0 = args.dbg ? clock64() : 0;
+    const long long t_role0 = TQT_DIAG_ON(args) ? clock64() : 0;
 
     if (warp == 0 || warp == 10) {
         // ===================== producers (both CTAs) =====================
@@ -410,10 +418,10 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
             for (uint32_t ch = 0; ch < nchunks; ++ch) {
                 uint32_t r[32];
                 __syncwarp();
-                const long long tl0 = args.dbg ? clock64() : 0;
+                const long long tl0 = TQT_DIAG_ON(args) ? clock64() : 0;
                 ptx::tmem_ld_32x32b_x32(t_addr + ch * 32u, r);
                 ptx::tmem_wait_ld();
-                if (args.dbg) wcyc[2] += clock64() - tl0;
+                if (TQT_DIAG_ON(args)) wcyc[2] += clock64() - tl0;
                 if (row_ok) {
                     const uint32_t c0 = ch * 32u;
                     const uint32_t nvalid = min(32u, ncols - c0);
@@ -493,7 +501,7 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
         }
     }
 
-    if (args.dbg && lane == 0 && (warp == 0 || warp == 1 || warp == 2)) {
+    if (TQT_DIAG_ON(args) && lane == 0 && (warp == 0 || warp == 1 || warp == 2)) {
         long long *d = args.dbg + (size_t)blockIdx.x * 16 + (warp == 0 ? 0 : warp == 1 ? 4 : 8);
         d[0] = wcyc[0];
         d[1] = wcyc[1];
@@ -699,13 +707,13 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
     // the preceding kernel (the activation quantiser); everything below reads what it produced.
     if (args.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     long long wcyc[3] = {0, 0, 0};
-    const long long t_role0 = args.dbg ? clock64() : 0;
+    const long long t_role0 = TQT_DIAG_ON(args) ? clock64() : 0;
     // how long a waiting thread may stay suspended in hardware before it polls again: the waits on the critical
     // loop (issuer <-> converters) poll often, the others sleep long
     // diagnostic: with inject bit 6 the timing buffer of pair 0's leader CTA receives a per-step timeline instead
     // (2048 int64: [0,512) issuer, [512,1024) converter warp 10, [1024,1536) converter warp 14, [1536,2048) epilogue warp 2)
-    long long *trace = (args.dbg && (args.inject & 64u) && blockIdx.x == 0) ? args.dbg : nullptr;
-    long long *trace_peer = (args.dbg && (args.inject & 64u) && blockIdx.x == 1) ? args.dbg + 1536 : nullptr;   // peer CTA: converter warp 12
+    long long *trace = (TQT_DIAG_ON(args) && (args.inject & 64u) && blockIdx.x == 0) ? args.dbg : nullptr;
+    long long *trace_peer = (TQT_DIAG_ON(args) && (args.inject & 64u) && blockIdx.x == 1) ? args.dbg + 1536 : nullptr;   // peer CTA: converter warp 12
     const uint32_t hint_mma = (args.inject & 16u) ? 0u : ptx::kTryWaitSuspendNs;
     const uint32_t hint_conv = (args.inject & 32u) ? 0u : ptx::kTryWaitSuspendNs;
     bool conv_failed = false;   // a converter warp whose waits ran out does not help with the epilogue
@@ -1249,10 +1257,10 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
 #pragma unroll 1
                 for (uint32_t q8 = 0; q8 < 32u && q8 < nvalid; q8 += 8u) {
                     uint32_t r[8];
-                    const long long tl0 = args.dbg ? clock64() : 0;
+                    const long long tl0 = TQT_DIAG_ON(args) ? clock64() : 0;
                     ptx::tmem_ld_32x32b_x8(t_addr + c0 + q8, r);
                     ptx::tmem_wait_ld();
-                    if (args.dbg) wcyc[2] += clock64() - tl0;
+                    if (TQT_DIAG_ON(args)) wcyc[2] += clock64() - tl0;
                     constexpr bool kRepl = replicate;
 #pragma unroll
                     for (uint32_t jj = 0; jj < 8; ++jj) {
@@ -1298,7 +1306,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         }
     }
 
-    if (args.dbg && !(args.inject & 64u) && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 10)) {
+    if (TQT_DIAG_ON(args) && !(args.inject & 64u) && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 10)) {
         long long *d = args.dbg + (size_t)blockIdx.x * 16 + (warp == 0 ? 0 : warp == 1 ? 4 : warp == 2 ? 8 : 12);
         d[0] = wcyc[0];
         d[1] = wcyc[1];

@@ -32,11 +32,16 @@
 
 namespace tqt {
 
-// Diagnostic: when a timing buffer is installed (tqt_cuda_debug_set_timing_buffer) each role adds up
-// the cycles it spends inside its waits; slot meaning is listed where the buffer is written.
+// Diagnostic (builds with -DTQT_B200_DIAG only): when a timing buffer is installed (tqt_cuda_debug_set_timing_buffer) each
+// role adds up the cycles it spends inside its waits; slot meaning is listed where the buffer is written.
+#ifdef TQT_B200_DIAG
+#define TQT_DIAG_ON(args) ((args).dbg != nullptr)
+#else
+#define TQT_DIAG_ON(args) false
+#endif
 #define TQT_TIMED(slot, call)                                   \
     ([&]() -> bool {                                            \
-        if (!args.dbg) return (call);                           \
+        if (!TQT_DIAG_ON(args)) return (call);                  \
         const long long _t0 = clock64();                        \
         const bool _r = (call);                                 \
         wcyc[slot] += clock64() - _t0;                          \
@@ -147,7 +152,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
     ptx::tc_fence_after();
     const uint32_t tmem_base = *sTmemBase;
     long long wcyc[3] = {0, 0, 0};
-    const long long t_role0 = args.dbg ? clock64() : 0;
+    const long long t_role0 = TQT_DIAG_ON(args) ? clock64() : 0;
 
     if (warp == 0) {
         // ===================== producer =====================
@@ -505,7 +510,7 @@ __global__ void __launch_bounds__(ModeCfg<BM>::kThreads, 1) gemm_umma_kernel(con
         }
     }
 
-    if (args.dbg && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 6)) {
+    if (TQT_DIAG_ON(args) && lane == 0 && (warp == 0 || warp == 1 || warp == 2 || warp == 6)) {
         // slots per CTA: producer 0-3, MMA 4-7, epilogue warp 8-11, converter warp 12-15; each {wait0, wait1, wait2, total}
         long long *d = args.dbg + (size_t)blockIdx.x * 16 + (warp == 0 ? 0 : warp == 1 ? 4 : warp == 2 ? 8 : 12);
         d[0] = wcyc[0];
