@@ -90,15 +90,12 @@ __device__ __forceinline__ long long wait_limit(volatile int *abort_flag) { retu
 // Bounded wait.  Every polling thread spins on try_wait, which itself suspends the thread in hardware for up to
 // hint_ns nanoseconds (sleeping between polls in software was measured to cost throughput, because the pipelines
 // are latency-sensitive).
+// The polling loop with its time limit is one out-of-line function: inlined at every wait it made the kernels' hot
+// loops several times longer, and they are sensitive to code size.  The inlined part is a single test.
 template <bool CLUSTER>
-__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                               unsigned int *fault, unsigned int code, uint32_t hint_ns)
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, unsigned int *fault,
+                                            unsigned int code, uint32_t hint_ns)
 {
-    if (!CLUSTER && hint_ns == 0u) {
-        if (mbar_test_wait(bar, parity)) return true;   // the common case on the critical loops: already complete
-    } else if (CLUSTER ? mbar_try_wait_cluster(bar, parity, hint_ns) : mbar_try_wait(bar, parity, hint_ns)) {
-        return true;
-    }
     const long long t0 = clock64();
     unsigned int spins = 0;
     for (;;) {
@@ -112,6 +109,18 @@ __device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, vo
             }
         }
     }
+}
+
+template <bool CLUSTER>
+__device__ __forceinline__ bool mbar_wait_impl(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                               unsigned int *fault, unsigned int code, uint32_t hint_ns)
+{
+    if (!CLUSTER && hint_ns == 0u) {
+        if (mbar_test_wait(bar, parity)) return true;   // the common case on the critical loops: already complete
+    } else if (CLUSTER ? mbar_try_wait_cluster(bar, parity, hint_ns) : mbar_try_wait(bar, parity, hint_ns)) {
+        return true;
+    }
+    return mbar_wait_slow<CLUSTER>(bar, parity, abort_flag, fault, code, hint_ns);
 }
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
