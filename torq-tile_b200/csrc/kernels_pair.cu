@@ -858,6 +858,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
             constexpr uint32_t kStride = kDual ? 2u : 1u;     // this thread takes every kStride-th group
             const uint32_t peer_tmem_full = (PAIR && kDual) ? ptx::mapa(BAR(kTmemFull), 1) : 0u;
             uint32_t ti = 0, G0 = 0;   // G0 = groups of the tiles before this one
+            uint32_t gs = kDual ? who : 0u;   // this thread's current group modulo NG, carried along
             bool ok = true;
             // Whether this thread's next group's operands are ready is tested one group ahead: the test is issued after the
             // current group's MMAs and its result read after the commit, so its latency (~150-250 cycles even on a phase
@@ -882,7 +883,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     continue;
                 }
                 for (uint32_t g = g_first; g < ngroups; g += kStride) {
-                    const uint32_t Gc = G0 + g, slot = Gc & 1u, gs = Gc % NG;
+                    const uint32_t Gc = G0 + g, slot = Gc & 1u;
                     const bool tr = trace && who == 0u && Gc < 64u;   // diagnostic trace: first 64 groups of pair 0
                     if (tr) trace[Gc * 8 + 0] = clock64();
                     // all converter warps of both steps have written operand stages 2 slot, 2 slot + 1 (which also
@@ -938,6 +939,8 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     }
                     if (tr) trace[Gc * 8 + 3] = clock64();
                     ready = next_ready;
+                    gs += kStride;
+                    if (gs >= NG) gs -= NG;
                 }
             }
         }
@@ -977,6 +980,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         // stage at the end of the current step, the tensor-memory stage at the top of the step.  A phase seen complete
         // stays complete until this warp's own announcement lets the pipeline advance.
         bool full_ready = false;
+        uint32_t gs = 0, phs = 0;   // Gc % NG and (Gc / NG) & 1, carried along instead of divided out every step
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
             uint32_t tm_unused, tn;
             tile_coords(t, tmc, tnc, args.band_m, tm_unused, tn);
@@ -1019,9 +1023,11 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     }
                 }
             };
-            for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc) {
-                const uint32_t h = cset, gs = Gc % NG, s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
-                const uint32_t phs = (Gc / NG) & 1u;
+            for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc, gs = gs + 1u == NG ? 0u : gs + 1u, phs ^= (gs == 0u ? 1u : 0u)) {
+                const uint32_t h = cset, s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
+                // the same for the group two back (its MMAs free this tensor-memory stage) and for the next group
+                const uint32_t gs_p = gs >= 2u ? gs - 2u : gs + NG - 2u, ph_p = gs >= 2u ? phs : phs ^ 1u;
+                const uint32_t gs_n = gs + 1u == NG ? 0u : gs + 1u, ph_n = gs + 1u == NG ? phs ^ 1u : phs;
                 const bool step_valid = g * 2 + h < ksteps;
                 long long *ctr = (trace && lane == 0 && quad == 2 && Gc < 64u) ? trace + 512 + cset * 512 + Gc * 4 : nullptr;
                 if (trace_peer && lane == 0 && quad == 2 && cset == 0 && Gc < 64u) ctr = trace_peer + Gc * 4;
@@ -1030,8 +1036,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                 // requested during the previous step of this warp (or are requested here, for a tile's first step)
                 __half sc8[8];
                 if constexpr (kF16) load_scales(g * 2 + h, step_valid, sc8);
-                const uint32_t Gp = Gc - 2u;
-                const bool done_ready = Gc < 2u || ptx::mbar_test_wait(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u);
+                const bool done_ready = Gc < 2u || ptx::mbar_test_wait(BAR(kGroupDone + gs_p), ph_p);
                 if (!full_ready && !TQT_PTIMED(0, ptx::mbar_wait(BAR(kFull + s), phs, sAbort, args.fault, kFaultConverterWait))) {
                     ok = false;
                     break;
@@ -1047,8 +1052,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     // before is done: otherwise two announcements could fall into one phase of the barrier
                     full_ready = false;   // the next step's stage has not been tested
                     if (Gc >= 2u) {
-                        const uint32_t Gp = Gc - 2u;
-                        if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
+                        if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + gs_p), ph_p, sAbort, args.fault,
                                                                   kFaultConverterWait))) {
                             ok = false;
                             break;
@@ -1152,13 +1156,10 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     }
                 }
                 if (ctr) ctr[1] = clock64();
-                {
-                    const uint32_t Gn = Gc + 1u;
-                    full_ready = ptx::mbar_test_wait(BAR(kFull + (Gn % NG) * 2u + h), (Gn / NG) & 1u);
-                }
+                full_ready = ptx::mbar_test_wait(BAR(kFull + gs_n * 2u + h), ph_n);
                 // the MMAs of the group two groups back read this tensor-memory stage: they must be done
                 if (!done_ready) {
-                    if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + Gp % NG), (Gp / NG) & 1u, sAbort, args.fault,
+                    if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + gs_p), ph_p, sAbort, args.fault,
                                                               kFaultConverterWait, hint_conv))) {
                         ok = false;
                         break;
