@@ -57,7 +57,7 @@ namespace tqt {
 // int8 x int8
 // ======================================================================================================
 constexpr uint32_t kI8Stages = 6;
-constexpr uint32_t kI8Threads = 352;   // warp 0 producer (even K steps), warp 1 MMA / relay, warps 2..9 epilogue, warp 10 producer (odd K steps)
+constexpr uint32_t kI8Threads = 384;   // warp 0 producer (even K steps), warp 1 MMA / relay, warps 2..9 epilogue, warp 10 producer (odd K steps), warp 11 second MMA issuer
 constexpr uint32_t kI8Smem = 1024 + kI8Stages * 32768 + 8 * 3 * 128 * 4 + 256;
 
 // Work items of the int8 CTA-pair kernel.  Item w is a pair tile (256 x 256: two 128-column blocks of the N side), except
@@ -126,6 +126,7 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
     constexpr uint32_t kFull = 0, kPeerFull = S, kEmpty = 2 * S, kTmemFull = 3 * S, kTmemEmpty = 3 * S + 2;
     uint32_t *sTmemBase = reinterpret_cast<uint32_t *>(bars + 3 * S + 4);
     volatile int *sAbort = reinterpret_cast<volatile int *>(sTmemBase + 1);
+    volatile uint32_t *sIssued = reinterpret_cast<volatile uint32_t *>(sTmemBase + 3);   // K steps issued so far: whose turn it is
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
@@ -150,11 +151,12 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
             ptx::mbar_init(BAR(kEmpty + s), 1);
         }
         for (uint32_t e = 0; e < 2; ++e) {
-            ptx::mbar_init(BAR(kTmemFull + e), 1);
+            ptx::mbar_init(BAR(kTmemFull + e), 2);     // one commit per issuing thread
             ptx::mbar_init(BAR(kTmemEmpty + e), 16);   // 8 epilogue warps of each CTA
         }
         sAbort[0] = 0;
         sAbort[1] = (int)args.wait_shift;
+        *sIssued = 0u;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -242,14 +244,18 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                 }
             }
         }
-    } else if (warp == 1 && rank == 0) {
-        // ===================== MMA issuer (one thread of the leader CTA) =====================
-        // The issuing thread bounds this mainloop as it does the tensor-memory kernels' (a K step occupies the
-        // pipe for ~680 cycles; the thread needed ~1100 with two waits, a fence, four separate MMA issues and a
-        // commit per step): so one thread runs the loop, the four MMAs of a step go out in one instruction block
-        // from precomputed descriptor words, and whether the NEXT step's two barriers (own stage landed, peer's
-        // stage landed) have completed is tested after this step's MMAs and read after its commit, which takes the
-        // latency of the test (~200 cycles even on a long-completed phase) off the critical path.
+    } else if ((warp == 1 || warp == 11) && rank == 0) {
+        // ===================== MMA issuers (one thread each, leader CTA) =====================
+        // A K step occupies the pipe for ~680 cycles; one thread that waits for the step's two barriers (own stage
+        // landed, peer's stage landed), fences, issues the four MMAs and commits needs longer than that, and the pipe's
+        // queue does not cover the difference.  Two threads in different SM sub-partitions therefore take the K steps in
+        // turn (the counter sIssued hands the turn over, so the MMAs enter the pipe in step order: the first MMA of a
+        // tile overwrites the accumulator, and floating-point accumulation keeps one order): while one commits and tests
+        // its next step's barriers the other is issuing.  Each thread commits its own steps; the accumulator-full
+        // barrier takes one commit from each.  The four MMAs of a step go out in one instruction block from precomputed
+        // descriptor words, and the next step's barriers are tested after this step's MMAs and read after its commit.
+        static_assert(S % 2u == 0u, "the two issuing threads keep to the stages of their own parity");
+        const uint32_t who = warp == 1 ? 0u : 1u;
         if (lane == 0) {
             const bool b_mn = TMA && args.b_src == kSrcTmaMn;
             const uint32_t ffmt = args.in_bf16 ? 1u : 0u;
@@ -262,7 +268,8 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                                                       : ptx::make_desc_k_sw128(ptx::smem_u32(sB));
             const uint32_t a_lo0 = (uint32_t)a_desc0, a_hi = (uint32_t)(a_desc0 >> 32);
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
-            uint32_t it = 0, ti = 0, s = 0, ph = 0;
+            const uint32_t peer_tmem_full = ptx::mapa(BAR(kTmemFull), 1);
+            uint32_t it = 0, ti = 0, s = who, ph = 0;   // it = K steps of the items before this one; s, ph = this thread's next stage
             bool ok = true, ready = false;
             for (uint32_t w = pair; w < sp.count && ok; w += npairs) {
                 I8Work wk;
@@ -274,13 +281,33 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                     break;
                 }
                 const uint32_t d_tmem = tmem_base + acc * 256u;
-                for (uint32_t kb = 0; kb < KB; ++kb, ++it) {
+                const uint32_t kb_first = (it & 1u) ^ who;
+                if (kb_first >= KB) {
+                    // a one-step item that is the other thread's: only keep the accumulator-full barrier's count (the
+                    // wait above paces this: the barrier's previous phase has been consumed)
+                    ptx::mbar_arrive(BAR(kTmemFull + acc));
+                    ptx::mbar_arrive_cluster(peer_tmem_full + acc * 8u);
+                }
+                for (uint32_t kb = kb_first; kb < KB; kb += 2u) {
+                    const uint32_t step = it + kb;
                     if (!ready && (!TQT_PTIMED(1, ptx::mbar_wait(BAR(kFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, 0u)) ||
                                    !TQT_PTIMED(2, ptx::mbar_wait(BAR(kPeerFull + s), ph, sAbort, args.fault, kFaultMmaWaitFull, 0u)))) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
+                    if (*sIssued != step) {   // this thread's turn comes when the other one has issued step - 1
+                        const long long t0 = clock64();
+                        while (*sIssued != step) {
+                            if (*sAbort || clock64() - t0 > ptx::wait_limit(sAbort)) {
+                                if (!*sAbort && args.fault) atomicCAS(args.fault, 0u, (unsigned)kFaultMmaWaitFull);
+                                *sAbort = 1;
+                                ok = false;
+                                break;
+                            }
+                        }
+                        if (!ok) break;
+                    }
                     if constexpr (kFloat) {
                         if (b_mn)   // K slices of 16 rows of 128 bytes
                             ptx::mma_f16_ss_pair_group4<128>(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
@@ -290,15 +317,18 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                         ptx::mma_i8_ss_pair_group4<256>(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);
                     else
                         ptx::mma_i8_ss_pair_group4(d_tmem, a_lo0 + s * 1024u, a_hi, b_lo0 + s * 1024u, b_hi, idesc, kb);   // 16 KiB stages = 1024 units
-                    // the next step's stage (a phase seen complete stays complete until this thread commits it free again)
-                    const uint32_t s1 = s + 1u == S ? 0u : s + 1u, ph1 = s + 1u == S ? ph ^ 1u : ph;
+                    asm volatile("" ::: "memory");
+                    *sIssued = step + 1u;
+                    // this thread's next step's stage (a phase seen complete stays complete until this thread commits it free again)
+                    const uint32_t s1 = s + 2u >= S ? s + 2u - S : s + 2u, ph1 = s + 2u >= S ? ph ^ 1u : ph;
                     const bool next_ready = ptx::mbar_test_wait(BAR(kFull + s1), ph1) && ptx::mbar_test_wait(BAR(kPeerFull + s1), ph1);
                     ptx::tc_commit_pair(BAR(kEmpty + s), 3);
-                    if (kb == KB - 1) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
+                    if (kb + 2u >= KB) ptx::tc_commit_pair(BAR(kTmemFull + acc), 3);
                     ready = next_ready;
                     s = s1;
                     ph = ph1;
                 }
+                it += KB;
                 ++ti;
             }
         }
@@ -320,6 +350,8 @@ __device__ __forceinline__ void pair_i8_body(const UmmaArgs &args, const TmaOper
                 __syncwarp();
             }
         }
+    } else if (warp == 11) {
+        // the peer CTA's second-issuer warp has no role
     } else {
         // ===================== epilogue (8 warps per CTA) =====================
         const uint32_t quad = warp & 3u, half = (warp - 2u) >> 2;   // TMEM lane quadrant, column half
