@@ -162,7 +162,7 @@ def workload_config(cfg, world, n_local, R, set_bytes, graphs=True):
     """The `config` object of the JSON line; both arms (ours, reference) print the same one."""
     return {"workload": CONFIGS[cfg][3],
             "step": "activation quantise+pack (or pack) kernel + run_gemm, weights packed once outside" +
-                    ("; the two launches replayed as one CUDA graph" if graphs else ""),
+                    ("; launches replayed as CUDA graphs of several consecutive steps" if graphs else ""),
             "parallelism": f"N-sharded x{world}, no collective" if world > 1 else "single GPU",
             "n_per_gpu": n_local,
             "l2": f"rotating {R} weight/output sets per rank ({R * set_bytes / 1e6:.0f} MB) > 126 MB L2"}
@@ -343,17 +343,34 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, block=None):
+        """Time exactly `steps` steps.  block = (U, graph): the timed steps are issued as steps / U replays of one CUDA graph
+        that holds U consecutive steps (the sets rotate inside it), so that the host's launch cost per step does not bound
+        steps of a few tens of microseconds (column shards on 4-8 GPUs); the warm-up steps are single-step launches."""
         for i in range(warmup):
             fn(i)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for i in range(steps):
-            fn(warmup + i)
+        if block is None:
+            for i in range(steps):
+                fn(warmup + i)
+        else:
+            U, graph = block
+            assert steps % U == 0
+            for _ in range(steps // U):
+                graph.replay()
         e1.record()
         barrier()
         return max_over_ranks(e0.elapsed_time(e1) / steps)
+
+    def block_size(steps, R):
+        """Steps per block graph: the smallest divisor of `steps` that holds every rotating set and at least 8 steps."""
+        want = max(R, 8)
+        for u in range(want, steps + 1):
+            if steps % u == 0:
+                return u
+        return steps
 
     def measure(cfg, steps, warmup, sustain_s, with_e2e, with_gather):
         """One prefill configuration on this rank's column shard: device-timed step, run_gemm alone, sustained loop
@@ -387,18 +404,33 @@ def run_ours(args):
             def gemm_only(i):   # noqa: F811
                 return gemm_graphs[i % R]()
 
+            U = block_size(steps, R)
+
+            def block_graph(eager):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    for j in range(U):
+                        eager(j)
+                return g
+
+            step_block = (U, block_graph(lambda j: layers[j % R].step(a_dev)))
+            gemm_block = (U, block_graph(lambda j: layers[j % R].gemm(M)))
+        else:
+            U, step_block, gemm_block = 1, None, None
+
         ops = 2.0 * M * N * K               # whole job (all ranks)
         ops_local = 2.0 * M * n_local * K
         unit = "TOPS" if cfg != "c5" else "TFLOP/s"
         sampler = ClockSampler(local_rank)
         if rank == 0:
             sampler.start()
-        ms_step = timed(step_device, steps, warmup)
-        ms_gemm = timed(gemm_only, steps, warmup)
+        ms_step = timed(step_device, steps, warmup, step_block)
+        ms_gemm = timed(gemm_only, steps, warmup, gemm_block)
         # the timed region lasts milliseconds; keep the same step loop running for a second or so, so that the clock
         # samples (and the sustained figure) describe the kernels under load, power cap included
         sustain_steps = int(min(20000, max(steps, math.ceil(sustain_s * 1e3 / ms_step)))) if sustain_s > 0 else 0
-        ms_sustained = timed(step_device, sustain_steps, 0) if sustain_steps else None
+        sustain_steps = -(-sustain_steps // U) * U
+        ms_sustained = timed(step_device, sustain_steps, 0, step_block) if sustain_steps else None
         clocks = sampler.stop() if rank == 0 else None
         if clocks is not None:
             clocks["note"] = (f"sampled every {ClockSampler.PERIOD_MS} ms from the start of the timed region to the end of a "
@@ -767,7 +799,8 @@ def bench_decode(torch, lin, pkg, dev, peaks, K=4096, N=4096, copies=48, reps=20
     phases = None
     if M == 1:
         # clock64 phase stamps of the dp4a GEMV (thread 0 of every CTA), one buffer per launch of the same chain: where a
-        # GEMV's time goes when its predecessor is still running (the stamped graph is not the timed one)
+        # GEMV's time goes when its predecessor is still running (the stamped graph is not the timed one).  The stamps exist
+        # in library builds with -DTQT_B200_DIAG only; otherwise the buffers stay zero and `phases` is null.
         lib.tqt_cuda_debug_set_timing_buffer.argtypes = [ctypes.c_void_p]
         bufs = [torch.zeros(148 * 16, dtype=torch.int64, device=dev) for _ in layers]
 

@@ -43,8 +43,12 @@ def _stale(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, diag: bool = False) -> str:
+    """diag: compile the kernels' role timing, traces and GEMV phase stamps in (-DTQT_B200_DIAG; always a full rebuild,
+    and the next ordinary build has to be forced too).  They are left out of ordinary builds because the hot loops are
+    sensitive to code size."""
     os.makedirs(OBJ, exist_ok=True)
+    force = force or diag
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh", ".inc"))]
     headers += [os.path.join(HERE, "..", "include", f) for f in os.listdir(os.path.join(HERE, "..", "include"))]
     nvcc, gxx = _nvcc(), _gxx()
@@ -56,7 +60,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         objs.append(obj)
         if force or _stale(obj, [path] + headers):
             if src.endswith(".cu"):
-                cmd = [nvcc] + NVCC_FLAGS + ["-c", path, "-o", obj]
+                cmd = [nvcc] + NVCC_FLAGS + (["-DTQT_B200_DIAG"] if diag else []) + ["-c", path, "-o", obj]
             else:
                 cmd = [gxx] + CXX_FLAGS + ["-c", path, "-o", obj]
             if verbose:
@@ -78,4 +82,4 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose=True))
+    print(build(force="--force" in sys.argv, verbose=True, diag="--diag" in sys.argv))
