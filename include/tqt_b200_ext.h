@@ -140,7 +140,9 @@ void tqt_cuda_debug_inject_wait_failure(unsigned wait_shift, unsigned flags);
 
 /* Diagnostic: install a caller-owned device buffer of 16 int64 per CTA (148 CTAs at most) that the
  * tensor-core GEMM fills with the cycles each warp role spent waiting (producer, MMA issuer, one
- * epilogue warp, one converter warp: {wait0, wait1, wait2, total} each).  NULL switches it off. */
+ * epilogue warp, one converter warp: {wait0, wait1, wait2, total} each), and the one-row GEMV with six phase stamps per CTA.
+ * NULL switches it off.  The kernels contain this instrumentation only when the library was built with -DTQT_B200_DIAG
+ * (their hot loops are sensitive to code size); an ordinary build accepts the call and leaves the buffer untouched. */
 void tqt_cuda_debug_set_timing_buffer(void *dev_ptr);
 
 /* Diagnostic: launch, on the calling thread's stream, a kernel with the GEMV's launch shape (thread
