@@ -571,7 +571,15 @@ enum class TsKind : int { W4A8 = 0, W4A16 = 1 };
 
 constexpr uint32_t kTsMT = 192;            // activation rows per tile (MMA N) by default; 96 per CTA in a pair
 constexpr uint32_t kTsMTWide = 256;        // CTA pairs, launches of at most one tile per pair: one accumulator of 256 columns
-constexpr uint32_t kTsThreads = 640;       // warp 0 producer (step 0 of each group), 1 MMA, 2..9 epilogue, 10..17 converters, 18 producer (step 1), 19 second MMA issuer (CTA pairs)
+// Warp roles: 0 producer (step 0 of each group), 1 MMA issuer, 2..9 epilogue, then the converter sets of four warps
+// each (set c expands the K steps c, c + sets, c + 2 sets, ... numbered through the whole launch), then the producer of
+// step 1 and the second MMA issuer (CTA pairs).  W4A8 has two converter sets (640 threads); W4A16, whose expansion is
+// heavier (an f16 per weight, block scales), three (768 threads): 3.86 -> 3.62 ms at the 8192 x 8192 x 28672 shape,
+// while a third set changed nothing for W4A8.
+template <TsKind KD>
+constexpr uint32_t ts_sets() { return KD == TsKind::W4A16 ? 3u : 2u; }
+template <TsKind KD>
+constexpr uint32_t ts_threads() { return 32u * (10u + 4u * ts_sets<KD>() + 2u); }
 constexpr uint32_t kTsT = 4;               // tensor-memory operand stages (4 x 32 columns)
 
 // WIDE (CTA pairs only): 256 activation rows per tile on one accumulator, for launches of at most one tile per pair.
@@ -585,7 +593,8 @@ struct TsCfg {
     static constexpr uint32_t kActRows = PAIR ? kMT / 2u : kMT;    // activation rows this CTA stages per K step
     static constexpr uint32_t kActBytes = kActRows * 128u;         // stage stride
     static constexpr uint32_t kNibGroupBytes = kF16 ? 8192u : 2u * 8448u;   // int4 bytes per group of two K steps
-    static constexpr uint32_t kUsed = 1024u + S * kActBytes + NG * kNibGroupBytes + 2u * 2u * 128u * 4u + 512u;
+    static constexpr uint32_t kSets = ts_sets<KD>();               // converter sets
+    static constexpr uint32_t kUsed = 1024u + S * kActBytes + NG * kNibGroupBytes + 2u * kSets * 128u * 4u + 512u;
     // more than half of an SM's shared memory: one CTA per SM, which owns all 512 tensor-memory columns
     static constexpr uint32_t kSmem = kUsed > 120u * 1024u ? kUsed : 120u * 1024u;
 };
@@ -680,14 +689,15 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *sAct = smem;                                   // S x 12 or 24 KiB (multiples of 1024)
     uint8_t *sNib = sAct + S * kActBytes;                   // NG groups of packed int4
-    int32_t *sRsum = reinterpret_cast<int32_t *>(sNib + NG * Cfg::kNibGroupBytes);   // [2 accumulators][2 converter sets][128]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sRsum + 512);
+    int32_t *sRsum = reinterpret_cast<int32_t *>(sNib + NG * Cfg::kNibGroupBytes);   // [2 accumulators][converter sets][128]
+    constexpr uint32_t kSets = Cfg::kSets, kProd1Warp = 10u + 4u * kSets, kIssuer1Warp = kProd1Warp + 1u;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sRsum + 2u * kSets * 128u);
     constexpr uint32_t kFull = 0, kGroupDone = S, kConvFull = S + NG, kTmemFull = S + NG + T, kTmemEmpty = kTmemFull + 2,
                        kRsumFull = kTmemFull + 4, kRsumEmpty = kTmemFull + 6;
     uint32_t *sTmemBase = reinterpret_cast<uint32_t *>(bars + kTmemFull + 8);
     volatile int *sAbort = reinterpret_cast<volatile int *>(sTmemBase + 1);
-    // CTA pairs issue their MMAs from two threads that take the groups in turn (warp 1 the even ones, warp 19 the odd
-    // ones): sIssued counts the groups issued so far and hands the turn over
+    // CTA pairs issue their MMAs from two threads that take the groups in turn (warp 1 the even ones, the last warp the
+    // odd ones): sIssued counts the groups issued so far and hands the turn over
     constexpr bool kDual = PAIR;
     volatile uint32_t *sIssued = reinterpret_cast<volatile uint32_t *>(sTmemBase + 3);
 
@@ -712,7 +722,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         for (uint32_t e = 0; e < 2; ++e) {
             ptx::mbar_init(BAR(kTmemFull + e), kDual ? 2 : 1);   // one commit per issuing thread
             ptx::mbar_init(BAR(kTmemEmpty + e), PAIR ? 16 : 8);
-            ptx::mbar_init(BAR(kRsumFull + e), 8);   // 8 converter warps
+            ptx::mbar_init(BAR(kRsumFull + e), 4u * kSets);   // the converter warps
             ptx::mbar_init(BAR(kRsumEmpty + e), 8);
         }
         sAbort[0] = 0;
@@ -754,7 +764,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         // Phase 0: every warp of the grid quantises rows of the activations into the packed A operand this kernel is
         // about to read (one row per warp at a time), then all CTAs meet at a grid-wide barrier.
         // rows are dealt round-robin over the CTAs first, so that few rows still spread over every SM
-        const uint32_t gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * (kTsThreads / 32u);
+        const uint32_t gw = warp * gridDim.x + blockIdx.x, nw = gridDim.x * (blockDim.x / 32u);
         uint8_t *a_out = const_cast<uint8_t *>(args.A);
         float *sa_out = const_cast<float *>(args.scale_a);
         int32_t *zp_out = const_cast<int32_t *>(args.zp_a);
@@ -770,7 +780,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
 
     if (!run_roles) {
         // the grid barrier ran out: nothing was started, fall through to the teardown
-    } else if (warp == 0 || warp == 18) {
+    } else if (warp == 0 || warp == kProd1Warp) {
         // ===================== producers (both CTAs) =====================
         // The issue of a bulk copy costs its warp a few hundred cycles whatever its size (measured: one
         // warp sustains one set of copies per ~400-500 cycles, n warps n times that, up to ~72 B/clk per
@@ -868,7 +878,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                 }
             }
         }
-    } else if (warp == 1 || warp == 19) {
+    } else if (warp == 1 || warp == kIssuer1Warp) {
         // ===================== MMA issuers (one thread each, leader CTA; the rest of the warps idle) ==========
         // A group of eight MMAs occupies the tensor pipe for ~820 cycles (M256 x N192 x K32: 102.5 each).  One thread
         // that waits for the operands, fences, issues the eight MMAs and commits needs longer than that per group
@@ -1013,6 +1023,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         // stays complete until this warp's own announcement lets the pipeline advance.
         bool full_ready = false;
         uint32_t gs = 0, phs = 0;   // Gc % NG and (Gc / NG) & 1, carried along instead of divided out every step
+        uint32_t own = cset;        // the next K step this warp expands: steps are numbered 2 Gc + h through the launch
         for (uint32_t t = pair; t < num_tiles && ok; t += npairs, ++ti) {
             uint32_t tm_unused, tn;
             tile_coords(t, tmc, tnc, args.band_m, tm_unused, tn);
@@ -1056,12 +1067,15 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                 }
             };
             for (uint32_t g = 0; g < ngroups && ok; ++g, ++Gc, gs = gs + 1u == NG ? 0u : gs + 1u, phs ^= (gs == 0u ? 1u : 0u)) {
-                const uint32_t h = cset, s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
-                // the same for the group two back (its MMAs free this tensor-memory stage) and for the next group
+                if ((own >> 1) != Gc) continue;   // neither step of this group is this set's
+                const uint32_t h = own & 1u, s = gs * 2 + h, ts = (Gc & 1u) * 2 + h;
+                own += kSets;
+                // the same for the group two back (its MMAs free this tensor-memory stage) and for this warp's next step
                 const uint32_t gs_p = gs >= 2u ? gs - 2u : gs + NG - 2u, ph_p = gs >= 2u ? phs : phs ^ 1u;
-                const uint32_t gs_n = gs + 1u == NG ? 0u : gs + 1u, ph_n = gs + 1u == NG ? phs ^ 1u : phs;
+                const uint32_t h_n = own & 1u, gs_n1 = gs + (own >> 1) - Gc;   // one or two groups on
+                const uint32_t gs_n = gs_n1 >= NG ? gs_n1 - NG : gs_n1, ph_n = gs_n1 >= NG ? phs ^ 1u : phs;
                 const bool step_valid = g * 2 + h < ksteps;
-                long long *ctr = (trace && lane == 0 && quad == 2 && Gc < 64u) ? trace + 512 + cset * 512 + Gc * 4 : nullptr;
+                long long *ctr = (trace && lane == 0 && quad == 2 && cset < 2u && h == cset && Gc < 64u) ? trace + 512 + cset * 512 + Gc * 4 : nullptr;
                 if (trace_peer && lane == 0 && quad == 2 && cset == 0 && Gc < 64u) ctr = trace_peer + Gc * 4;
                 if (ctr) ctr[0] = clock64();
                 // W4A16: the block scales of a step (one per 8-k word) do not depend on the barriers; they were
@@ -1188,7 +1202,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     }
                 }
                 if (ctr) ctr[1] = clock64();
-                full_ready = ptx::mbar_test_wait(BAR(kFull + gs_n * 2u + h), ph_n);
+                full_ready = ptx::mbar_test_wait(BAR(kFull + gs_n * 2u + h_n), ph_n);
                 // the MMAs of the group two groups back read this tensor-memory stage: they must be done
                 if (!done_ready) {
                     if (!TQT_PTIMED(2, ptx::mbar_wait(BAR(kGroupDone + gs_p), ph_p, sAbort, args.fault,
@@ -1209,7 +1223,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     ok = false;
                     break;
                 }
-                sRsum[acc * 256 + cset * 128 + row] = rsum;
+                sRsum[(acc * kSets + cset) * 128u + row] = rsum;
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(BAR(kRsumFull + acc));
             }
@@ -1260,7 +1274,9 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
                     ok = false;
                     break;
                 }
-                rs = sRsum[acc * 256 + row] + sRsum[acc * 256 + 128 + row];
+                rs = 0;
+#pragma unroll
+                for (uint32_t c = 0; c < kSets; ++c) rs += sRsum[(acc * kSets + c) * 128u + row];
             }
             ptx::tc_fence_after();
             const uint32_t t_addr = tmem_base + acc * mt + half * hcols + ((quad * 32u) << 16);
@@ -1359,21 +1375,21 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
 }
 
 template <TsKind KD, Dtype TD, bool WIDE, bool REPL>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1) gemm_ts_pair_kernel(const UmmaArgs args)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ts_threads<KD>(), 1) gemm_ts_pair_kernel(const UmmaArgs args)
 {
     ts_body<KD, TD, true, WIDE, REPL>(args);
 }
 
 // W4A8 with the activation quantiser in front of the mainloop (one launch; needs every CTA resident: cooperative launch).
 template <Dtype TD>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1) gemm_ts_pair_fusedq_kernel(const UmmaArgs args)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ts_threads<TsKind::W4A8>(), 1) gemm_ts_pair_fusedq_kernel(const UmmaArgs args)
 {
     ts_body<TsKind::W4A8, TD, true, false, false, false, true>(args);
 }
 
 // Row-major operands: the tensor maps travel as a kernel parameter.
 template <TsKind KD, Dtype TD>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ts_threads<KD>(), 1)
     gemm_ts_pair_tma_kernel(const UmmaArgs args, const __grid_constant__ TmaOperands maps)
 {
     ts_body<KD, TD, true, false, false, true>(args, &maps);
@@ -1381,7 +1397,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTsThreads, 1)
 
 // Same kernel on one CTA (cta_group::1): the CTA stages all 192 activation rows itself.
 template <TsKind KD, Dtype TD>
-__global__ void __launch_bounds__(kTsThreads, 1) gemm_ts_kernel(const UmmaArgs args)
+__global__ void __launch_bounds__(ts_threads<KD>(), 1) gemm_ts_kernel(const UmmaArgs args)
 {
     ts_body<KD, TD, false, false, false>(args);
 }
@@ -1577,12 +1593,12 @@ static Result launch_ts(const UmmaArgs &a_in, bool pair, cudaStream_t st)
     constexpr uint32_t kSmemN = TsCfg<KD, true, false>::kSmem, kSmemW = TsCfg<KD, true, true>::kSmem;
     if (a.n_replicas) {   // output replicas: CTA-pair kernels only
         if (!pair) return Result{kUnsupported, 0};
-        if (mt == kTsMTWide) return launch_grid(gemm_ts_pair_kernel<KD, TD, true, true>, a, tiles, true, kTsThreads, kSmemW, st, set_wr);
-        return launch_grid(gemm_ts_pair_kernel<KD, TD, false, true>, a, tiles, true, kTsThreads, kSmemN, st, set_pr);
+        if (mt == kTsMTWide) return launch_grid(gemm_ts_pair_kernel<KD, TD, true, true>, a, tiles, true, ts_threads<KD>(), kSmemW, st, set_wr);
+        return launch_grid(gemm_ts_pair_kernel<KD, TD, false, true>, a, tiles, true, ts_threads<KD>(), kSmemN, st, set_pr);
     }
-    if (pair && mt == kTsMTWide) return launch_grid(gemm_ts_pair_kernel<KD, TD, true, false>, a, tiles, true, kTsThreads, kSmemW, st, set_w);
-    if (pair) return launch_grid(gemm_ts_pair_kernel<KD, TD, false, false>, a, tiles, true, kTsThreads, kSmemN, st, set_p);
-    return launch_grid(gemm_ts_kernel<KD, TD>, a, tiles, false, kTsThreads, TsCfg<KD, false, false>::kSmem, st, set_s);
+    if (pair && mt == kTsMTWide) return launch_grid(gemm_ts_pair_kernel<KD, TD, true, false>, a, tiles, true, ts_threads<KD>(), kSmemW, st, set_w);
+    if (pair) return launch_grid(gemm_ts_pair_kernel<KD, TD, false, false>, a, tiles, true, ts_threads<KD>(), kSmemN, st, set_p);
+    return launch_grid(gemm_ts_kernel<KD, TD>, a, tiles, false, ts_threads<KD>(), TsCfg<KD, false, false>::kSmem, st, set_s);
 }
 
 Result ts_gemm_w4a8(const UmmaArgs &a, Dtype td, bool pair, cudaStream_t st)
@@ -1637,7 +1653,7 @@ static Result launch_fusedq(const UmmaArgs &a, uint32_t tiles, cudaStream_t st)
     const uint32_t max_pairs = (uint32_t)sm_count_cached() / 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (tiles < max_pairs ? tiles : max_pairs), 1, 1);
-    cfg.blockDim = dim3(kTsThreads, 1, 1);
+    cfg.blockDim = dim3(ts_threads<TsKind::W4A8>(), 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
@@ -1688,7 +1704,7 @@ static Result launch_ts_tma(const UmmaArgs &a_in, const TmaOperands &maps, cudaS
     const uint32_t tiles = ((a.m + kTsMT - 1) / kTsMT) * ((nblocks + 1) / 2);
     static bool set_attr[64] = {false};
     note_kernel(kKernelTsTma);
-    return launch_grid(gemm_ts_pair_tma_kernel<KD, TD>, a, tiles, true, kTsThreads, TsCfg<KD, true, false>::kSmem, st, set_attr, maps);
+    return launch_grid(gemm_ts_pair_tma_kernel<KD, TD>, a, tiles, true, ts_threads<KD>(), TsCfg<KD, true, false>::kSmem, st, set_attr, maps);
 }
 
 Result ts_gemm_unpacked(const UmmaArgs &a, bool w4a16, Dtype td, size_t lda, size_t ldb, cudaStream_t st)
