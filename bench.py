@@ -237,7 +237,7 @@ ISSUE_RATE_INT8_TOPS = 2.0 * 128 * 192 * 32 / 102.5 * 148 * 1.965e9 / 1e12   # 4
 # profiles/ (file named beside each figure): taken under ncu on an earlier run of the same kernels, NOT measured by
 # the run that prints the line.
 NCU_TRAFFIC = {"c3": (55.7e6, "profiles/gemm_ts_pair_w4a8_c3.txt"), "c4": (33.7e6, "profiles/gemm_pair_i8_c4.txt"),
-               "c5": (1500.0e6, "profiles/gemm_ts_pair_w4a16_c5.txt")}
+               "c5": (1438.5e6, "profiles/gemm_ts_pair_w4a16_c5.txt")}
 
 
 def algorithmic_bytes(cfg, n_local):
