@@ -573,13 +573,14 @@ constexpr uint32_t kTsMT = 192;            // activation rows per tile (MMA N) b
 constexpr uint32_t kTsMTWide = 256;        // CTA pairs, launches of at most one tile per pair: one accumulator of 256 columns
 // Warp roles: 0 producer (step 0 of each group), 1 MMA issuer, 2..9 epilogue, then the converter sets of four warps
 // each (set c expands the K steps c, c + sets, c + 2 sets, ... numbered through the whole launch), then the producer of
-// step 1 and the second MMA issuer (CTA pairs).  W4A8 has two converter sets (640 threads); W4A16, whose expansion is
-// heavier (an f16 per weight, block scales), three (768 threads): 3.86 -> 3.62 ms at the 8192 x 8192 x 28672 shape,
-// while a third set changed nothing for W4A8.
-template <TsKind KD>
-constexpr uint32_t ts_sets() { return KD == TsKind::W4A16 ? 3u : 2u; }
-template <TsKind KD>
-constexpr uint32_t ts_threads() { return 32u * (10u + 4u * ts_sets<KD>() + 2u); }
+// step 1 and the second MMA issuer (CTA pairs).  Packed W4A8 has two converter sets (640 threads); W4A16, whose expansion
+// is heavier (an f16 per weight, block scales), and the row-major nibble order (byte permutes, row sums by dp4a) three
+// (768 threads): 3.86 -> 3.62 ms at the 8192 x 8192 x 28672 W4A16 shape, while a third set changed nothing for packed W4A8.
+template <TsKind KD, bool UNP = false>
+__host__ __device__ constexpr uint32_t ts_sets() { return (KD == TsKind::W4A16 || UNP) ? 3u : 2u; }
+template <TsKind KD, bool UNP = false>
+__host__ __device__ constexpr uint32_t ts_threads() { return 32u * (10u + 4u * ts_sets<KD, UNP>() + 2u); }
+constexpr uint32_t kTsMaxSets = 3;
 constexpr uint32_t kTsT = 4;               // tensor-memory operand stages (4 x 32 columns)
 
 // WIDE (CTA pairs only): 256 activation rows per tile on one accumulator, for launches of at most one tile per pair.
@@ -593,8 +594,7 @@ struct TsCfg {
     static constexpr uint32_t kActRows = PAIR ? kMT / 2u : kMT;    // activation rows this CTA stages per K step
     static constexpr uint32_t kActBytes = kActRows * 128u;         // stage stride
     static constexpr uint32_t kNibGroupBytes = kF16 ? 8192u : 2u * 8448u;   // int4 bytes per group of two K steps
-    static constexpr uint32_t kSets = ts_sets<KD>();               // converter sets
-    static constexpr uint32_t kUsed = 1024u + S * kActBytes + NG * kNibGroupBytes + 2u * kSets * 128u * 4u + 512u;
+    static constexpr uint32_t kUsed = 1024u + S * kActBytes + NG * kNibGroupBytes + 2u * kTsMaxSets * 128u * 4u + 512u;
     // more than half of an SM's shared memory: one CTA per SM, which owns all 512 tensor-memory columns
     static constexpr uint32_t kSmem = kUsed > 120u * 1024u ? kUsed : 120u * 1024u;
 };
@@ -690,8 +690,8 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
     uint8_t *sAct = smem;                                   // S x 12 or 24 KiB (multiples of 1024)
     uint8_t *sNib = sAct + S * kActBytes;                   // NG groups of packed int4
     int32_t *sRsum = reinterpret_cast<int32_t *>(sNib + NG * Cfg::kNibGroupBytes);   // [2 accumulators][converter sets][128]
-    constexpr uint32_t kSets = Cfg::kSets, kProd1Warp = 10u + 4u * kSets, kIssuer1Warp = kProd1Warp + 1u;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(sRsum + 2u * kSets * 128u);
+    constexpr uint32_t kSets = ts_sets<KD, UNP>(), kProd1Warp = 10u + 4u * kSets, kIssuer1Warp = kProd1Warp + 1u;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sRsum + 2u * kTsMaxSets * 128u);
     constexpr uint32_t kFull = 0, kGroupDone = S, kConvFull = S + NG, kTmemFull = S + NG + T, kTmemEmpty = kTmemFull + 2,
                        kRsumFull = kTmemFull + 4, kRsumEmpty = kTmemFull + 6;
     uint32_t *sTmemBase = reinterpret_cast<uint32_t *>(bars + kTmemFull + 8);
@@ -1389,7 +1389,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ts_threads<TsKind::W
 
 // Row-major operands: the tensor maps travel as a kernel parameter.
 template <TsKind KD, Dtype TD>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ts_threads<KD>(), 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ts_threads<KD, true>(), 1)
     gemm_ts_pair_tma_kernel(const UmmaArgs args, const __grid_constant__ TmaOperands maps)
 {
     ts_body<KD, TD, true, false, false, true>(args, &maps);
@@ -1704,7 +1704,7 @@ static Result launch_ts_tma(const UmmaArgs &a_in, const TmaOperands &maps, cudaS
     const uint32_t tiles = ((a.m + kTsMT - 1) / kTsMT) * ((nblocks + 1) / 2);
     static bool set_attr[64] = {false};
     note_kernel(kKernelTsTma);
-    return launch_grid(gemm_ts_pair_tma_kernel<KD, TD>, a, tiles, true, ts_threads<KD>(), TsCfg<KD, true, false>::kSmem, st, set_attr, maps);
+    return launch_grid(gemm_ts_pair_tma_kernel<KD, TD>, a, tiles, true, ts_threads<KD, true>(), TsCfg<KD, true, false>::kSmem, st, set_attr, maps);
 }
 
 Result ts_gemm_unpacked(const UmmaArgs &a, bool w4a16, Dtype td, size_t lda, size_t ldb, cudaStream_t st)
