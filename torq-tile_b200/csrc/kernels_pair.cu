@@ -718,7 +718,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; ++s) ptx::mbar_init(BAR(kFull + s), 1);
         for (uint32_t g = 0; g < NG; ++g) ptx::mbar_init(BAR(kGroupDone + g), 1);
-        for (uint32_t s = 0; s < 2; ++s) ptx::mbar_init(BAR(kConvFull + s), PAIR ? 16 : 8);   // per group slot: 8 converter warps per CTA
+        for (uint32_t s = 0; s < 2; ++s) ptx::mbar_init(BAR(kConvFull + s), PAIR ? 16 : 8);   // per group slot: two steps announced by four converter warps each, per CTA
         for (uint32_t e = 0; e < 2; ++e) {
             ptx::mbar_init(BAR(kTmemFull + e), kDual ? 2 : 1);   // one commit per issuing thread
             ptx::mbar_init(BAR(kTmemEmpty + e), PAIR ? 16 : 8);
@@ -784,7 +784,7 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         // ===================== producers (both CTAs) =====================
         // The issue of a bulk copy costs its warp a few hundred cycles whatever its size (measured: one
         // warp sustains one set of copies per ~400-500 cycles, n warps n times that, up to ~72 B/clk per
-        // SM), so the two K steps of a group are issued by two warps: warp 0 step 0, warp 18 step 1.
+        // SM), so the two K steps of a group are issued by two warps: warp 0 step 0, the warp after the converters step 1.
         const uint32_t ph = warp == 0 ? 0u : 1u;
         uint32_t Gc = 0;   // groups issued so far
         uint32_t withheld = 0xffffffffu;   // group whose stage this warp left without copies and arrive (test knob)
@@ -988,12 +988,13 @@ __device__ __forceinline__ void ts_body(const UmmaArgs &args, const TmaOperands 
         }
         __syncwarp();
     } else if (warp >= 10) {
-        // ===================== converters (warps 10..17): int4 -> MMA operand type, into tensor memory ========
-        // Two warps per tensor-memory lane quadrant: set 0 (warps 10..13) takes step 0 of every group, set 1
-        // (warps 14..17) step 1.  A step is fetched and expanded into registers before the warp waits for its
-        // tensor-memory stage to be free; the store is then announced at once (deferring the announcement
-        // past the next step's expansion, to hide the store latency, put that expansion on the MMA's
-        // critical path: the converters have slack, the MMA issuer has none).
+        // ===================== converters (warps 10 ..): int4 -> MMA operand type, into tensor memory ========
+        // Sets of four warps, one per tensor-memory lane quadrant.  The K steps are numbered through the whole launch
+        // (2 * group + step) and set c takes the steps c, c + sets, ...: with two sets (packed W4A8) set 0 has step 0 of
+        // every group and set 1 step 1; with three every set meets both.  A step is fetched and expanded into registers
+        // before the warp waits for its tensor-memory stage to be free; the store is then announced at once (deferring the
+        // announcement past the next step's expansion, to hide the store latency, would put that expansion on the MMAs'
+        // critical path).
         const uint32_t quad = warp & 3u, cset = (warp - 10u) >> 2;
         const uint32_t row = quad * 32u + lane;
         const uint32_t swz_in = (row >> 1) & 3u;
